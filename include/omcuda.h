@@ -1,0 +1,282 @@
+/*
+ * libomcuda: B200 (sm_100a) implementation of onnx-mlir's quantized-linear
+ * path behind the reference's own C calling conventions.
+ *
+ * Three groups of entry points, all plain C:
+ *
+ *  1. Accelerator runtime hooks, named and shaped like the in-tree NNPA
+ *     accelerator's (src/Accelerators/NNPA/Runtime/OMRuntimeNNPA.c:36-250):
+ *     OMIsInitAccelCUDA, OMInitAccelCUDA, OMInitCompatibleAccelCUDA,
+ *     OMShutdownAccelCUDA.  The generated run_main_graph calls the
+ *     "compatible" hook first (src/Conversion/KrnlToLLVM/KrnlEntryPoint.cpp:149-187).
+ *
+ *  2. krnl.call targets (omcuda<Op>): what the compiler plugin emits in place
+ *     of the CPU loops.  Calling convention of krnl.call
+ *     (src/Dialect/Krnl/Krnl.td:52-96, src/Conversion/KrnlToLLVM/KrnlCall.cpp:34-226):
+ *     output tensors first, then inputs, each a non-owning `OMTensor *`
+ *     (NULL for an absent optional input), then integer attributes as int64_t
+ *     and float attributes as double in attribute-name order; return void;
+ *     the callee neither allocates nor frees the tensors' buffers.  Buffers
+ *     may live in host or device memory; host buffers are staged through HBM
+ *     inside the call.  Errors are sticky per thread (see omcudaGetLastError)
+ *     and set errno, the convention run_main_graph uses to report failure
+ *     (src/Runtime/ExecutionSession.cpp:324-362).
+ *
+ *  3. Device-pointer entry points (omcudaDev<Op>): the same kernels for
+ *     callers that already hold device buffers and a CUDA stream.
+ *
+ * There is no CPU fallback: every entry point fails with OMCUDA_ECUDA when no
+ * usable GPU is present.
+ */
+#ifndef OMCUDA_H
+#define OMCUDA_H
+
+#include <stdint.h>
+
+#include "omcuda_runtime_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------------- */
+/* Status                                                                   */
+/* ---------------------------------------------------------------------- */
+
+typedef enum {
+  OMCUDA_OK = 0,
+  OMCUDA_EINVAL = 1,    /* bad argument: dtype, rank, shape, stride, NULL */
+  OMCUDA_ENOMEM = 2,    /* device or host allocation failed */
+  OMCUDA_ECUDA = 3,     /* CUDA runtime / driver error, or no GPU */
+  OMCUDA_ETIMEDOUT = 4, /* a bounded device-side wait gave up */
+  OMCUDA_ENOTSUP = 5    /* valid ONNX but outside what the kernels cover */
+} omcudaStatus;
+
+/* Sticky per-thread status of the krnl.call-level entry points: the first
+ * failure is kept and later calls return without doing work until cleared.
+ * Replaces nothing in the reference; run_main_graph would test it (or errno)
+ * before building its output list. */
+int omcudaGetLastError(void);
+const char *omcudaGetLastErrorString(void);
+void omcudaClearError(void);
+
+/* ---------------------------------------------------------------------- */
+/* Accelerator runtime hooks (OMRuntimeNNPA.c:36-118,156-250 pattern)       */
+/* ---------------------------------------------------------------------- */
+
+extern long OMIsInitAccelCUDA;
+/* Thread-safe, idempotent: picks the device (OMCUDA_DEVICE, else LOCAL_RANK,
+ * else 0), creates the library stream and the device-memory pool. */
+void OMInitAccelCUDA(void);
+/* Returns non-zero when the library can serve a model compiled against
+ * version `versionNum` (0xMMmmpp); on failure sets errno = EPERM and returns
+ * 0, as OMInitCompatibleAccelNNPA does (OMRuntimeNNPA.c:156-232). */
+uint64_t OMInitCompatibleAccelCUDA(uint64_t versionNum);
+void OMShutdownAccelCUDA(void);
+#define OMCUDA_VERSION 0x000100u
+
+/* ---------------------------------------------------------------------- */
+/* Device-resident tensors and streams                                      */
+/* ---------------------------------------------------------------------- */
+
+/* A stock OMTensor whose buffer is device memory from the library pool.  The
+ * wrapper is non-owning in the reference's sense (omTensorDestroy must not
+ * free() a device pointer): release with omcudaTensorDestroy. */
+OMTensor *omcudaTensorCreateOnDevice(
+    const int64_t *shape, int64_t rank, OM_DATA_TYPE dtype);
+/* Copies (host or device source) into a new device / owning host tensor. */
+OMTensor *omcudaTensorToDevice(const OMTensor *src);
+OMTensor *omcudaTensorToHost(const OMTensor *src);
+/* Releases a tensor made by the three calls above (buffer and wrapper). */
+void omcudaTensorDestroy(OMTensor *t);
+/* 1 when the tensor's data pointer is device memory, 0 for host memory. */
+int omcudaTensorIsOnDevice(const OMTensor *t);
+/* Pinned host memory for fast staging of host tensors. */
+void *omcudaHostAlloc(int64_t bytes);
+void omcudaHostFree(void *p);
+/* Raw device memory from the pool (stream-ordered reuse on the library
+ * stream). */
+void *omcudaDeviceAlloc(int64_t bytes);
+void omcudaDeviceFree(void *p);
+/* The stream krnl.call-level entry points launch on (a cudaStream_t).  A
+ * caller may substitute its own for the calling thread; NULL restores the
+ * library stream. */
+void *omcudaGetStream(void);
+void omcudaSetStream(void *stream);
+void omcudaSynchronize(void);
+/* Declares that a tensor's buffer is a model constant (krnl.global): its
+ * prepared form (K-major copy and column sums of a MatMulInteger /
+ * QLinearMatMul B operand) is built once and cached until
+ * omcudaForgetConstants.  Without this, B is prepared on every call. */
+void omcudaRegisterConstant(const OMTensor *t);
+void omcudaForgetConstants(void);
+/* Number of kernels this library has launched in this process. */
+int64_t omcudaLaunchCount(void);
+
+/* ---------------------------------------------------------------------- */
+/* krnl.call targets                                                        */
+/* ---------------------------------------------------------------------- */
+
+/* Replaces ONNXDynamicQuantizeLinearOpLowering
+ * (src/Conversion/ONNXToKrnl/Quantization/DynamicQuantizeLinear.cpp:101-158).
+ * x: f32 any rank; y: u8 same shape; yScale: f32 rank 0; yZp: u8 rank 0. */
+void omcudaDynamicQuantizeLinear(
+    OMTensor *y, OMTensor *yScale, OMTensor *yZp, const OMTensor *x);
+
+/* Replaces ONNXQuantizeLinearOpLowering (QuantizeLinear.cpp:155-246):
+ * per-tensor scale, u8 or i8 output chosen by y's dtype; zp may be NULL. */
+void omcudaQuantizeLinear(OMTensor *y, const OMTensor *x,
+    const OMTensor *scale, const OMTensor *zp);
+
+/* Replaces ONNXMatMulIntegerOpLowering
+ * (src/Conversion/ONNXToKrnl/Math/MatMulInteger.cpp:32-92) and the i32
+ * onnx.MatMul it creates.  A: u8/i8 [..,M,K]; B: u8/i8 [K,N]; Y: i32
+ * [..,M,N]; aZp: NULL, scalar, [1] or [M]; bZp: NULL, scalar, [1] or [N]. */
+void omcudaMatMulInteger(OMTensor *Y, const OMTensor *A, const OMTensor *B,
+    const OMTensor *aZp, const OMTensor *bZp);
+
+/* Replaces ONNXQLinearMatMulOpLowering
+ * (src/Conversion/ONNXToKrnl/Math/QLinearMatMul.cpp:32-142), including its
+ * wrap-around (not saturating) conversion of the result to 8 bits. */
+void omcudaQLinearMatMul(OMTensor *y, const OMTensor *a, const OMTensor *aScale,
+    const OMTensor *aZp, const OMTensor *b, const OMTensor *bScale,
+    const OMTensor *bZp, const OMTensor *yScale, const OMTensor *yZp);
+
+/* Replaces the scalar body of ONNXDequantizeLinearOp
+ * (src/Conversion/ONNXToKrnl/Math/Elementwise.cpp:1438-1461), per-tensor. */
+void omcudaDequantizeLinear(OMTensor *y, const OMTensor *x,
+    const OMTensor *scale, const OMTensor *zp);
+
+/* The fused subgraph DynamicQuantizeLinear -> MatMulInteger -> Cast(f32) ->
+ * Mul -> [Mul] -> [Add], i.e. the pattern the NNPA plugin matches in
+ * src/Accelerators/NNPA/Conversion/ONNXToZHigh/ONNXToZHigh.cpp:895-1215,
+ * replacing the four CPU lowerings it spans.  X: f32 [..,K]; Wq: i8/u8 [K,N];
+ * wScale: f32 scalar or [N]; wZp: NULL or matching Wq; bias: NULL or f32 [N].
+ * scaleForm 0: Y = f32(acc) * (x_scale * w_scale) + bias
+ * scaleForm 1: Y = (f32(acc) * x_scale) * w_scale + bias */
+void omcudaDynQuantLinear(OMTensor *Y, const OMTensor *X, const OMTensor *Wq,
+    const OMTensor *wScale, const OMTensor *wZp, const OMTensor *bias,
+    int64_t scaleForm);
+
+/* fp32 ops a quantized encoder graph holds between its linears. */
+/* src/Conversion/ONNXToKrnl/Math/Softmax.cpp:268-312 (axis = last). */
+void omcudaSoftmax(OMTensor *y, const OMTensor *x, int64_t axis);
+/* src/Conversion/ONNXToKrnl/NN/Normalization.cpp:342-406,748-880 (axis = last);
+ * bias may be NULL. */
+void omcudaLayerNormalization(OMTensor *y, const OMTensor *x,
+    const OMTensor *scale, const OMTensor *bias, int64_t axis, double epsilon);
+/* src/Conversion/ONNXToKrnl/Math/Elementwise.cpp:358-388 (approximate=none). */
+void omcudaGelu(OMTensor *y, const OMTensor *x);
+/* Elementwise Add with equal shapes (Math/Elementwise.cpp). */
+void omcudaAdd(OMTensor *y, const OMTensor *a, const OMTensor *b);
+/* src/Conversion/ONNXToKrnl/Tensor/Transpose.cpp, perm (0,2,1,3) on rank 4. */
+void omcudaTranspose0213(OMTensor *y, const OMTensor *x);
+/* Batched fp32 onnx.MatMul, equal batch dims
+ * (src/Conversion/ONNXToKrnl/Math/MatMul.cpp:488-507). */
+void omcudaMatMulF32(OMTensor *y, const OMTensor *a, const OMTensor *b);
+/* The attention subgraph of the encoder configs as one call: q,k,v,y are f32
+ * [B,S,heads*dh]; scores = QK^T * scale, softmax over keys, times V. */
+void omcudaAttention(OMTensor *y, const OMTensor *q, const OMTensor *k,
+    const OMTensor *v, int64_t heads, double scale);
+
+/* ---------------------------------------------------------------------- */
+/* Device-pointer entry points                                              */
+/* ---------------------------------------------------------------------- */
+
+/* Bytes of scratch omcudaDevDynamicQuantizeLinear needs for n elements. */
+int64_t omcudaDevDqlScratchBytes(int64_t n);
+/* DynamicQuantizeLinear on device buffers.  scratch: device memory of at
+ * least omcudaDevDqlScratchBytes(n), zero-filled once before first use (the
+ * kernel leaves it zeroed).  params_out (device, 2 floats, may be NULL)
+ * receives {scale, zero point as float}. */
+int omcudaDevDynamicQuantizeLinear(const float *x, int64_t n, uint8_t *y,
+    float *y_scale, uint8_t *y_zp, void *scratch, void *stream);
+/* Quantize with given device scalars (scale f32; zp as 8-bit of y's type or
+ * NULL). */
+int omcudaDevQuantizeLinear(const float *x, int64_t n, void *y, int y_signed,
+    const float *scale, const void *zp, void *stream);
+
+/* A B operand prepared for the tensor-core GEMM: K-major copy Bt[N][Kp] and
+ * column sums of B as i32. */
+typedef struct {
+  void *bt;        /* device, N * kp bytes */
+  int32_t *colsum; /* device, N entries: sum over k of B[k][n] (widened) */
+  int64_t K, N, kp;
+  int b_signed;
+} omcudaPreparedB;
+int64_t omcudaDevPreparedBBytes(int64_t K, int64_t N, int64_t *kp);
+int omcudaDevPrepareB(const void *B, int b_signed, int64_t K, int64_t N,
+    omcudaPreparedB *out /* bt, colsum preallocated */, void *stream);
+
+typedef enum {
+  OMCUDA_EPI_I32 = 0,     /* MatMulInteger: i32 out */
+  OMCUDA_EPI_DEQUANT = 1, /* Cast f32, Mul scale(s), Add bias [, Gelu] */
+  OMCUDA_EPI_REQUANT = 2  /* QLinearMatMul: scale, round, +zp, wrap to 8 bit */
+} omcudaEpilogue;
+
+typedef struct {
+  int64_t M, N, K;
+  const void *A; /* device [M,K] row-major 8-bit */
+  int a_signed;
+  omcudaPreparedB B;
+  /* Zero points, device pointers to 8-bit values of the operand's type. */
+  const void *a_zp;
+  int64_t a_zp_len; /* 0, 1 or M */
+  const void *b_zp;
+  int64_t b_zp_len; /* 0, 1 or N */
+  /* Row sums of A (i32 [M]); required only when b_zp_len != 0. */
+  const int32_t *a_rowsum;
+  int epilogue; /* omcudaEpilogue */
+  void *Y;      /* i32 / f32 / 8-bit [M,N] */
+  /* DEQUANT: sa = device scalar (x_scale), sb = device w_scale (len 1 or N),
+   * form as in omcudaDynQuantLinear; bias device [N] or NULL; gelu flag.
+   * REQUANT: sb = device S[n] (len 1 or N) = (a_scale*b_scale[n])/y_scale,
+   * y_zp as int in the output type's domain, y_signed. */
+  const float *sa;
+  const float *sb;
+  int64_t sb_len;
+  int scale_form;
+  const float *bias;
+  int gelu;
+  int32_t y_zp;
+  int y_signed;
+  /* Optional (device, 2 floats {min, max} kept with atomics): running min/max
+   * of the f32 outputs, for a following DynamicQuantizeLinear. May be NULL. */
+  float *out_minmax;
+  /* 0 = choose; 1 = force the tcgen05 kernel; 2 = force the SIMT kernel. */
+  int kernel_choice;
+} omcudaGemmArgs;
+
+/* Device status word the GEMM writes on a bounded-wait timeout. */
+int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream);
+
+/* S[n] = (a_scale * b_scale[n]) / y_scale on device
+ * (QLinearMatMul.cpp:127). */
+int omcudaDevRequantScale(const float *a_scale, const float *b_scale,
+    int64_t len, const float *y_scale, float *S, void *stream);
+/* Row sums of an 8-bit [M,K] matrix as i32. */
+int omcudaDevRowSum(const void *A, int a_signed, int64_t M, int64_t K,
+    int32_t *rowsum, void *stream);
+
+int omcudaDevDequantizeLinear(const void *x, int dtype /*0 u8,1 i8,2 i32*/,
+    int64_t n, const float *scale, const void *zp, float *y, void *stream);
+int omcudaDevSoftmax(
+    const float *x, int64_t rows, int64_t cols, float *y, void *stream);
+int omcudaDevLayerNorm(const float *x, const float *residual, int64_t rows,
+    int64_t cols, const float *gamma, const float *beta, float eps, float *y,
+    float *out_minmax, void *stream);
+int omcudaDevGelu(const float *x, int64_t n, float *y, void *stream);
+int omcudaDevAdd(
+    const float *a, const float *b, int64_t n, float *y, void *stream);
+int omcudaDevTranspose0213(const float *x, int64_t B, int64_t S, int64_t H,
+    int64_t D, float *y, void *stream);
+int omcudaDevMatMulF32(const float *A, const float *B, int64_t batch,
+    int64_t M, int64_t N, int64_t K, float *C, void *stream);
+int omcudaDevAttention(const float *Q, const float *K, const float *V,
+    int64_t B, int64_t S, int64_t heads, int64_t dh, float scale, float *out,
+    void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,338 @@
+// DynamicQuantizeLinear / QuantizeLinear / DequantizeLinear kernels.
+//
+// Semantics follow onnx-mlir's lowering:
+//   min/max   src/Conversion/ONNXToKrnl/Math/Reduction.cpp:394-548 (minnum/maxnum,
+//             identities +inf/-inf)
+//   params    src/Conversion/ONNXToKrnl/Quantization/DynamicQuantizeLinear.cpp:43-84
+//   quantize  src/Conversion/ONNXToKrnl/Quantization/QuantizeLinear.cpp:122-145
+//   dequant   src/Conversion/ONNXToKrnl/Math/Elementwise.cpp:1438-1461
+//
+// Layout: tensors are flat, dense, row-major.  The reduction runs as a
+// single-pass grid reduction: every block leaves its partial min/max in
+// scratch, takes a ticket, and the block that draws the last ticket folds the
+// partials and derives scale and zero point, so no block ever waits on
+// another.  The quantize pass is a second launch that reads the two scalars
+// from device memory; for tensors that fit in L2 its read of x is served from
+// there.
+#include "../common.cuh"
+
+namespace omcuda {
+
+static constexpr int kDqlThreads = 256;
+static constexpr int kDqlMaxBlocks = 2048;
+
+struct DqlScratch {
+  unsigned int ticket;
+  unsigned int pad[15];
+  float part_min[kDqlMaxBlocks];
+  float part_max[kDqlMaxBlocks];
+  float params[4]; // scale, zero point as float
+};
+
+// fp32 arithmetic below uses the _rn intrinsics so that nothing is contracted
+// into an fma: the reference emits separate arith ops.
+__device__ __forceinline__ void dql_params_from_range(
+    float mn, float mx, float *scale, float *zp_f) {
+  float xmax = fmaxf(mx, 0.0f);
+  float xmin = fminf(mn, 0.0f);
+  float s = __fdiv_rn(__fsub_rn(xmax, xmin), 255.0f);
+  float inter = __fsub_rn(0.0f, __fdiv_rn(xmin, s));
+  float z = round_even(clipf(inter, 0.0f, 255.0f));
+  *scale = s;
+  *zp_f = z;
+}
+
+__global__ void __launch_bounds__(kDqlThreads)
+    dql_minmax_kernel(const float *__restrict__ x, int64_t n,
+        DqlScratch *__restrict__ scr, float *__restrict__ y_scale,
+        uint8_t *__restrict__ y_zp) {
+  float lo = INFINITY, hi = -INFINITY;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const bool aligned = ((uintptr_t)x & 15u) == 0;
+  if (aligned) {
+    const int64_t n4 = n >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    // Two independent loads in flight per thread per trip.
+    int64_t i = tid;
+    for (; i + nthreads < n4; i += 2 * nthreads) {
+      float4 a = __ldg(x4 + i);
+      float4 b = __ldg(x4 + i + nthreads);
+      lo = fminf(lo, fminf(fminf(a.x, a.y), fminf(a.z, a.w)));
+      hi = fmaxf(hi, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
+      lo = fminf(lo, fminf(fminf(b.x, b.y), fminf(b.z, b.w)));
+      hi = fmaxf(hi, fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+    }
+    for (; i < n4; i += nthreads) {
+      float4 a = __ldg(x4 + i);
+      lo = fminf(lo, fminf(fminf(a.x, a.y), fminf(a.z, a.w)));
+      hi = fmaxf(hi, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
+    }
+    for (int64_t j = (n4 << 2) + tid; j < n; j += nthreads) {
+      float v = x[j];
+      lo = fminf(lo, v);
+      hi = fmaxf(hi, v);
+    }
+  } else {
+    for (int64_t j = tid; j < n; j += nthreads) {
+      float v = x[j];
+      lo = fminf(lo, v);
+      hi = fmaxf(hi, v);
+    }
+  }
+  lo = warp_min(lo);
+  hi = warp_max(hi);
+  __shared__ float s_lo[kDqlThreads / 32], s_hi[kDqlThreads / 32];
+  __shared__ bool s_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    s_lo[warp] = lo;
+    s_hi[warp] = hi;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    lo = lane < kDqlThreads / 32 ? s_lo[lane] : INFINITY;
+    hi = lane < kDqlThreads / 32 ? s_hi[lane] : -INFINITY;
+    lo = warp_min(lo);
+    hi = warp_max(hi);
+    if (lane == 0) {
+      scr->part_min[blockIdx.x] = lo;
+      scr->part_max[blockIdx.x] = hi;
+      __threadfence();
+      unsigned int t = atomicAdd(&scr->ticket, 1u);
+      s_last = (t == gridDim.x - 1);
+    }
+  }
+  __syncthreads();
+  if (!s_last)
+    return;
+  // Last block: fold the partials (order does not matter for min/max).
+  __threadfence();
+  lo = INFINITY;
+  hi = -INFINITY;
+  for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) {
+    lo = fminf(lo, __ldcg(&scr->part_min[i]));
+    hi = fmaxf(hi, __ldcg(&scr->part_max[i]));
+  }
+  lo = warp_min(lo);
+  hi = warp_max(hi);
+  __syncthreads();
+  if (lane == 0) {
+    s_lo[warp] = lo;
+    s_hi[warp] = hi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kDqlThreads / 32; ++w) {
+      lo = fminf(lo, s_lo[w]);
+      hi = fmaxf(hi, s_hi[w]);
+    }
+    float s, z;
+    dql_params_from_range(lo, hi, &s, &z);
+    scr->params[0] = s;
+    scr->params[1] = z;
+    if (y_scale)
+      *y_scale = s;
+    if (y_zp)
+      *y_zp = (uint8_t)(unsigned int)z; // fptoui then trunc; z is in [0,255]
+    scr->ticket = 0; // leave the scratch ready for the next call
+  }
+}
+
+// Scale / zero point from a running range kept by a producer's epilogue
+// (ordered-uint encoding, see f32_to_ordered); re-arms the range.
+__global__ void dql_params_from_range_kernel(uint32_t *__restrict__ range,
+    float *__restrict__ params, float *__restrict__ y_scale,
+    uint8_t *__restrict__ y_zp) {
+  if (threadIdx.x != 0 || blockIdx.x != 0)
+    return;
+  float lo = ordered_to_f32(range[0]);
+  float hi = ordered_to_f32(range[1]);
+  float s, z;
+  dql_params_from_range(lo, hi, &s, &z);
+  params[0] = s;
+  params[1] = z;
+  if (y_scale)
+    *y_scale = s;
+  if (y_zp)
+    *y_zp = (uint8_t)(unsigned int)z;
+  range[0] = 0xffffffffu; // +inf side: any value lowers it
+  range[1] = 0u;          // -inf side: any value raises it
+}
+
+template <bool kSigned>
+__device__ __forceinline__ uint32_t quantize_one(
+    float x, float scale, float zp_f) {
+  float q = __fdiv_rn(x, scale);
+  float r = round_even(q);
+  float a = __fadd_rn(r, zp_f);
+  if (kSigned) {
+    float s = clipf(a, -128.0f, 127.0f);
+    return (uint32_t)(int32_t)s & 0xffu; // fptosi, then trunc to 8 bits
+  }
+  float s = clipf(a, 0.0f, 255.0f);
+  return (uint32_t)s; // fptoui; already within 8 bits
+}
+
+template <bool kSigned>
+__device__ __forceinline__ uint32_t quantize_four(
+    float4 v, float scale, float zp_f) {
+  return quantize_one<kSigned>(v.x, scale, zp_f) |
+         (quantize_one<kSigned>(v.y, scale, zp_f) << 8) |
+         (quantize_one<kSigned>(v.z, scale, zp_f) << 16) |
+         (quantize_one<kSigned>(v.w, scale, zp_f) << 24);
+}
+
+// params: {scale, zp as float}.  If zp8 is non-NULL the zero point is read
+// from it instead (QuantizeLinear with a given 8-bit zero point).
+template <bool kSigned>
+__global__ void __launch_bounds__(kDqlThreads)
+    quantize_kernel(const float *__restrict__ x, int64_t n,
+        uint8_t *__restrict__ y, const float *__restrict__ params,
+        const float *__restrict__ scale_ptr, const void *__restrict__ zp8,
+        int has_zp) {
+  float scale, zp_f;
+  if (params) {
+    scale = __ldg(params);
+    zp_f = __ldg(params + 1);
+  } else {
+    scale = __ldg(scale_ptr);
+    if (!has_zp)
+      zp_f = 0.0f;
+    else if (kSigned)
+      zp_f = (float)*reinterpret_cast<const int8_t *>(zp8);
+    else
+      zp_f = (float)*reinterpret_cast<const uint8_t *>(zp8);
+  }
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const bool aligned = (((uintptr_t)x & 15u) == 0) && (((uintptr_t)y & 3u) == 0);
+  if (aligned) {
+    const int64_t n4 = n >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    uint32_t *y4 = reinterpret_cast<uint32_t *>(y);
+    int64_t i = tid;
+    // Four float4 loads in flight per thread; each is a fully coalesced
+    // 512-byte warp access, each store a 128-byte one.
+    for (; i + 3 * nthreads < n4; i += 4 * nthreads) {
+      float4 a = __ldcs(x4 + i);
+      float4 b = __ldcs(x4 + i + nthreads);
+      float4 c = __ldcs(x4 + i + 2 * nthreads);
+      float4 d = __ldcs(x4 + i + 3 * nthreads);
+      y4[i] = quantize_four<kSigned>(a, scale, zp_f);
+      y4[i + nthreads] = quantize_four<kSigned>(b, scale, zp_f);
+      y4[i + 2 * nthreads] = quantize_four<kSigned>(c, scale, zp_f);
+      y4[i + 3 * nthreads] = quantize_four<kSigned>(d, scale, zp_f);
+    }
+    for (; i < n4; i += nthreads)
+      y4[i] = quantize_four<kSigned>(__ldcs(x4 + i), scale, zp_f);
+    for (int64_t j = (n4 << 2) + tid; j < n; j += nthreads)
+      y[j] = (uint8_t)quantize_one<kSigned>(x[j], scale, zp_f);
+  } else {
+    for (int64_t j = tid; j < n; j += nthreads)
+      y[j] = (uint8_t)quantize_one<kSigned>(x[j], scale, zp_f);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+    dequantize_kernel(const T *__restrict__ x, int64_t n,
+        const float *__restrict__ scale, const T *__restrict__ zp,
+        float *__restrict__ y) {
+  const float s = __ldg(scale);
+  const float zf = zp ? (float)*zp : 0.0f;
+  const bool has_zp = zp != nullptr;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    float xf = (float)x[i];
+    float d = has_zp ? __fsub_rn(xf, zf) : xf;
+    y[i] = __fmul_rn(d, s);
+  }
+}
+
+static int grid_for(int64_t work_items, int per_block) {
+  int64_t want = ceil_div(work_items, per_block);
+  int64_t cap = (int64_t)sm_count() * 8;
+  if (cap > kDqlMaxBlocks)
+    cap = kDqlMaxBlocks;
+  if (want < 1)
+    want = 1;
+  return (int)(want < cap ? want : cap);
+}
+
+int launch_quantize_with_params(const float *x, int64_t n, uint8_t *y,
+    const float *params, cudaStream_t st) {
+  int grid = grid_for(n, kDqlThreads * 16);
+  quantize_kernel<false><<<grid, kDqlThreads, 0, st>>>(
+      x, n, y, params, nullptr, nullptr, 1);
+  OMCUDA_CHECK_LAUNCH("quantize_kernel");
+  return OMCUDA_OK;
+}
+
+int launch_params_from_range(uint32_t *range, float *params, float *y_scale,
+    uint8_t *y_zp, cudaStream_t st) {
+  dql_params_from_range_kernel<<<1, 32, 0, st>>>(range, params, y_scale, y_zp);
+  OMCUDA_CHECK_LAUNCH("dql_params_from_range_kernel");
+  return OMCUDA_OK;
+}
+
+} // namespace omcuda
+
+using namespace omcuda;
+
+extern "C" int64_t omcudaDevDqlScratchBytes(int64_t) {
+  return (int64_t)sizeof(DqlScratch);
+}
+
+extern "C" int omcudaDevDynamicQuantizeLinear(const float *x, int64_t n,
+    uint8_t *y, float *y_scale, uint8_t *y_zp, void *scratch, void *stream) {
+  if (n < 0 || (n > 0 && (!x || !y)) || !scratch)
+    return fail(OMCUDA_EINVAL, "DynamicQuantizeLinear: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  DqlScratch *scr = (DqlScratch *)scratch;
+  int grid = grid_for(n, kDqlThreads * 16);
+  dql_minmax_kernel<<<grid, kDqlThreads, 0, st>>>(x, n, scr, y_scale, y_zp);
+  OMCUDA_CHECK_LAUNCH("dql_minmax_kernel");
+  if (n > 0)
+    return launch_quantize_with_params(x, n, y, scr->params, st);
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaDevQuantizeLinear(const float *x, int64_t n, void *y,
+    int y_signed, const float *scale, const void *zp, void *stream) {
+  if (n < 0 || (n > 0 && (!x || !y)) || !scale)
+    return fail(OMCUDA_EINVAL, "QuantizeLinear: bad argument");
+  if (n == 0)
+    return OMCUDA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  int grid = grid_for(n, kDqlThreads * 16);
+  if (y_signed)
+    quantize_kernel<true><<<grid, kDqlThreads, 0, st>>>(
+        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr);
+  else
+    quantize_kernel<false><<<grid, kDqlThreads, 0, st>>>(
+        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr);
+  OMCUDA_CHECK_LAUNCH("quantize_kernel");
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaDevDequantizeLinear(const void *x, int dtype, int64_t n,
+    const float *scale, const void *zp, float *y, void *stream) {
+  if (n < 0 || (n > 0 && (!x || !y)) || !scale || dtype < 0 || dtype > 2)
+    return fail(OMCUDA_EINVAL, "DequantizeLinear: bad argument");
+  if (n == 0)
+    return OMCUDA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  int grid = grid_for(n, 256 * 4);
+  if (dtype == 0)
+    dequantize_kernel<uint8_t><<<grid, 256, 0, st>>>(
+        (const uint8_t *)x, n, scale, (const uint8_t *)zp, y);
+  else if (dtype == 1)
+    dequantize_kernel<int8_t><<<grid, 256, 0, st>>>(
+        (const int8_t *)x, n, scale, (const int8_t *)zp, y);
+  else
+    dequantize_kernel<int32_t><<<grid, 256, 0, st>>>(
+        (const int32_t *)x, n, scale, (const int32_t *)zp, y);
+  OMCUDA_CHECK_LAUNCH("dequantize_kernel");
+  return OMCUDA_OK;
+}

@@ -1,0 +1,344 @@
+// Operand preparation for the int8 GEMMs and the SIMT (dp4a) GEMM.
+//
+// prepare_b: B arrives [K,N] row-major (the ONNX layout of a MatMulInteger /
+// QLinearMatMul weight).  Both GEMM kernels consume it K-major, so it is
+// copied once into Bt[N][kp] (kp = K rounded up to 16, zero padded) together
+// with its column sums, which carry the A zero point through the epilogue
+// (see gemm_epilogue.cuh).
+//
+// gemm_i8_warp_kernel: one warp per output column n and per group of MT rows;
+// the 32 lanes split K in 16-byte chunks (coalesced 512-byte reads of the Bt
+// row), accumulate with dp4a, and fold with shuffles.  It is the path for
+// small M, where the GEMM is bound by reading the weight once from HBM, and
+// for shapes the tensor-core kernel does not take (K not a multiple of 16,
+// unaligned bases).  Integer accumulation wraps in 32 bits in any order, so
+// its results are bit-identical to the tensor-core kernel's.
+#include "../runtime/internal.h"
+#include "gemm_epilogue.cuh"
+
+namespace omcuda {
+
+// ---- B preparation -----------------------------------------------------------
+
+__global__ void __launch_bounds__(256)
+    transpose_b_kernel(const uint8_t *__restrict__ B, int64_t K, int64_t N,
+        int64_t kp, uint8_t *__restrict__ Bt) {
+  // 64(k) x 64(n) byte tile through shared memory; reads are coalesced along
+  // n, writes along k.
+  __shared__ uint8_t tile[64][65];
+  const int64_t k0 = (int64_t)blockIdx.y * 64, n0 = (int64_t)blockIdx.x * 64;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6; // 64 x 4
+  for (int r = ty; r < 64; r += 4) {
+    int64_t k = k0 + r, n = n0 + tx;
+    tile[r][tx] = (k < K && n < N) ? B[k * N + n] : (uint8_t)0;
+  }
+  __syncthreads();
+  for (int r = ty; r < 64; r += 4) {
+    int64_t n = n0 + r, k = k0 + tx;
+    if (n < N && k < kp)
+      Bt[n * kp + k] = tile[tx][r];
+  }
+}
+
+template <bool kSigned>
+__global__ void __launch_bounds__(256)
+    colsum_kernel(const uint8_t *__restrict__ B, int64_t K, int64_t N,
+        int32_t *__restrict__ colsum) {
+  // blockDim = (64, 4): 64 columns per block, K split four ways.
+  __shared__ int32_t part[4][64];
+  const int64_t n = (int64_t)blockIdx.x * 64 + threadIdx.x;
+  int32_t s = 0;
+  if (n < N) {
+    for (int64_t k = threadIdx.y; k < K; k += 4) {
+      uint8_t b = B[k * N + n];
+      s += kSigned ? (int32_t)(int8_t)b : (int32_t)b;
+    }
+  }
+  part[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && n < N)
+    colsum[n] = part[0][threadIdx.x] + part[1][threadIdx.x] +
+                part[2][threadIdx.x] + part[3][threadIdx.x];
+}
+
+template <bool kSigned>
+__global__ void __launch_bounds__(256)
+    rowsum_kernel(const uint8_t *__restrict__ A, int64_t M, int64_t K,
+        int32_t *__restrict__ rowsum) {
+  // One warp per row.
+  const int64_t m = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (m >= M)
+    return;
+  const int lane = threadIdx.x & 31;
+  int32_t s = 0;
+  for (int64_t k = lane; k < K; k += 32) {
+    uint8_t a = A[m * K + k];
+    s += kSigned ? (int32_t)(int8_t)a : (int32_t)a;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0)
+    rowsum[m] = s;
+}
+
+__global__ void requant_scale_kernel(const float *__restrict__ a_scale,
+    const float *__restrict__ b_scale, int64_t len,
+    const float *__restrict__ y_scale, float *__restrict__ S) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < len)
+    S[i] = __fdiv_rn(__fmul_rn(*a_scale, b_scale[i]), *y_scale);
+}
+
+// ---- SIMT GEMM ----------------------------------------------------------------
+
+template <bool kASigned, bool kBSigned>
+__device__ __forceinline__ int32_t dp4a_mixed(uint32_t a, uint32_t b, int32_t c) {
+  int32_t d;
+  if (kASigned && kBSigned)
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  else if (kASigned && !kBSigned)
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  else if (!kASigned && kBSigned)
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  else
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+__device__ __forceinline__ uint4 load_a_chunk(const uint8_t *__restrict__ A,
+    int64_t m, int64_t M, int64_t K, int64_t k0, bool vec_ok) {
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (m >= M)
+    return v;
+  if (vec_ok && k0 + 16 <= K)
+    return __ldg(reinterpret_cast<const uint4 *>(A + m * K + k0));
+  uint32_t w[4] = {0, 0, 0, 0};
+  for (int j = 0; j < 16; ++j) {
+    int64_t k = k0 + j;
+    if (k < K)
+      w[j >> 2] |= (uint32_t)A[m * K + k] << (8 * (j & 3));
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <int MT, bool kASigned, bool kBSigned>
+__global__ void __launch_bounds__(256)
+    gemm_i8_warp_kernel(const uint8_t *__restrict__ A,
+        const uint8_t *__restrict__ Bt, int64_t kp, EpiParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t m0 = (int64_t)blockIdx.y * MT;
+  if (n >= p.N)
+    return; // whole warp leaves together
+  const bool vec_ok = ((p.K & 15) == 0) && (((uintptr_t)A & 15u) == 0);
+  int32_t acc[MT];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+    acc[i] = 0;
+  const uint4 *brow = reinterpret_cast<const uint4 *>(Bt + n * kp);
+  const int64_t chunks = kp >> 4;
+  for (int64_t c = lane; c < chunks; c += 32) {
+    uint4 b = __ldg(brow + c);
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      uint4 a = load_a_chunk(A, m0 + i, p.M, p.K, c << 4, vec_ok);
+      int32_t s = acc[i];
+      s = dp4a_mixed<kASigned, kBSigned>(a.x, b.x, s);
+      s = dp4a_mixed<kASigned, kBSigned>(a.y, b.y, s);
+      s = dp4a_mixed<kASigned, kBSigned>(a.z, b.z, s);
+      s = dp4a_mixed<kASigned, kBSigned>(a.w, b.w, s);
+      acc[i] = s;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MT; ++i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+  }
+  // Lane i finishes row m0+i (MT <= 32).
+  const EpiScalars sc = epi_scalars(p);
+  float lo = INFINITY, hi = -INFINITY;
+  int32_t mine = 0;
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+    if (lane == i)
+      mine = acc[i];
+  const int64_t m = m0 + lane;
+  if (lane < MT && m < p.M) {
+    EpiRow row = epi_row(p, m);
+    int32_t v = epi_int(p, row, mine, n);
+    if (p.kind == OMCUDA_EPI_I32) {
+      reinterpret_cast<int32_t *>(p.Y)[m * p.N + n] = v;
+    } else if (p.kind == OMCUDA_EPI_DEQUANT) {
+      float y = epi_dequant(p, sc, v, n);
+      reinterpret_cast<float *>(p.Y)[m * p.N + n] = y;
+      lo = fminf(lo, y);
+      hi = fmaxf(hi, y);
+    } else {
+      reinterpret_cast<uint8_t *>(p.Y)[m * p.N + n] =
+          (uint8_t)epi_requant(p, sc, v, n);
+    }
+  }
+  if (p.out_range && p.kind == OMCUDA_EPI_DEQUANT)
+    epi_range_commit(p.out_range, lo, hi);
+}
+
+EpiParams make_epi_params(const omcudaGemmArgs &a) {
+  EpiParams p;
+  p.M = a.M;
+  p.N = a.N;
+  p.K = a.K;
+  p.a_zp = a.a_zp;
+  p.a_zp_len = a.a_zp ? (int)(a.a_zp_len > 1 ? 2 : a.a_zp_len) : 0;
+  p.a_signed = a.a_signed;
+  p.b_zp = a.b_zp;
+  p.b_zp_len = a.b_zp ? (int)(a.b_zp_len > 1 ? 2 : a.b_zp_len) : 0;
+  p.b_signed = a.B.b_signed;
+  p.colsum = a.B.colsum;
+  p.rowsum = a.a_rowsum;
+  p.kind = a.epilogue;
+  p.Y = a.Y;
+  p.sa = a.sa;
+  p.sb = a.sb;
+  p.sb_len = a.sb_len > 1 ? 2 : (int)a.sb_len;
+  p.form = a.scale_form;
+  p.bias = a.bias;
+  p.gelu = a.gelu;
+  p.y_zp = a.y_zp;
+  p.out_range = reinterpret_cast<uint32_t *>(a.out_minmax);
+  return p;
+}
+
+template <int MT>
+static void launch_warp_gemm(const omcudaGemmArgs &a, cudaStream_t st) {
+  EpiParams p = make_epi_params(a);
+  dim3 grid((unsigned)ceil_div(a.N, 8), (unsigned)ceil_div(a.M, MT));
+  const uint8_t *A = (const uint8_t *)a.A;
+  const uint8_t *Bt = (const uint8_t *)a.B.bt;
+  int sel = (a.a_signed ? 2 : 0) | (a.B.b_signed ? 1 : 0);
+  switch (sel) {
+  case 0:
+    gemm_i8_warp_kernel<MT, false, false><<<grid, 256, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  case 1:
+    gemm_i8_warp_kernel<MT, false, true><<<grid, 256, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  case 2:
+    gemm_i8_warp_kernel<MT, true, false><<<grid, 256, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  default:
+    gemm_i8_warp_kernel<MT, true, true><<<grid, 256, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  }
+}
+
+int launch_gemm_simt(const omcudaGemmArgs &a, cudaStream_t st) {
+  if (a.M <= 1)
+    launch_warp_gemm<1>(a, st);
+  else if (a.M <= 4)
+    launch_warp_gemm<4>(a, st);
+  else if (a.M <= 8)
+    launch_warp_gemm<8>(a, st);
+  else
+    launch_warp_gemm<16>(a, st);
+  OMCUDA_CHECK_LAUNCH("gemm_i8_warp_kernel");
+  return OMCUDA_OK;
+}
+
+} // namespace omcuda
+
+using namespace omcuda;
+
+extern "C" int64_t omcudaDevPreparedBBytes(int64_t K, int64_t N, int64_t *kp) {
+  int64_t k16 = (K + 15) & ~int64_t(15);
+  if (kp)
+    *kp = k16;
+  return N * k16;
+}
+
+extern "C" int omcudaDevPrepareB(const void *B, int b_signed, int64_t K,
+    int64_t N, omcudaPreparedB *out, void *stream) {
+  if (!B || !out || !out->bt || !out->colsum || K <= 0 || N <= 0)
+    return fail(OMCUDA_EINVAL, "PrepareB: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t kp;
+  omcudaDevPreparedBBytes(K, N, &kp);
+  out->K = K;
+  out->N = N;
+  out->kp = kp;
+  out->b_signed = b_signed;
+  dim3 tgrid((unsigned)ceil_div(N, 64), (unsigned)ceil_div(kp, 64));
+  transpose_b_kernel<<<tgrid, 256, 0, st>>>(
+      (const uint8_t *)B, K, N, kp, (uint8_t *)out->bt);
+  OMCUDA_CHECK_LAUNCH("transpose_b_kernel");
+  dim3 cblock(64, 4);
+  unsigned cgrid = (unsigned)ceil_div(N, 64);
+  if (b_signed)
+    colsum_kernel<true><<<cgrid, cblock, 0, st>>>(
+        (const uint8_t *)B, K, N, out->colsum);
+  else
+    colsum_kernel<false><<<cgrid, cblock, 0, st>>>(
+        (const uint8_t *)B, K, N, out->colsum);
+  OMCUDA_CHECK_LAUNCH("colsum_kernel");
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaDevRowSum(const void *A, int a_signed, int64_t M,
+    int64_t K, int32_t *rowsum, void *stream) {
+  if (!A || !rowsum || M <= 0 || K <= 0)
+    return fail(OMCUDA_EINVAL, "RowSum: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  unsigned grid = (unsigned)ceil_div(M, 8);
+  if (a_signed)
+    rowsum_kernel<true><<<grid, 256, 0, st>>>((const uint8_t *)A, M, K, rowsum);
+  else
+    rowsum_kernel<false><<<grid, 256, 0, st>>>((const uint8_t *)A, M, K, rowsum);
+  OMCUDA_CHECK_LAUNCH("rowsum_kernel");
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaDevRequantScale(const float *a_scale, const float *b_scale,
+    int64_t len, const float *y_scale, float *S, void *stream) {
+  if (!a_scale || !b_scale || !y_scale || !S || len <= 0)
+    return fail(OMCUDA_EINVAL, "RequantScale: bad argument");
+  requant_scale_kernel<<<(unsigned)ceil_div(len, 256), 256, 0,
+      (cudaStream_t)stream>>>(a_scale, b_scale, len, y_scale, S);
+  OMCUDA_CHECK_LAUNCH("requant_scale_kernel");
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
+  if (!args)
+    return fail(OMCUDA_EINVAL, "GemmI8: null args");
+  const omcudaGemmArgs &a = *args;
+  if (a.M < 0 || a.N <= 0 || a.K <= 0 || !a.A || !a.B.bt || !a.Y)
+    return fail(OMCUDA_EINVAL, "GemmI8: bad shape or null operand");
+  if (a.M == 0)
+    return OMCUDA_OK;
+  if (a.B.K != a.K || a.B.N != a.N)
+    return fail(OMCUDA_EINVAL, "GemmI8: prepared B does not match K,N");
+  if (a.a_zp && a.a_zp_len != 1 && a.a_zp_len != a.M)
+    return fail(OMCUDA_EINVAL, "GemmI8: a_zp length must be 1 or M");
+  if (a.b_zp && a.b_zp_len != 1 && a.b_zp_len != a.N)
+    return fail(OMCUDA_EINVAL, "GemmI8: b_zp length must be 1 or N");
+  if (a.b_zp && a.b_zp_len != 0 && !a.a_rowsum)
+    return fail(OMCUDA_EINVAL, "GemmI8: b_zp needs the row sums of A");
+  if (a.a_zp && a.a_zp_len != 0 && !a.B.colsum)
+    return fail(OMCUDA_EINVAL, "GemmI8: a_zp needs the column sums of B");
+  if (a.epilogue == OMCUDA_EPI_DEQUANT && (!a.sa || !a.sb))
+    return fail(OMCUDA_EINVAL, "GemmI8: dequant epilogue needs both scales");
+  if (a.epilogue == OMCUDA_EPI_REQUANT && !a.sb)
+    return fail(OMCUDA_EINVAL, "GemmI8: requant epilogue needs S");
+  if (a.epilogue != OMCUDA_EPI_I32 && a.sb_len != 1 && a.sb_len != a.N)
+    return fail(OMCUDA_EINVAL, "GemmI8: scale length must be 1 or N");
+  cudaStream_t st = (cudaStream_t)stream;
+  bool tc_ok = gemm_tc_supported(a);
+  if (a.kernel_choice == 1 && !tc_ok)
+    return fail(OMCUDA_ENOTSUP,
+        "GemmI8: tensor-core kernel needs K %% 16 == 0 and 16-byte aligned A");
+  bool use_tc = (a.kernel_choice == 1) ||
+                (a.kernel_choice == 0 && tc_ok && a.M > 16);
+  return use_tc ? launch_gemm_tc(a, st) : launch_gemm_simt(a, st);
+}
