@@ -1,0 +1,437 @@
+"""Benchmark of the quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME]
+    python bench.py --impl reference ...      # CPU arm, same metric and config
+
+One JSON line on stdout (rank 0).  Workloads (synthetic, seeded, with the
+shapes and value distributions of the reference configurations):
+
+  mmi_4096    DynamicQuantizeLinear -> MatMulInteger -> Cast/Mul dequant,
+              X f32 [4096,4096] ~ N(0,1), W int8 [4096,4096] U{-127..127};
+              metric int8 TOPS (2*M*N*K per step).
+  qlinear_c2  QLinearMatMul A u8 [32,512,1024] x B i8 [1024,4096] -> u8,
+              per-column b_scale; metric int8 TOPS.
+
+A step is one pass of the workload's graph over one batch.  `value` is timed
+with inputs resident in HBM; `e2e` runs the same graph through the krnl.call
+entry points with pinned host buffers, host<->device copies inside the timed
+region.  With N > 1 every rank runs the workload on its own batch (weights
+replicated, no data-path collective): weak scaling.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "onnx-mlir_b200"))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+L2_FLUSH_BYTES = 256 << 20
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0,
+            "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while running."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                 "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                mhz.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(mhz)) if mhz else None,
+                "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# ---------------------------------------------------------------------------
+# GPU workloads
+# ---------------------------------------------------------------------------
+
+class GpuEnv:
+    def __init__(self, local_rank):
+        import torch
+        import omcuda
+        from omcuda import dev
+        self.torch, self.m, self.dev = torch, omcuda, dev
+        torch.cuda.set_device(local_rank)
+        os.environ.setdefault("OMCUDA_DEVICE", str(local_rank))
+        omcuda.init()
+        self.stream = torch.cuda.current_stream()
+        omcuda.lib().omcudaSetStream(ctypes.c_void_p(self.stream.cuda_stream))
+        self.device = torch.device("cuda", local_rank)
+        self.flush_buf = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8,
+                                     device=self.device)
+
+    def sptr(self):
+        return ctypes.c_void_p(self.stream.cuda_stream)
+
+    def flush_l2(self):
+        self.flush_buf.zero_()
+
+    def t(self, a):
+        return self.torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
+
+    def pinned(self, a):
+        t = self.torch.from_numpy(np.ascontiguousarray(a)).pin_memory()
+        return t
+
+
+class LinearWorkload:
+    """DQL -> int8 GEMM -> dequant (mmi_4096) or QLinearMatMul (qlinear_c2)."""
+
+    def __init__(self, env, name, seed):
+        self.env, self.name = env, name
+        torch, dev = env.torch, env.dev
+        rng = np.random.default_rng(seed)
+        if name == "mmi_4096":
+            self.M = self.N = self.K = 4096
+            self.kind = "dynquant"
+            self.Xh = rng.normal(size=(self.M, self.K)).astype(np.float32)
+            self.Wh = rng.integers(-127, 128, (self.K, self.N), dtype=np.int8)
+            self.w_scale = np.float32(0.02 * 4 / 127)
+        elif name == "qlinear_c2":
+            self.M, self.K, self.N = 32 * 512, 1024, 4096
+            self.kind = "qlinear"
+            self.Ah = rng.integers(0, 256, (32, 512, self.K), dtype=np.uint8)
+            self.Wh = rng.integers(-127, 128, (self.K, self.N), dtype=np.int8)
+            self.bs = rng.uniform(0.001, 0.01, self.N).astype(np.float32)
+        else:
+            raise ValueError(name)
+        M, N, K = self.M, self.N, self.K
+        self.ops = 2.0 * M * N * K
+        self.units = self.ops  # metric unit: int8 operations
+        # resident device state
+        W = env.t(self.Wh)
+        nbytes, kp = dev.prepared_b_bytes(K, N)
+        self.bt = torch.empty(nbytes, dtype=torch.uint8, device=env.device)
+        self.colsum = torch.empty(N, dtype=torch.int32, device=env.device)
+        self.pb = dev.prepare_b(W.data_ptr(), True, K, N, self.bt.data_ptr(),
+                                self.colsum.data_ptr(), env.sptr())
+        g = dev.GemmArgs()
+        g.M, g.N, g.K = M, N, K
+        g.B = self.pb
+        if self.kind == "dynquant":
+            self.X = env.t(self.Xh)
+            self.xq = torch.empty((M, K), dtype=torch.uint8, device=env.device)
+            self.xs = torch.empty(1, dtype=torch.float32, device=env.device)
+            self.xz = torch.empty(1, dtype=torch.uint8, device=env.device)
+            self.ws = env.t(np.array([self.w_scale], np.float32))
+            self.scr = torch.zeros(dev.dql_scratch_bytes(), dtype=torch.uint8,
+                                   device=env.device)
+            self.Y = torch.empty((M, N), dtype=torch.float32, device=env.device)
+            g.A, g.a_signed = self.xq.data_ptr(), 0
+            g.a_zp, g.a_zp_len = self.xz.data_ptr(), 1
+            g.epilogue = dev.EPI_DEQUANT
+            g.sa, g.sb, g.sb_len = self.xs.data_ptr(), self.ws.data_ptr(), 1
+            self.h2d = M * K * 4
+            self.d2h = M * N * 4
+            # algorithmic bytes of the GEMM launch: A + B + f32 Y
+            self.gemm_bytes = M * K + K * N + 4 * M * N
+        else:
+            self.A = env.t(self.Ah.reshape(M, K))
+            self.az = env.t(np.array([128], np.uint8))
+            self.bz = env.t(np.zeros(N, np.int8))
+            self.S = torch.empty(N, dtype=torch.float32, device=env.device)
+            a_s = env.t(np.array([0.02], np.float32))
+            y_s = env.t(np.array([0.5], np.float32))
+            dev.requant_scale(a_s.data_ptr(), env.t(self.bs).data_ptr(), N,
+                              y_s.data_ptr(), self.S.data_ptr(), env.sptr())
+            self.rs = torch.empty(M, dtype=torch.int32, device=env.device)
+            self.Y = torch.empty((M, N), dtype=torch.uint8, device=env.device)
+            g.A, g.a_signed = self.A.data_ptr(), 0
+            g.a_zp, g.a_zp_len = self.az.data_ptr(), 1
+            g.b_zp, g.b_zp_len = self.bz.data_ptr(), N
+            g.a_rowsum = self.rs.data_ptr()
+            g.epilogue = dev.EPI_REQUANT
+            g.sb, g.sb_len = self.S.data_ptr(), N
+            g.y_zp, g.y_signed = 128, 0
+            self.h2d = M * K
+            self.d2h = M * N
+            self.gemm_bytes = M * K + K * N + M * N + 8 * N
+        g.Y = self.Y.data_ptr()
+        self.g = g
+        self.launches_per_step = 3
+        env.torch.cuda.synchronize()
+        # e2e: pinned host tensors wrapped as OMTensors
+        m = env.m
+        if self.kind == "dynquant":
+            self.hX = env.pinned(self.Xh)
+            self.hY = torch.empty((M, N), dtype=torch.float32).pin_memory()
+            self.oX = m.Tensor.from_numpy(self.hX.numpy())
+            self.oY = m.Tensor.from_numpy(self.hY.numpy())
+            self.oW = m.Tensor.from_numpy(self.Wh)
+            self.oWs = m.Tensor.from_numpy(np.array(self.w_scale, np.float32))
+            m.lib().omcudaRegisterConstant(self.oW.handle)
+        else:
+            self.hA = env.pinned(self.Ah)
+            self.hY = torch.empty((32, 512, N), dtype=torch.uint8).pin_memory()
+            self.oA = m.Tensor.from_numpy(self.hA.numpy())
+            self.oY = m.Tensor.from_numpy(self.hY.numpy())
+            self.oW = m.Tensor.from_numpy(self.Wh)
+            self.oS = [m.Tensor.from_numpy(np.asarray(v)) for v in (
+                np.float32(0.02), np.uint8(128), self.bs, np.zeros(N, np.int8),
+                np.float32(0.5), np.uint8(128))]
+            m.lib().omcudaRegisterConstant(self.oW.handle)
+
+    def step(self, gemm_events=None):
+        env, dev = self.env, self.env.dev
+        if self.kind == "dynquant":
+            dev.dynamic_quantize_linear(self.X.data_ptr(), self.M * self.K,
+                                        self.xq.data_ptr(), self.xs.data_ptr(),
+                                        self.xz.data_ptr(), self.scr.data_ptr(),
+                                        env.sptr())
+        else:
+            dev.row_sum(self.A.data_ptr(), 0, self.M, self.K, self.rs.data_ptr(),
+                        env.sptr())
+        if gemm_events:
+            gemm_events[0].record(env.stream)
+        dev.gemm_i8(self.g, env.sptr())
+        if gemm_events:
+            gemm_events[1].record(env.stream)
+
+    def step_e2e(self):
+        L = self.env.m.lib()
+        if self.kind == "dynquant":
+            L.omcudaDynQuantLinear(self.oY.handle, self.oX.handle, self.oW.handle,
+                                   self.oWs.handle, None, None, 0)
+        else:
+            s = self.oS
+            L.omcudaQLinearMatMul(self.oY.handle, self.oA.handle, s[0].handle,
+                                  s[1].handle, self.oW.handle, s[2].handle,
+                                  s[3].handle, s[4].handle, s[5].handle)
+        self.env.m.check()
+
+    def config(self):
+        return {"workload": self.name, "M": self.M, "N": self.N, "K": self.K,
+                "l2": "flushed between timed iterations (256 MiB write)",
+                "graph": ("DynamicQuantizeLinear->MatMulInteger->Cast/Mul"
+                          if self.kind == "dynquant" else "QLinearMatMul")}
+
+    def cpu_sample(self, orc, threads, rows):
+        """Times the reference-shaped CPU lowering on `rows` rows; returns ops/s."""
+        rng = np.random.default_rng(0)
+        A = rng.integers(0, 256, (rows, self.K), dtype=np.uint8)
+        t0 = time.perf_counter()
+        orc.ref_shaped_matmul_integer(A, self.Wh, 128, threads)
+        dt = time.perf_counter() - t0
+        return 2.0 * rows * self.N * self.K / dt, dt
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    env = GpuEnv(local_rank)
+    wl = LinearWorkload(env, args.workload, seed=42 + rank)
+    peaks = load_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, per_step_events=True, extra=None):
+        for _ in range(warmup):
+            env.flush_l2()
+            fn()
+        barrier()
+        evs = [(torch.cuda.Event(enable_timing=True),
+                torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        for i in range(steps):
+            env.flush_l2()
+            evs[i][0].record(env.stream)
+            fn() if extra is None else fn(extra[i])
+            evs[i][1].record(env.stream)
+        barrier()
+        ms = sum(a.elapsed_time(b) for a, b in evs)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=env.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local_rank)
+    launches0 = env.m.launch_count()
+    gemm_evs = [(torch.cuda.Event(enable_timing=True),
+                 torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda ev=None: wl.step(ev), args.steps, args.warmup, extra=gemm_evs)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = (env.m.launch_count() - launches0) * args.steps // (
+        args.steps + args.warmup)
+    gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_evs) / args.steps
+    env.m.synchronize()
+
+    e2e_steps = max(1, min(args.steps, 10))
+    e2e_ms = timed(wl.step_e2e, e2e_steps, 1)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    value = wl.units * world * args.steps / (ms * 1e-3) / 1e12
+    e2e_value = wl.units * world * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    achieved = wl.ops / (gemm_ms * 1e-3) / 1e12
+    out = {
+        "metric": "MatMulInteger int8 TOPS", "value": value, "unit": "TOPS",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8*s8->s32",
+        "data": "synthetic", "config": wl.config(),
+        "e2e": {"value": e2e_value, "unit": "TOPS",
+                "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
+                "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {
+            "kernel": "gemm_i8_tc_kernel", "bound": "tensor",
+            "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
+            "frac": achieved / int8_peak,
+            "peak_source": "2 x %s bf16 cuBLAS burst (%s); int8 itself is not "
+                           "in MEASURED_PEAKS.json" % (peaks["bf16_tflops"],
+                                                       peaks["source"]),
+            "kernel_ms": gemm_ms,
+            "algorithmic_bytes": wl.gemm_bytes,
+            "traffic": None,
+        },
+    }
+    # CPU baseline on a bounded sample of the same GEMM (rank 0, N=1 only).
+    if world == 1 and not args.no_cpu_baseline:
+        import oracle_lib
+        orc = oracle_lib.Oracle(os.path.join(ROOT, "oracle", "_build",
+                                             "liboracle.so"))
+        threads = orc.L.orc_max_threads()
+        rows = 256
+        ops_s, dt = wl.cpu_sample(orc, threads, rows)
+        out["cpu_baseline"] = {
+            "value": ops_s / 1e12, "unit": "TOPS", "cores": threads,
+            "kind": "port",
+            "sample": "%d of %d rows of the same [K=%d,N=%d] GEMM, "
+                      "reference-shaped lowering (widen to i32, 4x8x8 tile), "
+                      "%.1f s" % (rows, wl.M, wl.K, wl.N, dt)}
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """CPU arm: the reference-shaped port of the same GEMM on all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle_lib
+    orc = oracle_lib.Oracle(os.path.join(ROOT, "oracle", "_build", "liboracle.so"))
+    threads = orc.L.orc_max_threads()
+    shapes = {"mmi_4096": (4096, 4096, 4096), "qlinear_c2": (16384, 4096, 1024)}
+    M, N, K = shapes[args.workload]
+    rng = np.random.default_rng(42)
+    W = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    rows = 128
+    A = rng.integers(0, 256, (rows, K), dtype=np.uint8)
+    for _ in range(args.warmup):
+        orc.ref_shaped_matmul_integer(A, W, 128, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.ref_shaped_matmul_integer(A, W, 128, threads)
+    dt = time.perf_counter() - t0
+    value = 2.0 * rows * N * K * args.steps / dt / 1e12
+    sample = ("%d of %d rows per step, reference-shaped lowering on %d threads"
+              % (rows, M, threads))
+    print(json.dumps({
+        "impl": "reference", "metric": "MatMulInteger int8 TOPS", "value": value,
+        "unit": "TOPS", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8*s8->s32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "M": M, "N": N, "K": K},
+        "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads,
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0}}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="omcuda", choices=["omcuda", "reference"])
+    ap.add_argument("--workload", default="mmi_4096")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "omcuda" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

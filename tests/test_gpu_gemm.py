@@ -1,0 +1,231 @@
+"""GPU parity: MatMulInteger, QLinearMatMul and the fused dynamic-quantized
+linear through the C ABI against the CPU oracle.  Bit-exact for int32 / uint8
+results; fp32 dequantized outputs are expected bit-exact too and are checked
+at the 1e-5 relative tolerance the path's contract states."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from gpu_util import DevGemm
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+KATS = json.load(open(os.path.join(HERE, "golden", "lit_kats.json")))["cases"]
+NP = {"ui8": np.uint8, "i8": np.int8, "i32": np.int32, "f32": np.float32}
+
+
+def arr(t):
+    return None if t is None else np.array(t["data"], dtype=NP[t["dtype"]]).reshape(t["shape"])
+
+
+def rand8(rng, shape, dt):
+    if dt == np.uint8:
+        return rng.integers(0, 256, shape, dtype=np.uint8)
+    return rng.integers(-128, 128, shape, dtype=np.int8)
+
+
+@pytest.mark.parametrize("kat", [k for k in KATS if k["op"] == "MatMulInteger"],
+                         ids=lambda k: k["name"])
+def test_lit_vectors(gpu, kat):
+    A, B = arr(kat["A"]), arr(kat["B"])
+    want = arr(kat["expected"])
+    broadcast_batch = B.ndim > 2 and (A.ndim != B.ndim or A.shape[:-2] != B.shape[:-2])
+    if broadcast_batch or A.ndim == 1 and B.ndim > 2:
+        with pytest.raises(gpu.OmcudaError) as ei:
+            gpu.matmul_integer(A, B, arr(kat["a_zero_point"]), arr(kat["b_zero_point"]))
+        assert ei.value.code in (gpu.ENOTSUP, gpu.EINVAL)
+        return
+    got = gpu.matmul_integer(A, B, arr(kat["a_zero_point"]), arr(kat["b_zero_point"]))
+    assert np.array_equal(got.reshape(want.shape), want)
+
+
+SHAPES = [(1, 16, 8), (1, 768, 768), (16, 4096, 512), (5, 7, 3), (127, 100, 33),
+          (128, 128, 256), (129, 144, 264), (300, 768, 100), (256, 1024, 640),
+          (513, 48, 1000), (128, 768, 768)]
+
+
+@pytest.mark.parametrize("choice", [1, 2], ids=["tcgen05", "simt"])
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_matmul_integer_kernels(gpu, orc, shape, choice):
+    M, K, N = shape
+    if choice == 1 and K % 16:
+        pytest.skip("tensor-core kernel needs K % 16 == 0; the SIMT kernel covers it")
+    rng = np.random.default_rng(M * 31 + K * 7 + N)
+    A, B = rand8(rng, (M, K), np.uint8), rand8(rng, (K, N), np.int8)
+    az = rng.integers(0, 256, 1, dtype=np.uint8)
+    dg = DevGemm(gpu)
+    want = orc.matmul_integer_2d(A, B, az, None)
+    got = dg.matmul_integer(A, B, az, None, choice)
+    assert np.array_equal(got, want), np.argwhere(got != want)[:8]
+
+
+@pytest.mark.parametrize("choice", [1, 2], ids=["tcgen05", "simt"])
+@pytest.mark.parametrize("adt,bdt", [(np.uint8, np.uint8), (np.int8, np.int8),
+                                     (np.int8, np.uint8), (np.uint8, np.int8)])
+def test_signedness_and_zero_point_forms(gpu, orc, adt, bdt, choice):
+    rng = np.random.default_rng(11)
+    M, K, N = 130, 160, 72
+    A, B = rand8(rng, (M, K), adt), rand8(rng, (K, N), bdt)
+    dg = DevGemm(gpu)
+    for az, bz in [(None, None), (rand8(rng, 1, adt), None), (None, rand8(rng, 1, bdt)),
+                   (rand8(rng, M, adt), rand8(rng, N, bdt)),
+                   (rand8(rng, 1, adt), rand8(rng, N, bdt))]:
+        want = orc.matmul_integer_2d(A, B, az, bz)
+        got = dg.matmul_integer(A, B, az, bz, choice)
+        assert np.array_equal(got, want)
+
+
+def test_matmul_integer_api_shapes(gpu, orc):
+    rng = np.random.default_rng(12)
+    # 3-D A times 2-D B (the encoder's broadcast-A form), host and device tensors
+    A, B = rand8(rng, (4, 33, 64), np.uint8), rand8(rng, (64, 48), np.int8)
+    az = np.array(7, np.uint8)
+    want = orc.matmul_integer(A, B, az, None)
+    assert np.array_equal(gpu.matmul_integer(A, B, az, None), want)
+    assert np.array_equal(gpu.matmul_integer(A, B, az, None, device=True).numpy(), want)
+    # equal batch dims on both sides
+    A, B = rand8(rng, (3, 17, 32), np.int8), rand8(rng, (3, 32, 20), np.int8)
+    assert np.array_equal(gpu.matmul_integer(A, B), orc.matmul_integer(A, B))
+    # vector operands
+    a, b = rand8(rng, 32, np.uint8), rand8(rng, (32, 9), np.int8)
+    assert np.array_equal(gpu.matmul_integer(a, b), orc.matmul_integer(a, b))
+    # per-row a zero point, per-column b zero point
+    A, B = rand8(rng, (21, 32), np.uint8), rand8(rng, (32, 9), np.uint8)
+    az, bz = rand8(rng, 21, np.uint8), rand8(rng, 9, np.uint8)
+    assert np.array_equal(gpu.matmul_integer(A, B, az, bz), orc.matmul_integer_2d(A, B, az, bz))
+
+
+def test_worst_case_magnitude_k14336(gpu, orc):
+    # |acc| <= 255 * 128 * 14336 < 2^31: no overflow at the largest K of the sweep
+    M, K, N = 64, 14336, 128
+    A = np.full((M, K), 255, np.uint8)
+    B = np.full((K, N), -128, np.int8)
+    B[:, ::2] = 127
+    dg = DevGemm(gpu)
+    want = orc.matmul_integer_2d(A, B, None, None)
+    assert np.array_equal(dg.matmul_integer(A, B, None, None, 1), want)
+    assert np.array_equal(dg.matmul_integer(A, B, None, None, 2), want)
+
+
+def test_full_size_4096_checksums(gpu):
+    # Size-independent property at the headline GEMM size: row and column sums
+    # of Y equal A @ rowsum(B) and colsum(A) @ B, computed exactly in int64.
+    rng = np.random.default_rng(13)
+    M = N = K = 4096
+    A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    az = np.array([113], np.uint8)
+    Y = DevGemm(gpu).matmul_integer(A, B, az, None, 1).astype(np.int64)
+    As = A.astype(np.int64) - 113
+    assert np.array_equal(Y.sum(1), As @ B.astype(np.int64).sum(1))
+    assert np.array_equal(Y.sum(0), As.sum(0) @ B.astype(np.int64))
+
+
+def qlinear_case(rng, lead, K, N, per_column=True):
+    A = rng.integers(0, 256, lead + (K,), dtype=np.uint8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    bs = rng.uniform(0.001, 0.01, N if per_column else 1).astype(np.float32)
+    bz = np.zeros(N if per_column else 1, np.int8)
+    return A, B, bs, bz
+
+
+def test_qlinear_matmul_small_with_wrap(gpu, orc):
+    rng = np.random.default_rng(14)
+    A, B, bs, bz = qlinear_case(rng, (3, 50), 256, 96)
+    bs = (bs * np.float32(16)).astype(np.float32)  # widen so results leave [0,255]
+    args = (A, np.float32(0.02), np.uint8(128), B, bs, bz, np.float32(0.5), np.uint8(128))
+    want = orc.qlinear_matmul(*args)
+    # make sure the case reaches outside [0,255] before the truncation
+    acc = (A.reshape(-1, 256).astype(np.int64) - 128) @ B.astype(np.int64)
+    pre = np.rint(acc * ((np.float32(0.02) * bs) / np.float32(0.5))[None, :]) + 128
+    assert (pre > 255).any() and (pre < 0).any()
+    got = gpu.qlinear_matmul(*args)
+    assert np.array_equal(got, want)
+    bz2 = rng.integers(-5, 6, 96, dtype=np.int8)
+    args2 = (A, np.float32(0.02), np.uint8(120), B, bs, bz2, np.float32(0.5), np.uint8(3))
+    assert np.array_equal(gpu.qlinear_matmul(*args2), orc.qlinear_matmul(*args2))
+
+
+def test_qlinear_matmul_int8_output_scalar_scale(gpu, orc):
+    rng = np.random.default_rng(15)
+    A = rng.integers(-128, 128, (40, 64), dtype=np.int8)
+    B = rng.integers(-128, 128, (64, 24), dtype=np.int8)
+    args = (A, np.float32(0.1), np.int8(-4), B, np.array([0.05], np.float32),
+            np.array([2], np.int8), np.float32(0.7), np.int8(-9))
+    assert np.array_equal(gpu.qlinear_matmul(*args), orc.qlinear_matmul(*args))
+
+
+def test_config2_qlinear_matmul_full_size(gpu, orc):
+    # A u8 [32,512,1024], B i8 [1024,4096], per-column b_scale: the whole
+    # output on the GPU, a seeded sample of 192 rows against the oracle, plus a
+    # byte histogram sanity check that the wrap region is populated.
+    rng = np.random.default_rng(42)
+    A, B, bs, bz = qlinear_case(rng, (32, 512), 1024, 4096)
+    args = (np.float32(0.02), np.uint8(128), B, bs, bz, np.float32(0.5), np.uint8(128))
+    got = gpu.qlinear_matmul(A, *args).reshape(-1, 4096)
+    rows = rng.choice(32 * 512, 192, replace=False)
+    want = orc.qlinear_matmul(A.reshape(-1, 1024)[rows], *args)
+    assert np.array_equal(got[rows], want)
+
+
+def test_config1_dyn_quant_linear(gpu, orc):
+    rng = np.random.default_rng(42)
+    X = rng.normal(size=(128, 768)).astype(np.float32)
+    W = rng.integers(-127, 128, (768, 768), dtype=np.int8)
+    bias = rng.normal(0, 0.02, 768).astype(np.float32)
+    w_scale = np.float32(0.0157)
+    ref = orc.dyn_quant_linear(X, W, w_scale, bias)
+    # step by step, as the unfused graph runs
+    xq, xs, xz = gpu.dynamic_quantize_linear(X)
+    assert np.array_equal(xq, ref["xq"]) and xs == ref["x_scale"] and xz == ref["x_zp"]
+    acc = gpu.matmul_integer(xq, W, xz, None)
+    assert np.array_equal(acc, ref["acc"])
+    # fused
+    Y = gpu.dyn_quant_linear(X, W, w_scale, None, bias, 0)
+    assert np.allclose(Y, ref["Y"], rtol=1e-5, atol=0)
+    assert Y.tobytes() == ref["Y"].tobytes()
+    Yd = gpu.dyn_quant_linear(X, W, w_scale, None, bias, 0, device=True).numpy()
+    assert Yd.tobytes() == ref["Y"].tobytes()
+
+
+def test_dyn_quant_linear_forms(gpu, orc):
+    rng = np.random.default_rng(16)
+    X = rng.normal(size=(2, 37, 96)).astype(np.float32)
+    W = rng.integers(-127, 128, (96, 40), dtype=np.int8)
+    ref = orc.dyn_quant_linear(X, W, 0.01, None)
+    # form 1: (acc * x_scale) * w_scale, two roundings on the tensor
+    want1 = orc.dequant_tail(ref["acc"], ref["x_scale"], np.float32(0.01), 1, None)
+    got1 = gpu.dyn_quant_linear(X, W, np.float32(0.01), None, None, 1)
+    assert got1.tobytes() == want1.tobytes()
+    # per-column weight scale
+    ws = rng.uniform(0.005, 0.02, 40).astype(np.float32)
+    s = (ref["x_scale"] * ws).astype(np.float32)
+    want = (ref["acc"].astype(np.float32) * s).astype(np.float32)
+    got = gpu.dyn_quant_linear(X, W, ws, None, None, 0)
+    assert got.tobytes() == want.tobytes()
+    # weight zero point
+    wz = np.array(3, np.int8)
+    acc = orc.matmul_integer(ref["xq"], W, ref["x_zp"], wz)
+    want = orc.dequant_tail(acc, ref["x_scale"] * np.float32(0.01), 0.0, 0, None)
+    got = gpu.dyn_quant_linear(X, W, np.float32(0.01), wz, None, 0)
+    assert got.tobytes() == want.tobytes()
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (16, 4096, 14336), (256, 14336, 4096),
+                                   (4096, 4096, 4096)])
+def test_config3_sweep_members(gpu, orc, M, K, N):
+    # DynamicQuantizeLinear over the whole X, then sampled rows of the GEMM and
+    # of the dequantized output against the oracle.
+    rng = np.random.default_rng(M + K + N)
+    X = rng.normal(size=(M, K)).astype(np.float32)
+    W = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    w_scale = np.float32(0.02 * 4 / 127)
+    xq, xs, xz = orc.dynamic_quantize_linear(X)
+    Y = gpu.dyn_quant_linear(X, W, w_scale, None, None, 0)
+    rows = rng.choice(M, min(M, 48), replace=False)
+    acc = orc.matmul_integer_2d(xq[rows], W, xz.reshape(1), None)
+    want = orc.dequant_tail(acc, xs * w_scale, 0.0, 0, None)
+    assert np.allclose(Y[rows], want, rtol=1e-5, atol=0)
+    assert Y[rows].tobytes() == want.tobytes()
