@@ -43,6 +43,8 @@ struct EpiParams {
   int gelu;
   int32_t y_zp;
   uint32_t *out_range; // ordered-uint {min,max} or nullptr
+  int vec_ok;    // per-column vectors are 16-byte aligned: 128-bit loads allowed
+  int line_store; // set by the tensor-core launcher: Y takes 16-byte line stores
 };
 
 // Host: flattens the public argument block (gemm_simt.cu).

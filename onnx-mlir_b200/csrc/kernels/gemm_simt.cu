@@ -208,6 +208,9 @@ EpiParams make_epi_params(const omcudaGemmArgs &a) {
   p.gelu = a.gelu;
   p.y_zp = a.y_zp;
   p.out_range = reinterpret_cast<uint32_t *>(a.out_minmax);
+  p.vec_ok = ((((uintptr_t)a.B.colsum | (uintptr_t)a.bias | (uintptr_t)a.sb) & 15u) == 0) &&
+             (a.N % 4 == 0);
+  p.line_store = 0;
   return p;
 }
 

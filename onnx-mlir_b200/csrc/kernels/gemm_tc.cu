@@ -19,8 +19,10 @@
 //              (M=128, N=BN, K=32 per instruction, four per stage) into one of
 //              two TMEM accumulator buffers and commits to mbarriers to free
 //              the smem stage / publish the accumulator.
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp owns the 32
-//              TMEM lanes its id modulo 4 selects), apply the epilogue, store.
+//   warps 2-9  epilogue: tcgen05.ld the accumulator (a warp may read the 32
+//              TMEM lanes its id modulo 4 selects; the two warps of a lane
+//              quadrant split the tile's columns), apply the epilogue, stage
+//              the results in shared memory and store whole 128-byte lines.
 // The two accumulator buffers let the epilogue of tile i overlap the MMAs of
 // tile i+1.
 //
@@ -39,7 +41,7 @@ namespace {
 constexpr int kBM = 128;       // rows of A per tile
 constexpr int kBK = 128;       // bytes (= int8 elements) of K per stage
 constexpr int kUmmaK = 32;     // K of one tcgen05.mma kind::i8
-constexpr int kThreads = 192;  // 6 warps
+constexpr int kThreads = 320;  // 10 warps: producer, MMA, 8 epilogue
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // ---- PTX wrappers -------------------------------------------------------------
@@ -190,26 +192,142 @@ struct TcConfig {
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN; // two accumulator buffers
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024; // + align slack
+  // Output staging: per epilogue warp one slab of 32 rows x 128 bytes.
+  static constexpr int kSlabBytes = 32 * 128;
+  static constexpr int kStagingBytes = 8 * kSlabBytes;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kStagingBytes + 1024; // + alignment slack
 };
 
-// ---- epilogue store helpers -----------------------------------------------------
+// ---- shared-memory staging helper ------------------------------------------------
 
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a,
+    uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a),
+               "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+
+// ---- epilogue arithmetic on one 32-column chunk ---------------------------------------
+
+// Loads 32 consecutive per-column values with 16-byte loads when allowed.
 template <typename T>
-__device__ __forceinline__ void store_chunk32(T *dst, const uint32_t (&w)[32],
-    int valid, bool vec_ok) {
-  // dst points at 32 consecutive 4-byte outputs of one row.
+__device__ __forceinline__ void load_cols32(
+    const T *base, int64_t n, int valid, bool vec_ok, T (&out)[32]) {
   if (vec_ok && valid == 32) {
-    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+    const uint4 *p4 = reinterpret_cast<const uint4 *>(base + n);
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      d4[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+    for (int j = 0; j < 8; ++j) {
+      uint4 q = __ldg(p4 + j);
+      out[4 * j + 0] = *reinterpret_cast<T *>(&q.x);
+      out[4 * j + 1] = *reinterpret_cast<T *>(&q.y);
+      out[4 * j + 2] = *reinterpret_cast<T *>(&q.z);
+      out[4 * j + 3] = *reinterpret_cast<T *>(&q.w);
+    }
   } else {
-    uint32_t *d = reinterpret_cast<uint32_t *>(dst);
 #pragma unroll
     for (int j = 0; j < 32; ++j)
-      if (j < valid)
-        d[j] = w[j];
+      out[j] = (j < valid) ? __ldg(base + n + j) : T(0);
+  }
+}
+
+// Turns 32 raw accumulators of one row into 32 output words (EPI_I32: the
+// corrected i32; EPI_DEQUANT: f32 bits; EPI_REQUANT: one byte per word).
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
+    const EpiScalars &sc, const EpiRow &row, int64_t nc, int valid,
+    uint32_t (&v)[32], float &lo, float &hi) {
+  if (p.b_zp_len != 0) {
+    // General zero-point form: per-element path.
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < valid) {
+        int32_t a = epi_int(p, row, (int32_t)v[j], nc + j);
+        if (EPI == OMCUDA_EPI_I32) {
+          v[j] = (uint32_t)a;
+        } else if (EPI == OMCUDA_EPI_DEQUANT) {
+          float y = epi_dequant(p, sc, a, nc + j);
+          lo = fminf(lo, y);
+          hi = fmaxf(hi, y);
+          v[j] = __float_as_uint(y);
+        } else {
+          v[j] = epi_requant(p, sc, a, nc + j);
+        }
+      }
+    }
+    return;
+  }
+  const bool vec = p.vec_ok != 0;
+  if (p.a_zp_len != 0) {
+    int32_t cs[32];
+    load_cols32(p.colsum, nc, valid, vec, cs);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      v[j] -= (uint32_t)row.az * (uint32_t)cs[j];
+  }
+  if (EPI == OMCUDA_EPI_I32)
+    return;
+  if (EPI == OMCUDA_EPI_DEQUANT) {
+    float f[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      f[j] = __int2float_rn((int32_t)v[j]);
+    if (p.sb_len == 1) {
+      if (p.form == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          f[j] = __fmul_rn(f[j], sc.s0);
+      } else {
+        const float sb = __ldg(p.sb);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          f[j] = __fmul_rn(__fmul_rn(f[j], sc.sa), sb);
+      }
+    } else {
+      float sb[32];
+      load_cols32(p.sb, nc, valid, vec, sb);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        f[j] = (p.form == 0) ? __fmul_rn(f[j], __fmul_rn(sc.sa, sb[j]))
+                             : __fmul_rn(__fmul_rn(f[j], sc.sa), sb[j]);
+    }
+    if (p.bias) {
+      float b[32];
+      load_cols32(p.bias, nc, valid, vec, b);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        f[j] = __fadd_rn(f[j], b[j]);
+    }
+    if (p.gelu) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        f[j] = gelu_erf(f[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (j < valid) {
+        lo = fminf(lo, f[j]);
+        hi = fmaxf(hi, f[j]);
+      }
+      v[j] = __float_as_uint(f[j]);
+    }
+    return;
+  }
+  // EPI_REQUANT
+  if (p.sb_len == 1) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float r = round_even(__fmul_rn(__int2float_rn((int32_t)v[j]), sc.s0));
+      v[j] = ((uint32_t)__float2int_rz(r) + (uint32_t)p.y_zp) & 0xffu;
+    }
+  } else {
+    float S[32];
+    load_cols32(p.sb, nc, valid, vec, S);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float r = round_even(__fmul_rn(__int2float_rn((int32_t)v[j]), S[j]));
+      v[j] = ((uint32_t)__float2int_rz(r) + (uint32_t)p.y_zp) & 0xffu;
+    }
   }
 }
 
@@ -217,13 +335,21 @@ __device__ __forceinline__ void store_chunk32(T *dst, const uint32_t (&w)[32],
 
 // ---- the kernel -------------------------------------------------------------------
 
-template <int BN>
+template <int BN, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a,
         const __grid_constant__ CUtensorMap map_b, EpiParams p, uint32_t idesc,
         int *status) {
   using Cfg = TcConfig<BN>;
   constexpr int kStages = Cfg::kStages;
+  constexpr int kOutBytes = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
+  // Each of the two epilogue warps that share a TMEM lane quadrant takes one
+  // half of the tile's columns and walks it in slabs of up to 128 bytes per row.
+  constexpr int kHalfCols = BN / 2;
+  constexpr int kSlabCols =
+      (128 / kOutBytes) < kHalfCols ? (128 / kOutBytes) : kHalfCols;
+  constexpr int kSlabsPerHalf = kHalfCols / kSlabCols;
+  static_assert(kHalfCols % 32 == 0 && kHalfCols % kSlabCols == 0, "tile shape");
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kStages];
@@ -239,6 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // 128-byte-swizzled tiles must start on a 1024-byte boundary.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t staging_base = smem_base + kStages * Cfg::kStageBytes;
 
   const int64_t tiles_m = ceil_div(p.M, kBM);
   const int64_t tiles_n = ceil_div(p.N, BN);
@@ -253,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_acc_full[b]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[b]), 4); // one arrive per epilogue warp
+      mbar_init(smem_u32(&bar_acc_empty[b]), 8); // one arrive per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -333,18 +460,42 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
-    const int quad = warp & 3; // TMEM lanes [32*quad, 32*quad+32)
+    // ---------------- epilogue (warps 2..9) ----------------
+    const int quad = warp & 3;       // TMEM lanes [32*quad, 32*quad+32)
+    const int ew = warp - 2;         // 0..7
+    const int c_lo = (ew >> 2) * kHalfCols; // this warp's half of the columns
     const EpiScalars sc = epi_scalars(p);
+    const bool use_slab = p.line_store != 0;
     const bool y4_ok = ((p.N & 3) == 0) && (((uintptr_t)p.Y & 15u) == 0);
     const bool y1_ok = ((p.N & 15) == 0) && (((uintptr_t)p.Y & 15u) == 0);
+    const uint32_t slab0 = staging_base + (uint32_t)ew * Cfg::kSlabBytes;
+    const uint32_t my_row = slab0 + (uint32_t)lane * 128u;
+    const uint32_t swz = (uint32_t)(lane & 7);
     bool ok = true;
     int64_t it = 0;
     for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       const int buf = (int)(it & 1);
       const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
-      const int64_t m = (t / tiles_n) * kBM + quad * 32 + lane;
-      const int64_t n0 = (t % tiles_n) * BN;
+      const int64_t m_warp = (t / tiles_n) * kBM + quad * 32;
+      const int64_t m = m_warp + lane;
+      const int64_t n0 = (t % tiles_n) * BN + c_lo;
+      // While the MMAs of this tile are still running, pull the per-column
+      // vectors this warp will need into L1.
+      {
+        const int line = lane & 7, which = lane >> 3;
+        const int64_t nl = n0 + 32 * line;
+        const void *src = nullptr;
+        if (32 * line < kHalfCols && nl < p.N) {
+          if (which == 0 && p.a_zp_len != 0)
+            src = p.colsum + nl;
+          else if (which == 1 && p.bias)
+            src = p.bias + nl;
+          else if (which == 2 && p.sb && p.sb_len != 1)
+            src = p.sb + nl;
+        }
+        if (src)
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
+      }
       if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase, abortp, t0)) {
         ok = false;
         break;
@@ -358,66 +509,108 @@ __global__ void __launch_bounds__(kThreads, 1)
         row = epi_row(p, m);
       float lo = INFINITY, hi = -INFINITY;
       const uint32_t taddr =
-          tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+          tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
+      if (use_slab) {
+        // Results pass through a swizzled shared-memory slab (32 rows x 128
+        // bytes per warp) so that the global stores are whole 128-byte lines:
+        // each thread writes its own row into the slab, then the warp reads
+        // the slab back eight 16-byte pieces per row and stores four full
+        // rows per instruction.
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t v[32];
-        __syncwarp(); // tcgen05.ld is warp-collective: enter it converged
-        tmem_ld32(taddr + (uint32_t)c, v);
-        tmem_ld_wait();
-        const int64_t nc = n0 + c;
-        int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
-        if (!row_ok || valid <= 0) {
-          // rows / columns past the edge of Y: nothing to store
-        } else if (p.kind == OMCUDA_EPI_I32) {
+        for (int g = 0; g < kSlabsPerHalf; ++g) {
+          const int64_t ng = n0 + (int64_t)g * kSlabCols;
+#pragma unroll 1
+          for (int cc = 0; cc < kSlabCols; cc += 32) {
+            uint32_t v[32];
+            __syncwarp(); // tcgen05.ld is warp-collective: enter it converged
+            tmem_ld32(taddr + (uint32_t)(g * kSlabCols + cc), v);
+            tmem_ld_wait();
+            const int64_t nc = ng + cc;
+            const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
+            if (row_ok && valid > 0)
+              epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
+            if (kOutBytes == 4) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < valid)
-              v[j] = (uint32_t)epi_int(p, row, (int32_t)v[j], nc + j);
-          store_chunk32(reinterpret_cast<int32_t *>(p.Y) + m * p.N + nc, v,
-              valid, y4_ok);
-        } else if (p.kind == OMCUDA_EPI_DEQUANT) {
+              for (int j = 0; j < 8; ++j)
+                st_shared_v4(my_row + (((uint32_t)j ^ swz) << 4), v[4 * j],
+                    v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+              uint32_t w[8];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (j < valid) {
-              int32_t a = epi_int(p, row, (int32_t)v[j], nc + j);
-              float y = epi_dequant(p, sc, a, nc + j);
-              lo = fminf(lo, y);
-              hi = fmaxf(hi, y);
-              v[j] = __float_as_uint(y);
+              for (int j = 0; j < 8; ++j)
+                w[j] = v[4 * j] | (v[4 * j + 1] << 8) | (v[4 * j + 2] << 16) |
+                       (v[4 * j + 3] << 24);
+              const uint32_t c16 = (uint32_t)(cc >> 4);
+              st_shared_v4(my_row + (((c16) ^ swz) << 4), w[0], w[1], w[2], w[3]);
+              st_shared_v4(my_row + (((c16 + 1) ^ swz) << 4), w[4], w[5], w[6],
+                  w[7]);
             }
           }
-          store_chunk32(reinterpret_cast<float *>(p.Y) + m * p.N + nc, v,
-              valid, y4_ok);
-        } else {
-          uint32_t packed[8];
+          __syncwarp();
+          // Lane l serves 16-byte piece (l & 7) of rows (l >> 3) + 4*i.
+          const uint32_t piece = (uint32_t)(lane & 7);
+          const int64_t col_b = ng * kOutBytes + piece * 16; // byte column in Y
+          const bool col_ok = (col_b < p.N * kOutBytes) &&
+                              ((int)piece * 16 < kSlabCols * kOutBytes);
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            packed[j] = 0;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (j < valid) {
-              int32_t a = epi_int(p, row, (int32_t)v[j], nc + j);
-              packed[j >> 2] |= epi_requant(p, sc, a, nc + j) << (8 * (j & 3));
-            }
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            uint32_t q0, q1, q2, q3;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(q0), "=r"(q1), "=r"(q2), "=r"(q3)
+                         : "r"(slab0 + (uint32_t)r * 128u +
+                               ((piece ^ (uint32_t)(r & 7)) << 4)));
+            const int64_t mr = m_warp + r;
+            if (col_ok && mr < p.M)
+              *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.Y) +
+                                         mr * p.N * kOutBytes + col_b) =
+                  make_uint4(q0, q1, q2, q3);
           }
-          uint8_t *dst = reinterpret_cast<uint8_t *>(p.Y) + m * p.N + nc;
-          if (y1_ok && valid == 32) {
-            uint4 *d4 = reinterpret_cast<uint4 *>(dst);
-            d4[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            d4[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          __syncwarp(); // slab is rewritten by the next group
+        }
+      } else {
+        // Fallback when the row pitch of Y is not a multiple of 16 bytes:
+        // direct stores, one row per thread.
+#pragma unroll 1
+        for (int c = 0; c < kHalfCols; c += 32) {
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(taddr + (uint32_t)c, v);
+          tmem_ld_wait();
+          const int64_t nc = n0 + c;
+          const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
+          if (!row_ok || valid <= 0)
+            continue;
+          epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
+          if (kOutBytes == 4) {
+            uint32_t *dst = reinterpret_cast<uint32_t *>(p.Y) + m * p.N + nc;
+            if (y4_ok && valid == 32) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                reinterpret_cast<uint4 *>(dst)[j] = make_uint4(
+                    v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < valid)
+                  dst[j] = v[j];
+            }
           } else {
-            for (int j = 0; j < valid; ++j)
-              dst[j] = (uint8_t)(packed[j >> 2] >> (8 * (j & 3)));
+            uint8_t *dst = reinterpret_cast<uint8_t *>(p.Y) + m * p.N + nc;
+            (void)y1_ok;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < valid)
+                dst[j] = (uint8_t)v[j];
           }
         }
       }
-      // The accumulator buffer may be overwritten once all four warps are done.
+      // The accumulator buffer may be overwritten once all eight warps are done.
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0)
         mbar_arrive(smem_u32(&bar_acc_empty[buf]));
-      if (p.out_range && p.kind == OMCUDA_EPI_DEQUANT)
+      if (p.out_range && EPI == OMCUDA_EPI_DEQUANT)
         epi_range_commit(p.out_range, lo, hi);
     }
   }
@@ -457,21 +650,23 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D map over a row-major [rows, cols_bytes] byte matrix whose row pitch is
-// pitch bytes; box = 128 bytes x box_rows, 128-byte swizzle, zero fill outside.
+// 2-D map over a row-major [rows, cols] matrix of esize-byte elements whose row
+// pitch is pitch bytes; box = 128 bytes x box_rows, 128-byte swizzle, zero
+// fill (loads) / clipping (stores) outside.
 int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t cols,
-    int64_t pitch, int box_rows) {
+    int64_t pitch, int box_rows, int esize = 1) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn)
     return fail(OMCUDA_ECUDA, "cuTensorMapEncodeTiled is not available");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)pitch};
-  cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)(kBK / esize), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base),
-      dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(map,
+      esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+      2, const_cast<void *>(base), dims, strides, box, estr,
+      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(OMCUDA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
   return OMCUDA_OK;
@@ -500,12 +695,12 @@ int *status_word() {
   return g_status_word;
 }
 
-template <int BN>
-int launch_bn(const omcudaGemmArgs &a, cudaStream_t st) {
+template <int BN, int EPI>
+int launch_bn_epi(const omcudaGemmArgs &a, cudaStream_t st) {
   using Cfg = TcConfig<BN>;
   static bool attr_set = false;
   if (!attr_set) {
-    OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc_kernel<BN>,
+    OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, EPI>,
         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set = true;
   }
@@ -516,17 +711,34 @@ int launch_bn(const omcudaGemmArgs &a, cudaStream_t st) {
   rc = make_map(&map_b, a.B.bt, a.N, a.B.kp, a.B.kp, BN);
   if (rc != OMCUDA_OK)
     return rc;
+  EpiParams p = make_epi_params(a);
+  // 16-byte stores of whole lines need an aligned base and row pitch.
+  const int esize = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
+  p.line_store = (((uintptr_t)a.Y & 15u) == 0) && ((a.N * esize) % 16 == 0);
   int *status = status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
-  EpiParams p = make_epi_params(a);
   int64_t tiles = ceil_div(a.M, kBM) * ceil_div(a.N, BN);
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   uint32_t idesc = make_idesc(a.a_signed, a.B.b_signed, BN);
-  gemm_i8_tc_kernel<BN><<<grid, kThreads, Cfg::kSmemBytes, st>>>(
+  gemm_i8_tc_kernel<BN, EPI><<<grid, kThreads, Cfg::kSmemBytes, st>>>(
       map_a, map_b, p, idesc, status);
   OMCUDA_CHECK_LAUNCH("gemm_i8_tc_kernel");
   return OMCUDA_OK;
+}
+
+template <int BN>
+int launch_bn(const omcudaGemmArgs &a, cudaStream_t st) {
+  switch (a.epilogue) {
+  case OMCUDA_EPI_I32:
+    return launch_bn_epi<BN, OMCUDA_EPI_I32>(a, st);
+  case OMCUDA_EPI_DEQUANT:
+    return launch_bn_epi<BN, OMCUDA_EPI_DEQUANT>(a, st);
+  case OMCUDA_EPI_REQUANT:
+    return launch_bn_epi<BN, OMCUDA_EPI_REQUANT>(a, st);
+  default:
+    return fail(OMCUDA_EINVAL, "GemmI8: unknown epilogue %d", a.epilogue);
+  }
 }
 
 } // namespace
