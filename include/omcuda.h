@@ -191,6 +191,26 @@ int64_t omcudaDevDqlScratchBytes(int64_t n);
  * receives {scale, zero point as float}. */
 int omcudaDevDynamicQuantizeLinear(const float *x, int64_t n, uint8_t *y,
     float *y_scale, uint8_t *y_zp, void *scratch, void *stream);
+/* DynamicQuantizeLinear for callers that cannot allocate device memory (a
+ * host whose HBM is entirely owned by its own arena, a loop that cannot
+ * afford the synchronisation cudaMalloc implies, a process whose allocation
+ * calls are refused).  Has no counterpart in the reference.  Same results as
+ * omcudaDevDynamicQuantizeLinear, but the reduction's scratch is a fixed
+ * 32 KiB array inside the library image (held on every GPU that loads the
+ * library until the process exits), and the call performs no cudaMalloc,
+ * cudaFree or other allocating call.  Limits and rules:
+ *  - n may not exceed OMCUDA_DQL_NOALLOC_MAX_ELEMS; larger inputs are rejected
+ *    with OMCUDA_EINVAL and nothing is launched.
+ *  - The first call on each device looks up the array's device address
+ *    (with that device current); make that first call before any stream
+ *    capture begins.
+ *  - All calls on a device share the one array, which keeps the previous
+ *    call's contents; the entry point re-zeroes the part that must start at
+ *    zero.  Two calls whose kernels overlap on the GPU (different streams,
+ *    no ordering between them) race on it: order them. */
+#define OMCUDA_DQL_NOALLOC_MAX_ELEMS ((int64_t)1 << 31)
+int omcudaDevDynamicQuantizeLinearNoAlloc(const float *x, int64_t n, uint8_t *y,
+    float *y_scale, uint8_t *y_zp, void *stream);
 /* Quantize with given device scalars (scale f32; zp as 8-bit of y's type or
  * NULL). */
 int omcudaDevQuantizeLinear(const float *x, int64_t n, void *y, int y_signed,

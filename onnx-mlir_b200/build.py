@@ -27,6 +27,7 @@ SOURCES = [
     "runtime/om_tensor.c",
     "runtime/context.cpp",
     "api/krnl_call_api.cpp",
+    "api/no_alloc.cu",
     "model/encoder.cpp",
     "kernels/dql.cu",
     "kernels/gemm_simt.cu",
