@@ -260,9 +260,9 @@ typedef struct {
   int gelu;
   int32_t y_zp;
   int y_signed;
-  /* Optional (device, 2 floats {min, max} kept with atomics): running min/max
-   * of the f32 outputs, for a following DynamicQuantizeLinear. May be NULL. */
-  float *out_minmax;
+  /* Optional running range (omcudaDevRangeInit) of the f32 outputs, for a
+   * following DynamicQuantizeLinear. May be NULL. */
+  void *out_minmax;
   /* 0 = choose; 1 = force the tcgen05 kernel; 2 = force the SIMT kernel. */
   int kernel_choice;
 } omcudaGemmArgs;
@@ -282,9 +282,10 @@ int omcudaDevDequantizeLinear(const void *x, int dtype /*0 u8,1 i8,2 i32*/,
     int64_t n, const float *scale, const void *zp, float *y, void *stream);
 int omcudaDevSoftmax(
     const float *x, int64_t rows, int64_t cols, float *y, void *stream);
+/* y = LayerNorm(x [+ residual]); out_minmax: optional running range of y. */
 int omcudaDevLayerNorm(const float *x, const float *residual, int64_t rows,
     int64_t cols, const float *gamma, const float *beta, float eps, float *y,
-    float *out_minmax, void *stream);
+    void *out_minmax, void *stream);
 int omcudaDevGelu(const float *x, int64_t n, float *y, void *stream);
 int omcudaDevAdd(
     const float *a, const float *b, int64_t n, float *y, void *stream);
@@ -295,6 +296,64 @@ int omcudaDevMatMulF32(const float *A, const float *B, int64_t batch,
 int omcudaDevAttention(const float *Q, const float *K, const float *V,
     int64_t B, int64_t S, int64_t heads, int64_t dh, float scale, float *out,
     void *stream);
+/* Same with explicit row pitches (in floats) of Q/K/V and of out, so that a
+ * fused [T,3H] QKV buffer can be read in place, and an optional running range
+ * of the outputs (see omcudaDevRangeInit). */
+int omcudaDevAttentionEx(const float *Q, const float *K, const float *V,
+    int64_t B, int64_t S, int64_t heads, int64_t dh, float scale, float *out,
+    int64_t ld_in, int64_t ld_out, void *out_range, void *stream);
+
+/* Running {min,max} ranges: 8 bytes each, kept by producer kernels (GEMM
+ * dequant epilogue, LayerNorm, attention) with integer atomics so that the
+ * DynamicQuantizeLinear that follows does not need its own reduction pass.
+ * omcudaDevRangeInit arms `count` ranges; omcudaDevQuantizeFromRange derives
+ * scale / zero point from one (exactly as DynamicQuantizeLinear.cpp:43-84
+ * does from the reduced min/max), re-arms it and quantizes x. */
+int omcudaDevRangeInit(void *ranges, int64_t count, void *stream);
+int omcudaDevQuantizeFromRange(const float *x, int64_t n, void *range,
+    uint8_t *y, float *params /* 2 floats */, float *y_scale, uint8_t *y_zp,
+    void *stream);
+
+/* ---------------------------------------------------------------------- */
+/* Encoder model harness                                                    */
+/* ---------------------------------------------------------------------- */
+
+/* Plays the part of the run_main_graph a compiled dynamic-quantized encoder
+ * model would export (src/Conversion/KrnlToLLVM/KrnlEntryPoint.cpp:236-338):
+ * unpack the input list, run the graph's ops in order through this library
+ * with every intermediate resident in HBM, pack the output list.  The graph is
+ * the post-LayerNorm BERT-shaped layer of the benchmark configurations:
+ *   q,k,v = DynQuantLinear(x);  ctx = softmax(q k^T / sqrt(dh)) v
+ *   h1 = LayerNorm(x + DynQuantLinear(ctx))
+ *   y  = LayerNorm(h1 + DynQuantLinear(Gelu(DynQuantLinear(h1))))
+ * where DynQuantLinear = DynamicQuantizeLinear -> MatMulInteger -> Cast ->
+ * Mul(x_scale * w_scale) -> Add(bias), weights int8 [in,out], per-tensor
+ * symmetric. */
+typedef struct omcudaEncoder omcudaEncoder;
+typedef struct {
+  int64_t layers, hidden, heads, ffn;
+  double epsilon;
+} omcudaEncoderConfig;
+typedef struct {
+  const OMTensor *wq, *wk, *wv, *wo, *w1, *w2; /* int8 [in,out] */
+  float w_scale[6];                            /* same order */
+  const OMTensor *bq, *bk, *bv, *bo, *b1, *b2; /* f32 biases */
+  const OMTensor *ln1_gamma, *ln1_beta, *ln2_gamma, *ln2_beta;
+} omcudaEncoderLayerWeights;
+
+omcudaEncoder *omcudaEncoderCreate(const omcudaEncoderConfig *cfg);
+/* Uploads one layer's constants (host or device tensors) and prepares the
+ * GEMM operands; the model-initialisation step of a compiled model. */
+int omcudaEncoderSetLayer(
+    omcudaEncoder *enc, int64_t layer, const omcudaEncoderLayerWeights *w);
+/* run_main_graph: one f32 input [batch, seq, hidden] (host or device), one f32
+ * output of the same shape and on the same side.  Returns NULL and sets errno
+ * on failure. */
+OMTensorList *omcudaEncoderRun(omcudaEncoder *enc, OMTensorList *inputs);
+/* Device-pointer form: x, y are device f32 [batch*seq, hidden]. */
+int omcudaEncoderRunDev(omcudaEncoder *enc, const float *x, int64_t batch,
+    int64_t seq, float *y, void *stream);
+void omcudaEncoderDestroy(omcudaEncoder *enc);
 
 #ifdef __cplusplus
 }

@@ -298,6 +298,17 @@ extern "C" int omcudaDevDynamicQuantizeLinear(const float *x, int64_t n,
   return OMCUDA_OK;
 }
 
+extern "C" int omcudaDevQuantizeFromRange(const float *x, int64_t n, void *range,
+    uint8_t *y, float *params, float *y_scale, uint8_t *y_zp, void *stream) {
+  if (n < 0 || (n > 0 && (!x || !y)) || !range || !params)
+    return fail(OMCUDA_EINVAL, "QuantizeFromRange: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = launch_params_from_range((uint32_t *)range, params, y_scale, y_zp, st);
+  if (rc != OMCUDA_OK || n == 0)
+    return rc;
+  return launch_quantize_with_params(x, n, y, params, st);
+}
+
 extern "C" int omcudaDevQuantizeLinear(const float *x, int64_t n, void *y,
     int y_signed, const float *scale, const void *zp, void *stream) {
   if (n < 0 || (n > 0 && (!x || !y)) || !scale)

@@ -220,12 +220,14 @@ template <int DH>
 __global__ void __launch_bounds__(kAttWarps * 32)
     attention_kernel(const float *__restrict__ Q, const float *__restrict__ Kt,
         const float *__restrict__ V, int64_t S, int64_t heads, float scale,
-        float *__restrict__ out) {
+        float *__restrict__ out, int64_t ld_in, int64_t ld_out,
+        uint32_t *__restrict__ out_range) {
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t bh = blockIdx.y;
   const int64_t b = bh / heads, h = bh % heads;
-  const int64_t H = heads * DH;
+  const int64_t H = ld_in;   // row pitch of Q, K, V in floats
+  const int64_t Ho = ld_out; // row pitch of out
   const int64_t q0 = ((int64_t)blockIdx.x * kAttWarps + warp) * kAttRows;
   // smem: Ktile[DH][33] | Vtile[32][DH] | q[warps][rows][DH] | p[warps][rows][S]
   float *ktile = smem;
@@ -311,6 +313,7 @@ __global__ void __launch_bounds__(kAttWarps * 32)
       }
     }
   }
+  float lo = INFINITY, hi = -INFINITY;
   for (int r = 0; r < kAttRows; ++r) {
     int64_t qi = q0 + r;
     if (qi >= S)
@@ -318,9 +321,30 @@ __global__ void __launch_bounds__(kAttWarps * 32)
 #pragma unroll
     for (int i = 0; i < kDPer; ++i) {
       int d = lane + 32 * i;
-      if (d < DH)
-        out[(b * S + qi) * H + h * DH + d] = o[r][i];
+      if (d < DH) {
+        out[(b * S + qi) * Ho + h * DH + d] = o[r][i];
+        lo = fminf(lo, o[r][i]);
+        hi = fmaxf(hi, o[r][i]);
+      }
     }
+  }
+  if (out_range) {
+    lo = warp_min(lo);
+    hi = warp_max(hi);
+    if (lane == 0 && lo <= hi) {
+      atomicMin(out_range, f32_to_ordered(lo));
+      atomicMax(out_range + 1, f32_to_ordered(hi));
+    }
+  }
+}
+
+// Arms running {min,max} ranges (ordered-uint encoding): min side all ones,
+// max side zero, so that the first value folded in replaces both.
+__global__ void range_init_kernel(uint32_t *ranges, int count) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) {
+    ranges[2 * i] = 0xffffffffu;
+    ranges[2 * i + 1] = 0u;
   }
 }
 
@@ -350,7 +374,7 @@ extern "C" int omcudaDevSoftmax(
 
 extern "C" int omcudaDevLayerNorm(const float *x, const float *residual,
     int64_t rows, int64_t cols, const float *gamma, const float *beta,
-    float eps, float *y, float *out_minmax, void *stream) {
+    float eps, float *y, void *out_minmax, void *stream) {
   if (rows < 0 || cols <= 0 || (rows > 0 && (!x || !y)) || !gamma)
     return fail(OMCUDA_EINVAL, "LayerNormalization: bad argument");
   if (rows == 0)
@@ -410,10 +434,28 @@ extern "C" int omcudaDevMatMulF32(const float *A, const float *B, int64_t batch,
   return OMCUDA_OK;
 }
 
+extern "C" int omcudaDevRangeInit(void *ranges, int64_t count, void *stream) {
+  if (!ranges || count <= 0)
+    return fail(OMCUDA_EINVAL, "RangeInit: bad argument");
+  range_init_kernel<<<(unsigned)ceil_div(count, 128), 128, 0,
+      (cudaStream_t)stream>>>((uint32_t *)ranges, (int)count);
+  OMCUDA_CHECK_LAUNCH("range_init_kernel");
+  return OMCUDA_OK;
+}
+
 extern "C" int omcudaDevAttention(const float *Q, const float *K, const float *V,
     int64_t B, int64_t S, int64_t heads, int64_t dh, float scale, float *out,
     void *stream) {
-  if (B < 0 || S <= 0 || heads <= 0 || !Q || !K || !V || !out)
+  return omcudaDevAttentionEx(Q, K, V, B, S, heads, dh, scale, out, heads * dh,
+      heads * dh, nullptr, stream);
+}
+
+extern "C" int omcudaDevAttentionEx(const float *Q, const float *K,
+    const float *V, int64_t B, int64_t S, int64_t heads, int64_t dh,
+    float scale, float *out, int64_t ld_in, int64_t ld_out, void *out_range,
+    void *stream) {
+  if (B < 0 || S <= 0 || heads <= 0 || !Q || !K || !V || !out ||
+      ld_in < heads * dh || ld_out < heads * dh)
     return fail(OMCUDA_EINVAL, "Attention: bad argument");
   if (B == 0)
     return OMCUDA_OK;
@@ -432,8 +474,8 @@ extern "C" int omcudaDevAttention(const float *Q, const float *K, const float *V
   do {                                                                         \
     OMCUDA_CHECK(cudaFuncSetAttribute(attention_kernel<DH>,                    \
         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));              \
-    attention_kernel<DH><<<grid, kAttWarps * 32, smem, st>>>(                  \
-        Q, K, V, S, heads, scale, out);                                        \
+    attention_kernel<DH><<<grid, kAttWarps * 32, smem, st>>>(Q, K, V, S,       \
+        heads, scale, out, ld_in, ld_out, (uint32_t *)out_range);              \
   } while (0)
   if (dh == 64)
     OMCUDA_LAUNCH_ATT(64);

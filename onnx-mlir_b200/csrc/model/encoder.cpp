@@ -1,0 +1,480 @@
+// Encoder model harness: the role of a compiled model's run_main_graph for the
+// dynamic-quantized BERT-shaped encoder configurations.
+//
+// The generated entry point of onnx-mlir unpacks an OMTensorList, calls the
+// graph function and packs the results
+// (src/Conversion/KrnlToLLVM/KrnlEntryPoint.cpp:236-338).  This harness does
+// the same around a fixed schedule of omcudaDev* launches, one per op of the
+// graph, with every intermediate kept in HBM:
+//
+//   per layer (T = batch*seq tokens, H hidden, F ffn):
+//     xq        = quantize(x)                 range of x from its producer
+//     qkv[T,3H] = GEMM(xq, [Wq|Wk|Wv]) dequant + bias   (one launch: the three
+//                 linears share xq; columns are independent, so the result
+//                 is bit-identical to three launches)
+//     ctx[T,H]  = attention(qkv)              keeps the range of ctx
+//     a[T,H]    = GEMM(quantize(ctx), Wo) dequant + bias
+//     h1        = LayerNorm(x + a)            keeps the range of h1
+//     f[T,F]    = GEMM(quantize(h1), W1) dequant + bias + Gelu, keeps range
+//     o[T,H]    = GEMM(quantize(f), W2) dequant + bias
+//     y         = LayerNorm(h1 + o)           keeps the range of y (next x)
+//
+// DynamicQuantizeLinear needs the min/max of its whole input before it can
+// write a byte.  Instead of a separate reduction pass, each producer folds the
+// min/max of what it writes into an 8-byte running range with integer
+// atomics; min/max is order-independent, so scale and zero point come out
+// bit-identical to the reference's reduction
+// (src/Conversion/ONNXToKrnl/Quantization/DynamicQuantizeLinear.cpp:29-84).
+// Only the very first activation needs the standalone min/max kernel.
+#include <cuda_runtime.h>
+
+#include <cerrno>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "../common.cuh"
+#include "../runtime/internal.h"
+
+using namespace omcuda;
+
+namespace {
+
+struct DevBuf {
+  void *p = nullptr;
+  size_t bytes = 0;
+  void ensure(size_t n) {
+    if (n <= bytes)
+      return;
+    if (p)
+      pool_free(p);
+    p = pool_alloc(n);
+    bytes = p ? n : 0;
+  }
+  void release() {
+    if (p)
+      pool_free(p);
+    p = nullptr;
+    bytes = 0;
+  }
+};
+
+struct LayerState {
+  bool set = false;
+  omcudaPreparedB wqkv{}, wo{}, w1{}, w2{};
+  DevBuf wqkv_bt, wqkv_cs, wo_bt, wo_cs, w1_bt, w1_cs, w2_bt, w2_cs;
+  DevBuf qkv_scale; // f32 [3H]: w_scale of q | k | v per column
+  DevBuf scal;      // f32 [3]: w_scale of wo, w1, w2
+  DevBuf bqkv, bo, b1, b2, ln1g, ln1b, ln2g, ln2b;
+  bool has_ln1b = false, has_ln2b = false;
+};
+
+} // namespace
+
+struct omcudaEncoder {
+  omcudaEncoderConfig cfg{};
+  std::vector<LayerState> layers;
+  // workspace, sized for the largest (batch*seq) seen
+  int64_t tokens = 0;
+  DevBuf xq, qkv, ctx, a, h1, f, o, ybuf[2];
+  DevBuf ranges;  // 4 running ranges per layer + 1
+  DevBuf params;  // 16 bytes per quantize site
+  DevBuf dql_scratch;
+};
+
+namespace {
+
+int upload(DevBuf &dst, const OMTensor *t, size_t bytes, cudaStream_t st) {
+  dst.ensure(bytes);
+  if (!dst.p)
+    return OMCUDA_ENOMEM;
+  return check_cuda(cudaMemcpyAsync(dst.p, omTensorGetDataPtr(t), bytes,
+                        cudaMemcpyDefault, st),
+      "encoder: upload");
+}
+
+bool is_i8_matrix(const OMTensor *t, int64_t k, int64_t n) {
+  return t && omTensorGetDataType(t) == ONNX_TYPE_INT8 &&
+         omTensorGetRank(t) == 2 && omTensorGetShape(t)[0] == k &&
+         omTensorGetShape(t)[1] == n;
+}
+
+bool is_f32_vec(const OMTensor *t, int64_t n) {
+  return t && omTensorGetDataType(t) == ONNX_TYPE_FLOAT &&
+         omTensorGetNumElems(t) == n;
+}
+
+int prepare(const void *w_dev, int64_t K, int64_t N, DevBuf &bt, DevBuf &cs,
+    omcudaPreparedB *pb, cudaStream_t st) {
+  int64_t kp;
+  int64_t bytes = omcudaDevPreparedBBytes(K, N, &kp);
+  bt.ensure((size_t)bytes);
+  cs.ensure((size_t)N * sizeof(int32_t));
+  if (!bt.p || !cs.p)
+    return OMCUDA_ENOMEM;
+  memset(pb, 0, sizeof(*pb));
+  pb->bt = bt.p;
+  pb->colsum = (int32_t *)cs.p;
+  return omcudaDevPrepareB(w_dev, 1, K, N, pb, st);
+}
+
+// out[K][3H] = [a | b | c], each [K][H]
+__global__ void concat_cols_kernel(const int8_t *a, const int8_t *b,
+    const int8_t *c, int64_t K, int64_t H, int8_t *out) {
+  int64_t total = K * 3 * H;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t k = i / (3 * H), n = i % (3 * H);
+    const int8_t *src = n < H ? a : (n < 2 * H ? b : c);
+    out[i] = src[k * H + (n % H)];
+  }
+}
+
+__global__ void fill_kernel(float *dst, int64_t n, float v) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n)
+    dst[i] = v;
+}
+
+int gemm(const uint8_t *A, const uint8_t *a_zp, const float *a_scale,
+    const omcudaPreparedB &B, int64_t M, const float *w_scale, int64_t ws_len,
+    const float *bias, int gelu, float *Y, void *out_range, cudaStream_t st) {
+  omcudaGemmArgs g;
+  memset(&g, 0, sizeof(g));
+  g.M = M;
+  g.N = B.N;
+  g.K = B.K;
+  g.A = A;
+  g.a_signed = 0;
+  g.B = B;
+  g.a_zp = a_zp;
+  g.a_zp_len = 1;
+  g.epilogue = OMCUDA_EPI_DEQUANT;
+  g.Y = Y;
+  g.sa = a_scale;
+  g.sb = w_scale;
+  g.sb_len = ws_len;
+  g.scale_form = 0;
+  g.bias = bias;
+  g.gelu = gelu;
+  g.out_minmax = out_range;
+  return omcudaDevGemmI8(&g, st);
+}
+
+int ensure_workspace(omcudaEncoder *e, int64_t T) {
+  const int64_t H = e->cfg.hidden, F = e->cfg.ffn;
+  const int64_t maxk = H > F ? H : F;
+  if (T > e->tokens) {
+    e->xq.ensure((size_t)(T * maxk));
+    e->qkv.ensure((size_t)(T * 3 * H) * 4);
+    e->ctx.ensure((size_t)(T * H) * 4);
+    e->a.ensure((size_t)(T * H) * 4);
+    e->h1.ensure((size_t)(T * H) * 4);
+    e->f.ensure((size_t)(T * F) * 4);
+    e->o.ensure((size_t)(T * H) * 4);
+    e->ybuf[0].ensure((size_t)(T * H) * 4);
+    e->ybuf[1].ensure((size_t)(T * H) * 4);
+    if (!e->xq.p || !e->qkv.p || !e->ctx.p || !e->a.p || !e->h1.p || !e->f.p ||
+        !e->o.p || !e->ybuf[0].p || !e->ybuf[1].p)
+      return OMCUDA_ENOMEM;
+    e->tokens = T;
+  }
+  if (!e->ranges.p) {
+    size_t nr = (size_t)(4 * e->cfg.layers + 1);
+    e->ranges.ensure(nr * 8);
+    e->params.ensure(nr * 16);
+    e->dql_scratch.ensure((size_t)omcudaDevDqlScratchBytes(0));
+    if (!e->ranges.p || !e->params.p || !e->dql_scratch.p)
+      return OMCUDA_ENOMEM;
+    int rc = check_cuda(cudaMemset(e->dql_scratch.p, 0, e->dql_scratch.bytes),
+        "encoder: scratch");
+    if (rc != OMCUDA_OK)
+      return rc;
+  }
+  return OMCUDA_OK;
+}
+
+} // namespace
+
+extern "C" omcudaEncoder *omcudaEncoderCreate(const omcudaEncoderConfig *cfg) {
+  if (ensure_init() != OMCUDA_OK)
+    return nullptr;
+  if (!cfg || cfg->layers <= 0 || cfg->hidden <= 0 || cfg->heads <= 0 ||
+      cfg->ffn <= 0 || cfg->hidden % cfg->heads != 0) {
+    fail(OMCUDA_EINVAL, "EncoderCreate: bad configuration");
+    return nullptr;
+  }
+  int64_t dh = cfg->hidden / cfg->heads;
+  if (dh != 32 && dh != 64 && dh != 128) {
+    fail(OMCUDA_ENOTSUP, "EncoderCreate: head size must be 32, 64 or 128");
+    return nullptr;
+  }
+  omcudaEncoder *e = new omcudaEncoder();
+  e->cfg = *cfg;
+  e->layers.resize((size_t)cfg->layers);
+  return e;
+}
+
+extern "C" int omcudaEncoderSetLayer(
+    omcudaEncoder *e, int64_t layer, const omcudaEncoderLayerWeights *w) {
+  if (!e || !w || layer < 0 || layer >= e->cfg.layers)
+    return fail(OMCUDA_EINVAL, "EncoderSetLayer: bad argument");
+  const int64_t H = e->cfg.hidden, F = e->cfg.ffn;
+  if (!is_i8_matrix(w->wq, H, H) || !is_i8_matrix(w->wk, H, H) ||
+      !is_i8_matrix(w->wv, H, H) || !is_i8_matrix(w->wo, H, H) ||
+      !is_i8_matrix(w->w1, H, F) || !is_i8_matrix(w->w2, F, H))
+    return fail(OMCUDA_EINVAL, "EncoderSetLayer: weights must be int8 [in,out]");
+  if (!is_f32_vec(w->bq, H) || !is_f32_vec(w->bk, H) || !is_f32_vec(w->bv, H) ||
+      !is_f32_vec(w->bo, H) || !is_f32_vec(w->b1, F) || !is_f32_vec(w->b2, H) ||
+      !is_f32_vec(w->ln1_gamma, H) || !is_f32_vec(w->ln2_gamma, H) ||
+      (w->ln1_beta && !is_f32_vec(w->ln1_beta, H)) ||
+      (w->ln2_beta && !is_f32_vec(w->ln2_beta, H)))
+    return fail(OMCUDA_EINVAL, "EncoderSetLayer: bias / LayerNorm shapes");
+  cudaStream_t st = current_stream();
+  LayerState &L = e->layers[(size_t)layer];
+  int rc = OMCUDA_OK;
+  // [Wq | Wk | Wv] as one [H, 3H] operand
+  DevBuf tq, tk, tv, cat, t1, t2, t3;
+  if ((rc = upload(tq, w->wq, (size_t)(H * H), st)) != OMCUDA_OK ||
+      (rc = upload(tk, w->wk, (size_t)(H * H), st)) != OMCUDA_OK ||
+      (rc = upload(tv, w->wv, (size_t)(H * H), st)) != OMCUDA_OK)
+    return rc;
+  cat.ensure((size_t)(3 * H * H));
+  if (!cat.p)
+    return OMCUDA_ENOMEM;
+  concat_cols_kernel<<<sm_count() * 4, 256, 0, st>>>((const int8_t *)tq.p,
+      (const int8_t *)tk.p, (const int8_t *)tv.p, H, H, (int8_t *)cat.p);
+  count_launch();
+  if ((rc = check_cuda(cudaGetLastError(), "concat_cols_kernel")) != OMCUDA_OK)
+    return rc;
+  if ((rc = prepare(cat.p, H, 3 * H, L.wqkv_bt, L.wqkv_cs, &L.wqkv, st)) != OMCUDA_OK)
+    return rc;
+  if ((rc = upload(t1, w->wo, (size_t)(H * H), st)) != OMCUDA_OK ||
+      (rc = prepare(t1.p, H, H, L.wo_bt, L.wo_cs, &L.wo, st)) != OMCUDA_OK)
+    return rc;
+  if ((rc = upload(t2, w->w1, (size_t)(H * F), st)) != OMCUDA_OK ||
+      (rc = prepare(t2.p, H, F, L.w1_bt, L.w1_cs, &L.w1, st)) != OMCUDA_OK)
+    return rc;
+  if ((rc = upload(t3, w->w2, (size_t)(F * H), st)) != OMCUDA_OK ||
+      (rc = prepare(t3.p, F, H, L.w2_bt, L.w2_cs, &L.w2, st)) != OMCUDA_OK)
+    return rc;
+  // scales
+  L.qkv_scale.ensure((size_t)(3 * H) * sizeof(float));
+  L.scal.ensure(4 * sizeof(float));
+  if (!L.qkv_scale.p || !L.scal.p)
+    return OMCUDA_ENOMEM;
+  for (int i = 0; i < 3; ++i) {
+    fill_kernel<<<(unsigned)ceil_div(H, 256), 256, 0, st>>>(
+        (float *)L.qkv_scale.p + i * H, H, w->w_scale[i]);
+    count_launch();
+  }
+  float hs[4] = {w->w_scale[3], w->w_scale[4], w->w_scale[5], 0.0f};
+  if ((rc = check_cuda(cudaMemcpyAsync(L.scal.p, hs, sizeof(hs),
+                           cudaMemcpyHostToDevice, st),
+           "encoder: scales")) != OMCUDA_OK)
+    return rc;
+  // biases and LayerNorm parameters
+  L.bqkv.ensure((size_t)(3 * H) * sizeof(float));
+  if (!L.bqkv.p)
+    return OMCUDA_ENOMEM;
+  const OMTensor *bs[3] = {w->bq, w->bk, w->bv};
+  for (int i = 0; i < 3; ++i)
+    if ((rc = check_cuda(cudaMemcpyAsync((float *)L.bqkv.p + i * H,
+                             omTensorGetDataPtr(bs[i]), (size_t)H * 4,
+                             cudaMemcpyDefault, st),
+             "encoder: bias")) != OMCUDA_OK)
+      return rc;
+  if ((rc = upload(L.bo, w->bo, (size_t)H * 4, st)) != OMCUDA_OK ||
+      (rc = upload(L.b1, w->b1, (size_t)F * 4, st)) != OMCUDA_OK ||
+      (rc = upload(L.b2, w->b2, (size_t)H * 4, st)) != OMCUDA_OK ||
+      (rc = upload(L.ln1g, w->ln1_gamma, (size_t)H * 4, st)) != OMCUDA_OK ||
+      (rc = upload(L.ln2g, w->ln2_gamma, (size_t)H * 4, st)) != OMCUDA_OK)
+    return rc;
+  L.has_ln1b = w->ln1_beta != nullptr;
+  L.has_ln2b = w->ln2_beta != nullptr;
+  if (L.has_ln1b &&
+      (rc = upload(L.ln1b, w->ln1_beta, (size_t)H * 4, st)) != OMCUDA_OK)
+    return rc;
+  if (L.has_ln2b &&
+      (rc = upload(L.ln2b, w->ln2_beta, (size_t)H * 4, st)) != OMCUDA_OK)
+    return rc;
+  // hs[] and the staging buffers go out of scope: finish the copies first.
+  if ((rc = check_cuda(cudaStreamSynchronize(st), "encoder: sync")) != OMCUDA_OK)
+    return rc;
+  tq.release();
+  tk.release();
+  tv.release();
+  cat.release();
+  t1.release();
+  t2.release();
+  t3.release();
+  L.set = true;
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
+    int64_t batch, int64_t seq, float *y, void *stream) {
+  if (!e || !x || !y || batch <= 0 || seq <= 0)
+    return fail(OMCUDA_EINVAL, "EncoderRun: bad argument");
+  for (auto &L : e->layers)
+    if (!L.set)
+      return fail(OMCUDA_EINVAL, "EncoderRun: a layer has no weights");
+  const int64_t H = e->cfg.hidden, F = e->cfg.ffn, heads = e->cfg.heads;
+  const int64_t dh = H / heads, T = batch * seq;
+  int rc = ensure_workspace(e, T);
+  if (rc != OMCUDA_OK)
+    return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const float att_scale = 1.0f / sqrtf((float)dh);
+  const float eps = (float)e->cfg.epsilon;
+  const int64_t nranges = 4 * e->cfg.layers + 1;
+  uint8_t *ranges = (uint8_t *)e->ranges.p;
+  float *params = (float *)e->params.p;
+  uint8_t *xq = (uint8_t *)e->xq.p;
+#define RUN(call)                                                              \
+  do {                                                                         \
+    rc = (call);                                                               \
+    if (rc != OMCUDA_OK)                                                       \
+      return rc;                                                               \
+  } while (0)
+  RUN(omcudaDevRangeInit(ranges, nranges, st));
+  // Slot layout of a quantize site (4 floats): [0] scale, [1] zero point as
+  // float (both read by the quantize pass), [2] scale as the op's y_scale
+  // output, [3] first byte: zero point as uint8 (the GEMM's a_zero_point).
+  // The model input has no producer here: it gets the standalone reduction.
+  RUN(omcudaDevDynamicQuantizeLinear(x, T * H, xq, params + 2,
+      (uint8_t *)(params + 3), e->dql_scratch.p, st));
+  const float *cur = x;
+  for (int64_t l = 0; l < e->cfg.layers; ++l) {
+    LayerState &L = e->layers[(size_t)l];
+    uint8_t *r_x = ranges + (size_t)(4 * l) * 8;
+    uint8_t *r_ctx = ranges + (size_t)(4 * l + 1) * 8;
+    uint8_t *r_h1 = ranges + (size_t)(4 * l + 2) * 8;
+    uint8_t *r_f = ranges + (size_t)(4 * l + 3) * 8;
+    uint8_t *r_y = ranges + (size_t)(4 * l + 4) * 8;
+    float *p_x = params + (size_t)(4 * l) * 4;
+    float *p_ctx = params + (size_t)(4 * l + 1) * 4;
+    float *p_h1 = params + (size_t)(4 * l + 2) * 4;
+    float *p_f = params + (size_t)(4 * l + 3) * 4;
+    float *nxt = (l + 1 == e->cfg.layers) ? y : (float *)e->ybuf[l & 1].p;
+    if (l > 0)
+      RUN(omcudaDevQuantizeFromRange(cur, T * H, r_x, xq, p_x, p_x + 2,
+          (uint8_t *)(p_x + 3), st));
+    RUN(gemm(xq, (const uint8_t *)(p_x + 3), p_x + 2, L.wqkv, T,
+        (const float *)L.qkv_scale.p, 3 * H, (const float *)L.bqkv.p, 0,
+        (float *)e->qkv.p, nullptr, st));
+    const float *q = (const float *)e->qkv.p;
+    RUN(omcudaDevAttentionEx(q, q + H, q + 2 * H, batch, seq, heads, dh,
+        att_scale, (float *)e->ctx.p, 3 * H, H, r_ctx, st));
+    RUN(omcudaDevQuantizeFromRange((const float *)e->ctx.p, T * H, r_ctx, xq,
+        p_ctx, p_ctx + 2, (uint8_t *)(p_ctx + 3), st));
+    RUN(gemm(xq, (const uint8_t *)(p_ctx + 3), p_ctx + 2, L.wo, T,
+        (const float *)L.scal.p, 1, (const float *)L.bo.p, 0, (float *)e->a.p,
+        nullptr, st));
+    RUN(omcudaDevLayerNorm(cur, (const float *)e->a.p, T, H,
+        (const float *)L.ln1g.p, L.has_ln1b ? (const float *)L.ln1b.p : nullptr,
+        eps, (float *)e->h1.p, r_h1, st));
+    RUN(omcudaDevQuantizeFromRange((const float *)e->h1.p, T * H, r_h1, xq,
+        p_h1, p_h1 + 2, (uint8_t *)(p_h1 + 3), st));
+    RUN(gemm(xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
+        (const float *)L.scal.p + 1, 1, (const float *)L.b1.p, 1,
+        (float *)e->f.p, r_f, st));
+    RUN(omcudaDevQuantizeFromRange((const float *)e->f.p, T * F, r_f, xq, p_f,
+        p_f + 2, (uint8_t *)(p_f + 3), st));
+    RUN(gemm(xq, (const uint8_t *)(p_f + 3), p_f + 2, L.w2, T,
+        (const float *)L.scal.p + 2, 1, (const float *)L.b2.p, 0,
+        (float *)e->o.p, nullptr, st));
+    RUN(omcudaDevLayerNorm((const float *)e->h1.p, (const float *)e->o.p, T, H,
+        (const float *)L.ln2g.p, L.has_ln2b ? (const float *)L.ln2b.p : nullptr,
+        eps, nxt, r_y, st));
+    cur = nxt;
+  }
+#undef RUN
+  return OMCUDA_OK;
+}
+
+extern "C" OMTensorList *omcudaEncoderRun(omcudaEncoder *e, OMTensorList *inputs) {
+  if (sticky_error() || ensure_init() != OMCUDA_OK)
+    return nullptr;
+  if (!e || !inputs || omTensorListGetSize(inputs) != 1) {
+    fail(OMCUDA_EINVAL, "EncoderRun: expected one input tensor");
+    return nullptr;
+  }
+  const OMTensor *x = omTensorListGetOmtByIndex(inputs, 0);
+  // The checks a generated entry point makes on its inputs
+  // (KrnlEntryPoint.cpp:430-545): element type, rank, static dimensions.
+  if (!x || omTensorGetDataType(x) != ONNX_TYPE_FLOAT || omTensorGetRank(x) != 3 ||
+      omTensorGetShape(x)[2] != e->cfg.hidden) {
+    fail(OMCUDA_EINVAL, "EncoderRun: input must be f32 [batch, seq, %lld]",
+        (long long)e->cfg.hidden);
+    return nullptr;
+  }
+  const int64_t B = omTensorGetShape(x)[0], S = omTensorGetShape(x)[1];
+  const int64_t n = B * S * e->cfg.hidden;
+  cudaStream_t st = current_stream();
+  const bool on_dev = omcudaTensorIsOnDevice(x) != 0;
+  OMTensor *out = nullptr;
+  if (on_dev) {
+    out = omcudaTensorCreateOnDevice(omTensorGetShape(x), 3, ONNX_TYPE_FLOAT);
+    if (!out)
+      return nullptr;
+    if (omcudaEncoderRunDev(e, (const float *)omTensorGetDataPtr(x), B, S,
+            (float *)omTensorGetDataPtr(out), st) != OMCUDA_OK) {
+      omcudaTensorDestroy(out);
+      return nullptr;
+    }
+  } else {
+    DevBuf dx, dy;
+    dx.ensure((size_t)n * 4);
+    dy.ensure((size_t)n * 4);
+    out = omTensorCreateEmpty(omTensorGetShape(x), 3, ONNX_TYPE_FLOAT);
+    bool ok = dx.p && dy.p && out;
+    ok = ok && check_cuda(cudaMemcpyAsync(dx.p, omTensorGetDataPtr(x),
+                              (size_t)n * 4, cudaMemcpyHostToDevice, st),
+                   "encoder: H2D") == OMCUDA_OK;
+    ok = ok && omcudaEncoderRunDev(e, (const float *)dx.p, B, S, (float *)dy.p,
+                   st) == OMCUDA_OK;
+    ok = ok && check_cuda(cudaMemcpyAsync(omTensorGetDataPtr(out), dy.p,
+                              (size_t)n * 4, cudaMemcpyDeviceToHost, st),
+                   "encoder: D2H") == OMCUDA_OK;
+    if (ok) {
+      omcudaSynchronize();
+      ok = !sticky_error();
+    }
+    dx.release();
+    dy.release();
+    if (!ok) {
+      if (out)
+        omTensorDestroy(out);
+      if (!sticky_error())
+        fail(OMCUDA_ENOMEM, "EncoderRun: allocation failed");
+      return nullptr;
+    }
+  }
+  OMTensor *arr[1] = {out};
+  OMTensorList *res = omTensorListCreate(arr, 1);
+  if (!res) {
+    fail(OMCUDA_ENOMEM, "EncoderRun: cannot build the output list");
+    return nullptr;
+  }
+  return res;
+}
+
+extern "C" void omcudaEncoderDestroy(omcudaEncoder *e) {
+  if (!e)
+    return;
+  if (OMIsInitAccelCUDA)
+    cudaStreamSynchronize(current_stream());
+  for (auto &L : e->layers) {
+    DevBuf *all[] = {&L.wqkv_bt, &L.wqkv_cs, &L.wo_bt, &L.wo_cs, &L.w1_bt,
+        &L.w1_cs, &L.w2_bt, &L.w2_cs, &L.qkv_scale, &L.scal, &L.bqkv, &L.bo,
+        &L.b1, &L.b2, &L.ln1g, &L.ln1b, &L.ln2g, &L.ln2b};
+    for (DevBuf *b : all)
+      b->release();
+  }
+  DevBuf *ws[] = {&e->xq, &e->qkv, &e->ctx, &e->a, &e->h1, &e->f, &e->o,
+      &e->ybuf[0], &e->ybuf[1], &e->ranges, &e->params, &e->dql_scratch};
+  for (DevBuf *b : ws)
+    b->release();
+  delete e;
+}

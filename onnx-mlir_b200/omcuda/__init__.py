@@ -389,3 +389,103 @@ def attention(q, k, v, heads, scale, device=False):
                           float(scale))
     check()
     return y if device else y.numpy()
+
+
+# ---- encoder model harness ---------------------------------------------------
+
+class _EncoderConfig(ctypes.Structure):
+    _fields_ = [("layers", ctypes.c_int64), ("hidden", ctypes.c_int64),
+                ("heads", ctypes.c_int64), ("ffn", ctypes.c_int64),
+                ("epsilon", ctypes.c_double)]
+
+
+class _EncoderLayerWeights(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("wq", "wk", "wv", "wo", "w1", "w2")] +
+                [("w_scale", ctypes.c_float * 6)] +
+                [(n, ctypes.c_void_p) for n in ("bq", "bk", "bv", "bo", "b1", "b2",
+                                                "ln1_gamma", "ln1_beta",
+                                                "ln2_gamma", "ln2_beta")])
+
+
+class Encoder:
+    """The run_main_graph-shaped harness for the BERT-shaped encoder configs
+    (omcudaEncoder* in omcuda.h).  `layers` is a list of dicts with int8
+    weights wq,wk,wv,wo [H,H], w1 [H,F], w2 [F,H], `sc` (6 weight scales),
+    f32 biases bq,bk,bv,bo,b1,b2 and ln1g,ln1b,ln2g,ln2b."""
+
+    def __init__(self, hidden, heads, ffn, layers, epsilon=1e-5):
+        L = lib()
+        L.omcudaEncoderCreate.restype = ctypes.c_void_p
+        L.omcudaEncoderCreate.argtypes = [ctypes.POINTER(_EncoderConfig)]
+        L.omcudaEncoderSetLayer.argtypes = [ctypes.c_void_p, ctypes.c_int64,
+                                            ctypes.POINTER(_EncoderLayerWeights)]
+        L.omcudaEncoderRun.restype = ctypes.c_void_p
+        L.omcudaEncoderRun.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        L.omcudaEncoderRunDev.argtypes = [ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_int64, ctypes.c_int64,
+                                          ctypes.c_void_p, ctypes.c_void_p]
+        L.omcudaEncoderDestroy.argtypes = [ctypes.c_void_p]
+        cfg = _EncoderConfig(len(layers), hidden, heads, ffn, epsilon)
+        self.hidden = hidden
+        self.handle = L.omcudaEncoderCreate(ctypes.byref(cfg))
+        if not self.handle:
+            check()
+            raise OmcudaError(EINVAL, "omcudaEncoderCreate failed")
+        for i, w in enumerate(layers):
+            keep = {}
+            lw = _EncoderLayerWeights()
+            names = {"wq": "wq", "wk": "wk", "wv": "wv", "wo": "wo", "w1": "w1",
+                     "w2": "w2", "bq": "bq", "bk": "bk", "bv": "bv", "bo": "bo",
+                     "b1": "b1", "b2": "b2", "ln1g": "ln1_gamma",
+                     "ln1b": "ln1_beta", "ln2g": "ln2_gamma", "ln2b": "ln2_beta"}
+            for src, dst in names.items():
+                if w.get(src) is None:
+                    continue
+                keep[src] = Tensor.from_numpy(w[src])
+                setattr(lw, dst, keep[src].handle)
+            for j in range(6):
+                lw.w_scale[j] = float(w["sc"][j])
+            rc = L.omcudaEncoderSetLayer(self.handle, i, ctypes.byref(lw))
+            if rc != 0:
+                check()
+                raise OmcudaError(rc, "omcudaEncoderSetLayer failed")
+
+    def run(self, x):
+        """run_main_graph: numpy [B,S,H] in, numpy out (staged through HBM), or
+        a device Tensor in, device Tensor out."""
+        L = lib()
+        dev = isinstance(x, Tensor)
+        t = x if dev else Tensor.from_numpy(np.asarray(x, np.float32))
+        arr = (ctypes.c_void_p * 1)(t.handle)
+        ins = L.omTensorListCreate(arr, 1)
+        outs = L.omcudaEncoderRun(self.handle, ins)
+        L.omTensorListDestroyShallow(ins)
+        if not outs:
+            check()
+            raise OmcudaError(ECUDA, "omcudaEncoderRun returned NULL")
+        o = L.omTensorListGetOmtByIndex(outs, 0)
+        L.omTensorListDestroyShallow(outs)
+        if dev:
+            return Tensor(o, None, True)
+        n = L.omTensorGetNumElems(o)
+        buf = (ctypes.c_char * (4 * n)).from_address(L.omTensorGetDataPtr(o))
+        out = np.frombuffer(buf, dtype=np.float32, count=n).reshape(t.shape).copy()
+        L.omTensorDestroy(o)
+        return out
+
+    def run_dev(self, x_ptr, batch, seq, y_ptr, stream):
+        rc = lib().omcudaEncoderRunDev(self.handle, x_ptr, batch, seq, y_ptr, stream)
+        if rc != 0:
+            check()
+            raise OmcudaError(rc, "omcudaEncoderRunDev failed")
+
+    def close(self):
+        if self.handle:
+            lib().omcudaEncoderDestroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
