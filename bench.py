@@ -11,6 +11,11 @@ shapes and value distributions of the reference configurations):
               metric int8 TOPS (2*M*N*K per step).
   qlinear_c2  QLinearMatMul A u8 [32,512,1024] x B i8 [1024,4096] -> u8,
               per-column b_scale; metric int8 TOPS.
+  bert_base   dynamic-quantized encoder, 12 layers, hidden 768, 12 heads,
+              FFN 3072, seq 128, batch 32; metric sequences/s.
+  bert_large  24 layers, hidden 1024, 16 heads, FFN 4096, seq 512, batch 256;
+              metric sequences/s.  With N > 1 the per-rank outputs are joined
+              by one NCCL all-gather inside the step.
 
 A step is one pass of the workload's graph over one batch.  `value` is timed
 with inputs resident in HBM; `e2e` runs the same graph through the krnl.call
@@ -137,6 +142,7 @@ class GpuEnv:
 
 class LinearWorkload:
     """DQL -> int8 GEMM -> dequant (mmi_4096) or QLinearMatMul (qlinear_c2)."""
+    metric, unit, dtype = "MatMulInteger int8 TOPS", "TOPS", "u8*s8->s32"
 
     def __init__(self, env, name, seed):
         self.env, self.name = env, name
@@ -266,14 +272,61 @@ class LinearWorkload:
                 "graph": ("DynamicQuantizeLinear->MatMulInteger->Cast/Mul"
                           if self.kind == "dynquant" else "QLinearMatMul")}
 
-    def cpu_sample(self, orc, threads, rows):
-        """Times the reference-shaped CPU lowering on `rows` rows; returns ops/s."""
-        rng = np.random.default_rng(0)
-        A = rng.integers(0, 256, (rows, self.K), dtype=np.uint8)
-        t0 = time.perf_counter()
-        orc.ref_shaped_matmul_integer(A, self.Wh, 128, threads)
-        dt = time.perf_counter() - t0
-        return 2.0 * rows * self.N * self.K / dt, dt
+
+class EncoderWorkload:
+    """BERT-shaped dynamic-quantized encoder through the model harness."""
+    SHAPES = {
+        "bert_base": dict(layers=12, H=768, heads=12, F=3072, S=128, B=32),
+        "bert_large": dict(layers=24, H=1024, heads=16, F=4096, S=512, B=256),
+    }
+    metric, unit, dtype = "quantized BERT seq/s", "seq/s", "u8*s8->s32 + f32"
+
+    def __init__(self, env, name, seed, world, dist):
+        from omcuda.synthetic import make_encoder
+        self.env, self.name, self.world, self.dist = env, name, world, dist
+        c = self.SHAPES[name]
+        self.c = c
+        torch = env.torch
+        self.layers = make_encoder(42, c["H"], c["F"], c["layers"])  # replicated
+        self.enc = env.m.Encoder(c["H"], c["heads"], c["F"], self.layers)
+        rng = np.random.default_rng(seed)
+        shape = (c["B"], c["S"], c["H"])
+        self.hX = torch.from_numpy(rng.normal(size=shape).astype(np.float32)).pin_memory()
+        self.X = self.hX.to(env.device)
+        self.Y = torch.empty(shape, dtype=torch.float32, device=env.device)
+        self.Yall = (torch.empty((world * c["B"],) + shape[1:], dtype=torch.float32,
+                                 device=env.device) if world > 1 else None)
+        self.oX = env.m.Tensor.from_numpy(self.hX.numpy())
+        self.units = float(c["B"])
+        T = c["B"] * c["S"]
+        self.h2d = T * c["H"] * 4
+        self.d2h = T * c["H"] * 4
+        self.launches_per_step = None
+        env.torch.cuda.synchronize()
+
+    def step(self, _ev=None):
+        c = self.c
+        self.enc.run_dev(self.X.data_ptr(), c["B"], c["S"], self.Y.data_ptr(),
+                         self.env.sptr())
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.Yall, self.Y)
+
+    def step_e2e(self):
+        out = self.enc.run(self.oX.array)   # host in, host out, copies inside
+        self.last = float(out.ravel()[0])
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.Yall, self.Y)
+
+    def config(self):
+        c = self.c
+        return {"workload": self.name, "layers": c["layers"], "hidden": c["H"],
+                "heads": c["heads"], "ffn": c["F"], "seq_len": c["S"],
+                "batch_per_gpu": c["B"],
+                "parallelism": "batch sharded, weights replicated, one "
+                               "all-gather of outputs per step" if self.world > 1
+                               else "single GPU",
+                "l2": "flushed between timed iterations (256 MiB write)",
+                "quantization": "per-shard dynamic (each rank quantizes its own batch)"}
 
 
 def run_gpu(args):
@@ -286,7 +339,11 @@ def run_gpu(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     env = GpuEnv(local_rank)
-    wl = LinearWorkload(env, args.workload, seed=42 + rank)
+    is_encoder = args.workload in EncoderWorkload.SHAPES
+    if is_encoder:
+        wl = EncoderWorkload(env, args.workload, 42 + rank, world, dist)
+    else:
+        wl = LinearWorkload(env, args.workload, seed=42 + rank)
     peaks = load_peaks()
 
     def barrier():
@@ -294,7 +351,7 @@ def run_gpu(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup, per_step_events=True, extra=None):
+    def timed(fn, steps, warmup, extra=None):
         for _ in range(warmup):
             env.flush_l2()
             fn()
@@ -315,105 +372,147 @@ def run_gpu(args):
         return ms
 
     sampler = ClockSampler(local_rank)
-    launches0 = env.m.launch_count()
     gemm_evs = [(torch.cuda.Event(enable_timing=True),
                  torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # warm-up outside the launch count and the GEMM statistics
+    for _ in range(args.warmup):
+        env.flush_l2()
+        wl.step()
+    barrier()
+    launches0 = env.m.launch_count()
+    if is_encoder:
+        wl.enc.set_profiling(True)
     if rank == 0:
         sampler.start()
-    ms = timed(lambda ev=None: wl.step(ev), args.steps, args.warmup, extra=gemm_evs)
+    ms = timed(lambda ev=None: wl.step(ev), args.steps, 0, extra=gemm_evs)
     clocks = sampler.stop() if rank == 0 else None
-    launches = (env.m.launch_count() - launches0) * args.steps // (
-        args.steps + args.warmup)
-    gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_evs) / args.steps
+    launches = env.m.launch_count() - launches0
+    if is_encoder:
+        gemm_ms_total, gemm_ops_total, gemm_n = wl.enc.gemm_stats()
+        wl.enc.set_profiling(False)
+        gemm_ms = gemm_ms_total / max(gemm_n, 1)
+        achieved = gemm_ops_total / (gemm_ms_total * 1e-3) / 1e12
+        roof_extra = {"launches_timed": gemm_n, "avg_launch_ms": gemm_ms,
+                      "share_of_step": gemm_ms_total / ms}
+        algo_bytes = None
+    else:
+        gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_evs) / args.steps
+        achieved = wl.ops / (gemm_ms * 1e-3) / 1e12
+        roof_extra = {"avg_launch_ms": gemm_ms}
+        algo_bytes = wl.gemm_bytes
     env.m.synchronize()
 
-    e2e_steps = max(1, min(args.steps, 10))
+    e2e_steps = max(1, min(args.steps, 5 if is_encoder else 10))
     e2e_ms = timed(wl.step_e2e, e2e_steps, 1)
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-    value = wl.units * world * args.steps / (ms * 1e-3) / 1e12
-    e2e_value = wl.units * world * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    scale = 1e12 if wl.unit == "TOPS" else 1.0
+    value = wl.units * world * args.steps / (ms * 1e-3) / scale
+    e2e_value = wl.units * world * e2e_steps / (e2e_ms * 1e-3) / scale
     int8_peak = 2.0 * peaks["bf16_tflops"]
-    achieved = wl.ops / (gemm_ms * 1e-3) / 1e12
+    roofline = {
+        "kernel": "gemm_i8_tc_kernel", "bound": "tensor",
+        "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
+        "frac": achieved / int8_peak,
+        "peak_source": "2 x %s TFLOP/s bf16 cuBLAS burst (%s); an int8 figure "
+                       "is not in MEASURED_PEAKS.json" % (peaks["bf16_tflops"],
+                                                          peaks["source"]),
+        "algorithmic_bytes": algo_bytes, "traffic": None}
+    roofline.update(roof_extra)
     out = {
-        "metric": "MatMulInteger int8 TOPS", "value": value, "unit": "TOPS",
+        "metric": wl.metric, "value": value, "unit": wl.unit,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "u8*s8->s32",
+        "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
         "data": "synthetic", "config": wl.config(),
-        "e2e": {"value": e2e_value, "unit": "TOPS",
+        "e2e": {"value": e2e_value, "unit": wl.unit,
                 "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
                 "steps": e2e_steps},
         "gpu_launches": int(launches),
         "clocks": clocks,
-        "roofline": {
-            "kernel": "gemm_i8_tc_kernel", "bound": "tensor",
-            "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-            "frac": achieved / int8_peak,
-            "peak_source": "2 x %s bf16 cuBLAS burst (%s); int8 itself is not "
-                           "in MEASURED_PEAKS.json" % (peaks["bf16_tflops"],
-                                                       peaks["source"]),
-            "kernel_ms": gemm_ms,
-            "algorithmic_bytes": wl.gemm_bytes,
-            "traffic": None,
-        },
+        "roofline": roofline,
     }
-    # CPU baseline on a bounded sample of the same GEMM (rank 0, N=1 only).
+    # CPU baseline on a bounded sample of the same workload (rank 0, N=1 only).
     if world == 1 and not args.no_cpu_baseline:
-        import oracle_lib
-        orc = oracle_lib.Oracle(os.path.join(ROOT, "oracle", "_build",
-                                             "liboracle.so"))
-        threads = orc.L.orc_max_threads()
-        rows = 256
-        ops_s, dt = wl.cpu_sample(orc, threads, rows)
-        out["cpu_baseline"] = {
-            "value": ops_s / 1e12, "unit": "TOPS", "cores": threads,
-            "kind": "port",
-            "sample": "%d of %d rows of the same [K=%d,N=%d] GEMM, "
-                      "reference-shaped lowering (widen to i32, 4x8x8 tile), "
-                      "%.1f s" % (rows, wl.M, wl.K, wl.N, dt)}
+        out["cpu_baseline"] = cpu_baseline(args.workload, wl)
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_reference(args):
-    """CPU arm: the reference-shaped port of the same GEMM on all host threads."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+def cpu_baseline(workload, wl=None, reps=1):
+    """Times the oracle's reference-shaped CPU code on a bounded sample."""
     import oracle_lib
     orc = oracle_lib.Oracle(os.path.join(ROOT, "oracle", "_build", "liboracle.so"))
     threads = orc.L.orc_max_threads()
+    if workload in EncoderWorkload.SHAPES:
+        c = EncoderWorkload.SHAPES[workload]
+        if wl is not None:
+            layer = wl.layers[0]
+        else:
+            from omcuda.synthetic import make_encoder
+            layer = make_encoder(42, c["H"], c["F"], 1)[0]
+        bs = 2 if workload == "bert_large" else 8
+        x = np.random.default_rng(0).normal(size=(bs * c["S"], c["H"])).astype(np.float32)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            orc.encoder_layer(x, bs, c["S"], c["H"], c["heads"], c["F"], layer)
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": bs / (dt * c["layers"]), "unit": "seq/s", "cores": threads,
+                "kind": "port", "seconds_per_rep": dt,
+                "sample": "one of %d layers on %d of %d sequences (%.1f s), scaled "
+                          "by the layer count; oracle ops with OpenMP"
+                          % (c["layers"], bs, c["B"], dt)}
     shapes = {"mmi_4096": (4096, 4096, 4096), "qlinear_c2": (16384, 4096, 1024)}
-    M, N, K = shapes[args.workload]
-    rng = np.random.default_rng(42)
-    W = rng.integers(-127, 128, (K, N), dtype=np.int8)
-    rows = 128
+    M, N, K = shapes[workload]
+    rng = np.random.default_rng(0)
+    rows = 256
     A = rng.integers(0, 256, (rows, K), dtype=np.uint8)
-    for _ in range(args.warmup):
-        orc.ref_shaped_matmul_integer(A, W, 128, threads)
+    W = wl.Wh if wl is not None else rng.integers(-127, 128, (K, N), dtype=np.int8)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(reps):
         orc.ref_shaped_matmul_integer(A, W, 128, threads)
-    dt = time.perf_counter() - t0
-    value = 2.0 * rows * N * K * args.steps / dt / 1e12
-    sample = ("%d of %d rows per step, reference-shaped lowering on %d threads"
-              % (rows, M, threads))
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 2.0 * rows * N * K / dt / 1e12, "unit": "TOPS",
+            "cores": threads, "kind": "port", "seconds_per_rep": dt,
+            "sample": "%d of %d rows of the same [K=%d,N=%d] GEMM, reference-shaped "
+                      "lowering (operands widened to i32, 4x8x8 register tile, "
+                      "OpenMP over rows), %.2f s" % (rows, M, K, N, dt)}
+
+
+def run_reference(args):
+    """CPU arm: the oracle's port of the reference's lowering on all host
+    threads, same metric and config, each step a bounded sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(args.warmup):
+        cpu_baseline(args.workload)
+    cb = cpu_baseline(args.workload, reps=args.steps)
+    is_encoder = args.workload in EncoderWorkload.SHAPES
+    if is_encoder:
+        c = EncoderWorkload.SHAPES[args.workload]
+        config = {"workload": args.workload, "layers": c["layers"], "hidden": c["H"],
+                  "heads": c["heads"], "ffn": c["F"], "seq_len": c["S"],
+                  "batch_per_gpu": c["B"]}
+        metric, dtype = EncoderWorkload.metric, EncoderWorkload.dtype
+    else:
+        M, N, K = {"mmi_4096": (4096, 4096, 4096),
+                   "qlinear_c2": (16384, 4096, 1024)}[args.workload]
+        config = {"workload": args.workload, "M": M, "N": N, "K": K}
+        metric, dtype = LinearWorkload.metric, LinearWorkload.dtype
+    dt = cb.pop("seconds_per_rep")
     print(json.dumps({
-        "impl": "reference", "metric": "MatMulInteger int8 TOPS", "value": value,
-        "unit": "TOPS", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
-        "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "u8*s8->s32",
-        "data": "synthetic",
-        "config": {"workload": args.workload, "M": M, "N": N, "K": K},
-        "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads,
-                         "kind": "port", "sample": sample},
-        "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0,
+        "impl": "reference", "metric": metric, "value": cb["value"],
+        "unit": cb["unit"], "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": dtype, "data": "synthetic", "config": config,
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": cb["unit"], "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0}}))
 
 
@@ -423,7 +522,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="omcuda", choices=["omcuda", "reference"])
-    ap.add_argument("--workload", default="mmi_4096")
+    ap.add_argument("--workload", default="bert_large",
+                    choices=["mmi_4096", "qlinear_c2", "bert_base", "bert_large"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "omcuda" else args.warmup

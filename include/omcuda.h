@@ -353,6 +353,12 @@ OMTensorList *omcudaEncoderRun(omcudaEncoder *enc, OMTensorList *inputs);
 /* Device-pointer form: x, y are device f32 [batch*seq, hidden]. */
 int omcudaEncoderRunDev(omcudaEncoder *enc, const float *x, int64_t batch,
     int64_t seq, float *y, void *stream);
+/* Optional: bracket every int8 GEMM launch of later runs with CUDA events on
+ * the run's stream; omcudaEncoderGemmStats returns their summed duration, the
+ * 2*M*N*K they cover and their count since profiling was switched on. */
+void omcudaEncoderSetProfiling(omcudaEncoder *enc, int on);
+int omcudaEncoderGemmStats(
+    omcudaEncoder *enc, double *ms_total, double *ops_total, int64_t *launches);
 void omcudaEncoderDestroy(omcudaEncoder *enc);
 
 #ifdef __cplusplus

@@ -80,6 +80,11 @@ struct omcudaEncoder {
   DevBuf ranges;  // 4 running ranges per layer + 1
   DevBuf params;  // 16 bytes per quantize site
   DevBuf dql_scratch;
+  // optional timing of the GEMM launches (omcudaEncoderSetProfiling)
+  bool profiling = false;
+  std::vector<cudaEvent_t> ev;   // start/end pairs, recorded on the run stream
+  size_t ev_used = 0;
+  double gemm_ops = 0.0;         // 2*M*N*K summed over the recorded launches
 };
 
 namespace {
@@ -136,9 +141,26 @@ __global__ void fill_kernel(float *dst, int64_t n, float v) {
     dst[i] = v;
 }
 
-int gemm(const uint8_t *A, const uint8_t *a_zp, const float *a_scale,
-    const omcudaPreparedB &B, int64_t M, const float *w_scale, int64_t ws_len,
-    const float *bias, int gelu, float *Y, void *out_range, cudaStream_t st) {
+int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
+    const float *a_scale, const omcudaPreparedB &B, int64_t M,
+    const float *w_scale, int64_t ws_len, const float *bias, int gelu, float *Y,
+    void *out_range, cudaStream_t st) {
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (e->profiling) {
+    while (e->ev.size() < e->ev_used + 2) {
+      cudaEvent_t ne;
+      if (cudaEventCreate(&ne) != cudaSuccess)
+        break;
+      e->ev.push_back(ne);
+    }
+    if (e->ev.size() >= e->ev_used + 2) {
+      e0 = e->ev[e->ev_used];
+      e1 = e->ev[e->ev_used + 1];
+      e->ev_used += 2;
+      e->gemm_ops += 2.0 * (double)M * (double)B.N * (double)B.K;
+      cudaEventRecord(e0, st);
+    }
+  }
   omcudaGemmArgs g;
   memset(&g, 0, sizeof(g));
   g.M = M;
@@ -158,7 +180,10 @@ int gemm(const uint8_t *A, const uint8_t *a_zp, const float *a_scale,
   g.bias = bias;
   g.gelu = gelu;
   g.out_minmax = out_range;
-  return omcudaDevGemmI8(&g, st);
+  int rc = omcudaDevGemmI8(&g, st);
+  if (e1)
+    cudaEventRecord(e1, st);
+  return rc;
 }
 
 int ensure_workspace(omcudaEncoder *e, int64_t T) {
@@ -360,7 +385,7 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
     if (l > 0)
       RUN(omcudaDevQuantizeFromRange(cur, T * H, r_x, xq, p_x, p_x + 2,
           (uint8_t *)(p_x + 3), st));
-    RUN(gemm(xq, (const uint8_t *)(p_x + 3), p_x + 2, L.wqkv, T,
+    RUN(gemm(e, xq, (const uint8_t *)(p_x + 3), p_x + 2, L.wqkv, T,
         (const float *)L.qkv_scale.p, 3 * H, (const float *)L.bqkv.p, 0,
         (float *)e->qkv.p, nullptr, st));
     const float *q = (const float *)e->qkv.p;
@@ -368,7 +393,7 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
         att_scale, (float *)e->ctx.p, 3 * H, H, r_ctx, st));
     RUN(omcudaDevQuantizeFromRange((const float *)e->ctx.p, T * H, r_ctx, xq,
         p_ctx, p_ctx + 2, (uint8_t *)(p_ctx + 3), st));
-    RUN(gemm(xq, (const uint8_t *)(p_ctx + 3), p_ctx + 2, L.wo, T,
+    RUN(gemm(e, xq, (const uint8_t *)(p_ctx + 3), p_ctx + 2, L.wo, T,
         (const float *)L.scal.p, 1, (const float *)L.bo.p, 0, (float *)e->a.p,
         nullptr, st));
     RUN(omcudaDevLayerNorm(cur, (const float *)e->a.p, T, H,
@@ -376,12 +401,12 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
         eps, (float *)e->h1.p, r_h1, st));
     RUN(omcudaDevQuantizeFromRange((const float *)e->h1.p, T * H, r_h1, xq,
         p_h1, p_h1 + 2, (uint8_t *)(p_h1 + 3), st));
-    RUN(gemm(xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
+    RUN(gemm(e, xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
         (const float *)L.scal.p + 1, 1, (const float *)L.b1.p, 1,
         (float *)e->f.p, r_f, st));
     RUN(omcudaDevQuantizeFromRange((const float *)e->f.p, T * F, r_f, xq, p_f,
         p_f + 2, (uint8_t *)(p_f + 3), st));
-    RUN(gemm(xq, (const uint8_t *)(p_f + 3), p_f + 2, L.w2, T,
+    RUN(gemm(e, xq, (const uint8_t *)(p_f + 3), p_f + 2, L.w2, T,
         (const float *)L.scal.p + 2, 1, (const float *)L.b2.p, 0,
         (float *)e->o.p, nullptr, st));
     RUN(omcudaDevLayerNorm((const float *)e->h1.p, (const float *)e->o.p, T, H,
@@ -460,11 +485,38 @@ extern "C" OMTensorList *omcudaEncoderRun(omcudaEncoder *e, OMTensorList *inputs
   return res;
 }
 
+extern "C" void omcudaEncoderSetProfiling(omcudaEncoder *e, int on) {
+  if (!e)
+    return;
+  e->profiling = on != 0;
+  e->ev_used = 0;
+  e->gemm_ops = 0.0;
+}
+
+extern "C" int omcudaEncoderGemmStats(
+    omcudaEncoder *e, double *ms_total, double *ops_total, int64_t *launches) {
+  if (!e || !ms_total || !ops_total || !launches)
+    return fail(OMCUDA_EINVAL, "EncoderGemmStats: bad argument");
+  double ms = 0.0;
+  for (size_t i = 0; i + 1 < e->ev_used; i += 2) {
+    OMCUDA_CHECK(cudaEventSynchronize(e->ev[i + 1]));
+    float t = 0.0f;
+    OMCUDA_CHECK(cudaEventElapsedTime(&t, e->ev[i], e->ev[i + 1]));
+    ms += t;
+  }
+  *ms_total = ms;
+  *ops_total = e->gemm_ops;
+  *launches = (int64_t)(e->ev_used / 2);
+  return OMCUDA_OK;
+}
+
 extern "C" void omcudaEncoderDestroy(omcudaEncoder *e) {
   if (!e)
     return;
   if (OMIsInitAccelCUDA)
     cudaStreamSynchronize(current_stream());
+  for (cudaEvent_t ev : e->ev)
+    cudaEventDestroy(ev);
   for (auto &L : e->layers) {
     DevBuf *all[] = {&L.wqkv_bt, &L.wqkv_cs, &L.wo_bt, &L.wo_cs, &L.w1_bt,
         &L.w1_cs, &L.w2_bt, &L.w2_cs, &L.qkv_scale, &L.scal, &L.bqkv, &L.bo,

@@ -479,6 +479,21 @@ class Encoder:
             check()
             raise OmcudaError(rc, "omcudaEncoderRunDev failed")
 
+    def set_profiling(self, on):
+        lib().omcudaEncoderSetProfiling.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        lib().omcudaEncoderSetProfiling(self.handle, int(on))
+
+    def gemm_stats(self):
+        """(summed GEMM ms, summed 2*M*N*K, launches) since profiling began."""
+        L = lib()
+        L.omcudaEncoderGemmStats.argtypes = [ctypes.c_void_p] * 4
+        ms, ops, n = ctypes.c_double(), ctypes.c_double(), ctypes.c_int64()
+        rc = L.omcudaEncoderGemmStats(self.handle, ctypes.byref(ms),
+                                      ctypes.byref(ops), ctypes.byref(n))
+        if rc != 0:
+            check()
+        return ms.value, ops.value, n.value
+
     def close(self):
         if self.handle:
             lib().omcudaEncoderDestroy(self.handle)

@@ -17,7 +17,7 @@ Three layers of evidence:
 import numpy as np
 import pytest
 
-from encoder_util import make_encoder
+from omcuda.synthetic import make_encoder
 
 pytestmark = pytest.mark.gpu
 
