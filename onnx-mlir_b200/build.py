@@ -33,6 +33,7 @@ SOURCES = [
     "kernels/gemm_simt.cu",
     "kernels/gemm_tc.cu",
     "kernels/encoder_ops.cu",
+    "kernels/attention_mma.cu",
 ]
 
 NVCC_FLAGS = [

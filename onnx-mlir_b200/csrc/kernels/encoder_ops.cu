@@ -8,6 +8,9 @@
 //   MatMul fp32         src/Conversion/ONNXToKrnl/Math/MatMul.cpp:488-507
 // Reductions are reordered relative to the reference's sequential loops; the
 // parity tolerance for these ops is 1e-3 relative.
+#include <cstdlib>
+#include <cstring>
+
 #include "../runtime/internal.h"
 #include "../common.cuh"
 
@@ -463,6 +466,15 @@ extern "C" int omcudaDevAttentionEx(const float *Q, const float *K,
     return fail(OMCUDA_ENOTSUP, "Attention: head size must be 32, 64 or 128");
   if (B * heads > 65535)
     return fail(OMCUDA_ENOTSUP, "Attention: batch*heads exceeds 65535");
+  // Tensor-core kernel unless the rows are not aligned for it or the SIMT
+  // kernel is asked for (OMCUDA_ATTENTION=simt, used to cross-check the two).
+  static const bool force_simt = [] {
+    const char *s = getenv("OMCUDA_ATTENTION");
+    return s && strcmp(s, "simt") == 0;
+  }();
+  if (!force_simt && attention_mma_supported(Q, K, V, out, dh, ld_in, ld_out))
+    return launch_attention_mma(Q, K, V, B, S, heads, dh, scale, out, ld_in,
+        ld_out, out_range, (cudaStream_t)stream);
   size_t smem = (size_t)(dh * 33 + 32 * dh + kAttWarps * kAttRows * dh +
                          (int64_t)kAttWarps * kAttRows * S) *
                 sizeof(float);

@@ -27,4 +27,11 @@ bool gemm_tc_supported(const omcudaGemmArgs &a);
 int launch_gemm_tc(const omcudaGemmArgs &a, cudaStream_t st);
 int launch_gemm_simt(const omcudaGemmArgs &a, cudaStream_t st);
 
+// attention_mma.cu
+bool attention_mma_supported(const float *Q, const float *K, const float *V,
+    const float *out, int64_t dh, int64_t ld_in, int64_t ld_out);
+int launch_attention_mma(const float *Q, const float *K, const float *V,
+    int64_t B, int64_t S, int64_t heads, int64_t dh, float scale, float *out,
+    int64_t ld_in, int64_t ld_out, void *out_range, cudaStream_t st);
+
 } // namespace omcuda
