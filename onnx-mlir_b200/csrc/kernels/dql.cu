@@ -53,18 +53,24 @@ __global__ void __launch_bounds__(kDqlThreads)
   if (aligned) {
     const int64_t n4 = n >> 2;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    // Two independent loads in flight per thread per trip.
+    // Four independent 16-byte loads in flight per thread per trip.
     int64_t i = tid;
-    for (; i + nthreads < n4; i += 2 * nthreads) {
-      float4 a = __ldg(x4 + i);
-      float4 b = __ldg(x4 + i + nthreads);
+    for (; i + 3 * nthreads < n4; i += 4 * nthreads) {
+      float4 a = __ldcs(x4 + i);
+      float4 b = __ldcs(x4 + i + nthreads);
+      float4 c = __ldcs(x4 + i + 2 * nthreads);
+      float4 d = __ldcs(x4 + i + 3 * nthreads);
       lo = fminf(lo, fminf(fminf(a.x, a.y), fminf(a.z, a.w)));
       hi = fmaxf(hi, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
       lo = fminf(lo, fminf(fminf(b.x, b.y), fminf(b.z, b.w)));
       hi = fmaxf(hi, fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
+      lo = fminf(lo, fminf(fminf(c.x, c.y), fminf(c.z, c.w)));
+      hi = fmaxf(hi, fmaxf(fmaxf(c.x, c.y), fmaxf(c.z, c.w)));
+      lo = fminf(lo, fminf(fminf(d.x, d.y), fminf(d.z, d.w)));
+      hi = fmaxf(hi, fmaxf(fmaxf(d.x, d.y), fmaxf(d.z, d.w)));
     }
     for (; i < n4; i += nthreads) {
-      float4 a = __ldg(x4 + i);
+      float4 a = __ldcs(x4 + i);
       lo = fminf(lo, fminf(fminf(a.x, a.y), fminf(a.z, a.w)));
       hi = fmaxf(hi, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
     }
@@ -160,8 +166,11 @@ __global__ void dql_params_from_range_kernel(uint32_t *__restrict__ range,
   range[1] = 0u;          // -inf side: any value raises it
 }
 
+// One element exactly as the reference computes it
+// (QuantizeLinear.cpp:124-145): IEEE divide, round half even, add the zero
+// point, clip, convert.
 template <bool kSigned>
-__device__ __forceinline__ uint32_t quantize_one(
+__device__ __forceinline__ uint32_t quantize_one_exact(
     float x, float scale, float zp_f) {
   float q = __fdiv_rn(x, scale);
   float r = round_even(q);
@@ -174,13 +183,56 @@ __device__ __forceinline__ uint32_t quantize_one(
   return (uint32_t)s; // fptoui; already within 8 bits
 }
 
+// Per-launch constants of the fast path.
+struct QuantConsts {
+  float scale, rcp, zp_f;
+  bool fast;
+};
+
+__device__ __forceinline__ QuantConsts make_quant_consts(float scale, float zp_f) {
+  QuantConsts c;
+  c.scale = scale;
+  c.zp_f = zp_f;
+  c.rcp = __fdiv_rn(1.0f, scale);
+  // The shortcut needs a normal, finite reciprocal; anything else (scale 0
+  // from an all-zero tensor, denormal or huge scales) takes the exact path.
+  const float as = fabsf(scale);
+  c.fast = (as > 1e-30f) && (as < 1e30f);
+  return c;
+}
+
+// Same result as quantize_one_exact with no divide or convert instruction on
+// the common path (those run on the quarter-rate special-function pipe and
+// would bound the kernel instead of HBM):
+//  * q' = x * RN(1/scale) is within 2.5 ulp of the IEEE quotient q.  Values
+//    with |q| > 512 saturate whatever their rounding, so q' is clamped to
+//    [-512, 512], where 2.5 ulp < 2e-4.
+//  * round half even by adding and subtracting 1.5 * 2^23 (exact for
+//    |q'| <= 2^22).  Unless q' lies within 1e-3 of a tie, q and q' round to the
+//    same integer; the rare near-tie element is redone with the exact divide.
+//  * after the clip the value is an integer in the output range, so its low
+//    eight bits can be read off the mantissa of (value + 1.5 * 2^23).
+// NaN quotients come out of the clamp as -512 and end at the lower clip
+// bound, which is where maxnum/minnum send a NaN in the reference as well.
 template <bool kSigned>
-__device__ __forceinline__ uint32_t quantize_four(
-    float4 v, float scale, float zp_f) {
-  return quantize_one<kSigned>(v.x, scale, zp_f) |
-         (quantize_one<kSigned>(v.y, scale, zp_f) << 8) |
-         (quantize_one<kSigned>(v.z, scale, zp_f) << 16) |
-         (quantize_one<kSigned>(v.w, scale, zp_f) << 24);
+__device__ __forceinline__ uint32_t quantize_one(float x, const QuantConsts &c) {
+  if (!c.fast)
+    return quantize_one_exact<kSigned>(x, c.scale, c.zp_f);
+  const float kMagic = 12582912.0f; // 1.5 * 2^23
+  float q = fminf(fmaxf(__fmul_rn(x, c.rcp), -512.0f), 512.0f);
+  float r = __fsub_rn(__fadd_rn(q, kMagic), kMagic);
+  if (fabsf(__fsub_rn(q, r)) > 0.499f)
+    r = round_even(__fdiv_rn(x, c.scale));
+  float a = __fadd_rn(r, c.zp_f);
+  float s = kSigned ? clipf(a, -128.0f, 127.0f) : clipf(a, 0.0f, 255.0f);
+  return __float_as_uint(__fadd_rn(s, kMagic)) & 0xffu;
+}
+
+template <bool kSigned>
+__device__ __forceinline__ uint32_t quantize_four(float4 v, const QuantConsts &c) {
+  return quantize_one<kSigned>(v.x, c) | (quantize_one<kSigned>(v.y, c) << 8) |
+         (quantize_one<kSigned>(v.z, c) << 16) |
+         (quantize_one<kSigned>(v.w, c) << 24);
 }
 
 // params: {scale, zp as float}.  If zp8 is non-NULL the zero point is read
@@ -204,6 +256,7 @@ __global__ void __launch_bounds__(kDqlThreads)
     else
       zp_f = (float)*reinterpret_cast<const uint8_t *>(zp8);
   }
+  const QuantConsts qc = make_quant_consts(scale, zp_f);
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   const bool aligned = (((uintptr_t)x & 15u) == 0) && (((uintptr_t)y & 3u) == 0);
@@ -219,18 +272,18 @@ __global__ void __launch_bounds__(kDqlThreads)
       float4 b = __ldcs(x4 + i + nthreads);
       float4 c = __ldcs(x4 + i + 2 * nthreads);
       float4 d = __ldcs(x4 + i + 3 * nthreads);
-      y4[i] = quantize_four<kSigned>(a, scale, zp_f);
-      y4[i + nthreads] = quantize_four<kSigned>(b, scale, zp_f);
-      y4[i + 2 * nthreads] = quantize_four<kSigned>(c, scale, zp_f);
-      y4[i + 3 * nthreads] = quantize_four<kSigned>(d, scale, zp_f);
+      y4[i] = quantize_four<kSigned>(a, qc);
+      y4[i + nthreads] = quantize_four<kSigned>(b, qc);
+      y4[i + 2 * nthreads] = quantize_four<kSigned>(c, qc);
+      y4[i + 3 * nthreads] = quantize_four<kSigned>(d, qc);
     }
     for (; i < n4; i += nthreads)
-      y4[i] = quantize_four<kSigned>(__ldcs(x4 + i), scale, zp_f);
+      y4[i] = quantize_four<kSigned>(__ldcs(x4 + i), qc);
     for (int64_t j = (n4 << 2) + tid; j < n; j += nthreads)
-      y[j] = (uint8_t)quantize_one<kSigned>(x[j], scale, zp_f);
+      y[j] = (uint8_t)quantize_one<kSigned>(x[j], qc);
   } else {
     for (int64_t j = tid; j < n; j += nthreads)
-      y[j] = (uint8_t)quantize_one<kSigned>(x[j], scale, zp_f);
+      y[j] = (uint8_t)quantize_one<kSigned>(x[j], qc);
   }
 }
 

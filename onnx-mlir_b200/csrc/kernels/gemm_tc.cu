@@ -31,6 +31,8 @@
 // a non-zero word to *status, releases its tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "../runtime/internal.h"
 #include "gemm_epilogue.cuh"
 
@@ -185,6 +187,85 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
   return d;
 }
 
+
+// ---- thread-block-cluster helpers (2-CTA kernel) -------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Address of the same shared-memory location in another CTA of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrive on an mbarrier that may live in the peer CTA (cluster address).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
+                   cluster_addr)
+               : "memory");
+}
+
+// TMA load of one CTA of a pair; completion bytes go to the mbarrier at
+// cluster address `bar` (the leader CTA's).  Plain load: every CTA fetches
+// its own tile, nothing is multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst,
+    const CUtensorMap *map, int32_t x, int32_t y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_dst),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::
+                   : "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr),
+               "r"(ncols)
+               : "memory");
+}
+
+// One MMA over both CTAs of the pair: M = 256 (128 rows from each CTA's A
+// tile), N = BN (each CTA's shared memory holds half of the B tile), K = 32.
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc,
+    uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+               "}" ::"r"(d_tmem),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+// Arrives, once the MMAs issued so far have completed, on the mbarrier at this
+// shared-memory offset in every CTA whose bit is set in cta_mask.  (This is a
+// barrier signal, not a data load.)
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(bar),
+      "h"(cta_mask)
+      : "memory");
+}
+
 template <int BN>
 struct TcConfig {
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
@@ -331,6 +412,127 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
   }
 }
 
+// Drains one accumulator tile half (this warp's 32 TMEM lanes x kHalfCols
+// columns starting at taddr) through the epilogue into Y.
+//   m_warp   first output row of this warp's 32 rows
+//   n0       first output column of this warp's column range
+//   slab0    this warp's 4 KiB staging slab in shared memory
+template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_tile(const EpiParams &p,
+    const EpiScalars &sc, uint32_t taddr, int64_t m_warp, int64_t n0,
+    uint32_t slab0, int lane, bool use_slab, float &lo, float &hi) {
+  constexpr int kOutBytes = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
+  constexpr int kHalfCols = BN / 2;
+  constexpr int kSlabCols =
+      (128 / kOutBytes) < kHalfCols ? (128 / kOutBytes) : kHalfCols;
+  constexpr int kSlabsPerHalf = kHalfCols / kSlabCols;
+  static_assert(kHalfCols % 32 == 0 && kHalfCols % kSlabCols == 0, "tile shape");
+  const int64_t m = m_warp + lane;
+  const uint32_t my_row = slab0 + (uint32_t)lane * 128u;
+  const uint32_t swz = (uint32_t)(lane & 7);
+  const bool y4_ok = ((p.N & 3) == 0) && (((uintptr_t)p.Y & 15u) == 0);
+  const bool row_ok = m < p.M;
+  EpiRow row;
+  row.az = 0;
+  row.rs = 0;
+  if (row_ok)
+    row = epi_row(p, m);
+  if (use_slab) {
+    // Results pass through a swizzled shared-memory slab (32 rows x 128
+    // bytes per warp) so that the global stores are whole 128-byte lines:
+    // each thread writes its own row into the slab, then the warp reads
+    // the slab back eight 16-byte pieces per row and stores four full
+    // rows per instruction.
+#pragma unroll 1
+    for (int g = 0; g < kSlabsPerHalf; ++g) {
+      const int64_t ng = n0 + (int64_t)g * kSlabCols;
+#pragma unroll 1
+      for (int cc = 0; cc < kSlabCols; cc += 32) {
+        uint32_t v[32];
+        __syncwarp(); // tcgen05.ld is warp-collective: enter it converged
+        tmem_ld32(taddr + (uint32_t)(g * kSlabCols + cc), v);
+        tmem_ld_wait();
+        const int64_t nc = ng + cc;
+        const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
+        if (row_ok && valid > 0)
+          epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
+        if (kOutBytes == 4) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(my_row + (((uint32_t)j ^ swz) << 4), v[4 * j],
+                v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+          uint32_t w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            w[j] = v[4 * j] | (v[4 * j + 1] << 8) | (v[4 * j + 2] << 16) |
+                   (v[4 * j + 3] << 24);
+          const uint32_t c16 = (uint32_t)(cc >> 4);
+          st_shared_v4(my_row + (((c16) ^ swz) << 4), w[0], w[1], w[2], w[3]);
+          st_shared_v4(my_row + (((c16 + 1) ^ swz) << 4), w[4], w[5], w[6],
+              w[7]);
+        }
+      }
+      __syncwarp();
+      // Lane l serves 16-byte piece (l & 7) of rows (l >> 3) + 4*i.
+      const uint32_t piece = (uint32_t)(lane & 7);
+      const int64_t col_b = ng * kOutBytes + piece * 16; // byte column in Y
+      const bool col_ok = (col_b < p.N * kOutBytes) &&
+                          ((int)piece * 16 < kSlabCols * kOutBytes);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = 4 * i + (lane >> 3);
+        uint32_t q0, q1, q2, q3;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(q0), "=r"(q1), "=r"(q2), "=r"(q3)
+                     : "r"(slab0 + (uint32_t)r * 128u +
+                           ((piece ^ (uint32_t)(r & 7)) << 4)));
+        const int64_t mr = m_warp + r;
+        if (col_ok && mr < p.M)
+          *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.Y) +
+                                     mr * p.N * kOutBytes + col_b) =
+              make_uint4(q0, q1, q2, q3);
+      }
+      __syncwarp(); // slab is rewritten by the next group
+    }
+  } else {
+    // Fallback when the row pitch of Y is not a multiple of 16 bytes:
+    // direct stores, one row per thread.
+#pragma unroll 1
+    for (int c = 0; c < kHalfCols; c += 32) {
+      uint32_t v[32];
+      __syncwarp();
+      tmem_ld32(taddr + (uint32_t)c, v);
+      tmem_ld_wait();
+      const int64_t nc = n0 + c;
+      const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
+      if (!row_ok || valid <= 0)
+        continue;
+      epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
+      if (kOutBytes == 4) {
+        uint32_t *dst = reinterpret_cast<uint32_t *>(p.Y) + m * p.N + nc;
+        if (y4_ok && valid == 32) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            reinterpret_cast<uint4 *>(dst)[j] = make_uint4(
+                v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid)
+              dst[j] = v[j];
+        }
+      } else {
+        uint8_t *dst = reinterpret_cast<uint8_t *>(p.Y) + m * p.N + nc;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < valid)
+            dst[j] = (uint8_t)v[j];
+      }
+    }
+  }
+}
+
 } // namespace
 
 // ---- the kernel -------------------------------------------------------------------
@@ -342,14 +544,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         int *status) {
   using Cfg = TcConfig<BN>;
   constexpr int kStages = Cfg::kStages;
-  constexpr int kOutBytes = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
-  // Each of the two epilogue warps that share a TMEM lane quadrant takes one
-  // half of the tile's columns and walks it in slabs of up to 128 bytes per row.
-  constexpr int kHalfCols = BN / 2;
-  constexpr int kSlabCols =
-      (128 / kOutBytes) < kHalfCols ? (128 / kOutBytes) : kHalfCols;
-  constexpr int kSlabsPerHalf = kHalfCols / kSlabCols;
-  static_assert(kHalfCols % 32 == 0 && kHalfCols % kSlabCols == 0, "tile shape");
+  constexpr int kHalfCols = BN / 2; // columns per epilogue warp of a lane quadrant
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kStages];
@@ -466,18 +661,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int c_lo = (ew >> 2) * kHalfCols; // this warp's half of the columns
     const EpiScalars sc = epi_scalars(p);
     const bool use_slab = p.line_store != 0;
-    const bool y4_ok = ((p.N & 3) == 0) && (((uintptr_t)p.Y & 15u) == 0);
-    const bool y1_ok = ((p.N & 15) == 0) && (((uintptr_t)p.Y & 15u) == 0);
     const uint32_t slab0 = staging_base + (uint32_t)ew * Cfg::kSlabBytes;
-    const uint32_t my_row = slab0 + (uint32_t)lane * 128u;
-    const uint32_t swz = (uint32_t)(lane & 7);
     bool ok = true;
     int64_t it = 0;
     for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       const int buf = (int)(it & 1);
       const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
       const int64_t m_warp = (t / tiles_n) * kBM + quad * 32;
-      const int64_t m = m_warp + lane;
       const int64_t n0 = (t % tiles_n) * BN + c_lo;
       // While the MMAs of this tile are still running, pull the per-column
       // vectors this warp will need into L1.
@@ -501,110 +691,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tcgen05_fence_after();
-      const bool row_ok = m < p.M;
-      EpiRow row;
-      row.az = 0;
-      row.rs = 0;
-      if (row_ok)
-        row = epi_row(p, m);
       float lo = INFINITY, hi = -INFINITY;
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
-      if (use_slab) {
-        // Results pass through a swizzled shared-memory slab (32 rows x 128
-        // bytes per warp) so that the global stores are whole 128-byte lines:
-        // each thread writes its own row into the slab, then the warp reads
-        // the slab back eight 16-byte pieces per row and stores four full
-        // rows per instruction.
-#pragma unroll 1
-        for (int g = 0; g < kSlabsPerHalf; ++g) {
-          const int64_t ng = n0 + (int64_t)g * kSlabCols;
-#pragma unroll 1
-          for (int cc = 0; cc < kSlabCols; cc += 32) {
-            uint32_t v[32];
-            __syncwarp(); // tcgen05.ld is warp-collective: enter it converged
-            tmem_ld32(taddr + (uint32_t)(g * kSlabCols + cc), v);
-            tmem_ld_wait();
-            const int64_t nc = ng + cc;
-            const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
-            if (row_ok && valid > 0)
-              epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
-            if (kOutBytes == 4) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                st_shared_v4(my_row + (((uint32_t)j ^ swz) << 4), v[4 * j],
-                    v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            } else {
-              uint32_t w[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                w[j] = v[4 * j] | (v[4 * j + 1] << 8) | (v[4 * j + 2] << 16) |
-                       (v[4 * j + 3] << 24);
-              const uint32_t c16 = (uint32_t)(cc >> 4);
-              st_shared_v4(my_row + (((c16) ^ swz) << 4), w[0], w[1], w[2], w[3]);
-              st_shared_v4(my_row + (((c16 + 1) ^ swz) << 4), w[4], w[5], w[6],
-                  w[7]);
-            }
-          }
-          __syncwarp();
-          // Lane l serves 16-byte piece (l & 7) of rows (l >> 3) + 4*i.
-          const uint32_t piece = (uint32_t)(lane & 7);
-          const int64_t col_b = ng * kOutBytes + piece * 16; // byte column in Y
-          const bool col_ok = (col_b < p.N * kOutBytes) &&
-                              ((int)piece * 16 < kSlabCols * kOutBytes);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = 4 * i + (lane >> 3);
-            uint32_t q0, q1, q2, q3;
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(q0), "=r"(q1), "=r"(q2), "=r"(q3)
-                         : "r"(slab0 + (uint32_t)r * 128u +
-                               ((piece ^ (uint32_t)(r & 7)) << 4)));
-            const int64_t mr = m_warp + r;
-            if (col_ok && mr < p.M)
-              *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.Y) +
-                                         mr * p.N * kOutBytes + col_b) =
-                  make_uint4(q0, q1, q2, q3);
-          }
-          __syncwarp(); // slab is rewritten by the next group
-        }
-      } else {
-        // Fallback when the row pitch of Y is not a multiple of 16 bytes:
-        // direct stores, one row per thread.
-#pragma unroll 1
-        for (int c = 0; c < kHalfCols; c += 32) {
-          uint32_t v[32];
-          __syncwarp();
-          tmem_ld32(taddr + (uint32_t)c, v);
-          tmem_ld_wait();
-          const int64_t nc = n0 + c;
-          const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
-          if (!row_ok || valid <= 0)
-            continue;
-          epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
-          if (kOutBytes == 4) {
-            uint32_t *dst = reinterpret_cast<uint32_t *>(p.Y) + m * p.N + nc;
-            if (y4_ok && valid == 32) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                reinterpret_cast<uint4 *>(dst)[j] = make_uint4(
-                    v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < valid)
-                  dst[j] = v[j];
-            }
-          } else {
-            uint8_t *dst = reinterpret_cast<uint8_t *>(p.Y) + m * p.N + nc;
-            (void)y1_ok;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < valid)
-                dst[j] = (uint8_t)v[j];
-          }
-        }
-      }
+      epilogue_tile<BN, EPI>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi);
       // The accumulator buffer may be overwritten once all eight warps are done.
       tcgen05_fence_before();
       __syncwarp();
@@ -621,6 +711,208 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && abort_flag)
+    atomicExch(status, 1);
+}
+
+
+// ---- the 2-CTA kernel ----------------------------------------------------------------
+//
+// Same pipeline on a cluster of two CTAs (two SMs) that share one 256 x 256
+// output tile: CTA r owns rows [128 r, 128 r + 128) of it.  Each CTA loads its
+// own 128-row A tile but only half of the B tile (128 of the 256 columns);
+// tcgen05.mma.cta_group::2 reads both halves.  Per SM that is 32 KiB of
+// operands per 128-byte K step instead of 48 KiB, which matters because the
+// single-CTA kernel is limited by how fast an SM can take operands in, not by
+// the tensor pipe.  Only the leader CTA (rank 0) issues MMAs:
+//   full[s]       (leader)  one arrive + 64 KiB of TMA bytes from both CTAs
+//   empty[s]      (each)    tcgen05.commit to both CTAs when the MMAs are done
+//   acc_full[b]   (each)    tcgen05.commit to both CTAs after the last K step
+//   acc_empty[b]  (leader)  16 arrives: the 8 epilogue warps of both CTAs
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap map_a,
+        const __grid_constant__ CUtensorMap map_b, EpiParams p, uint32_t idesc,
+        int *status) {
+  constexpr int BN = 256;
+  constexpr int kStages = 6;
+  constexpr int kABytes = kBM * kBK;
+  constexpr int kBHalfBytes = (BN / 2) * kBK;
+  constexpr int kStageBytes = kABytes + kBHalfBytes; // 32 KiB per CTA
+  constexpr int kTmemCols = 2 * BN;
+  constexpr int kSlabBytes = 32 * 128;
+  constexpr int kHalfCols = BN / 2;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[kStages];
+  __shared__ uint64_t bar_empty[kStages];
+  __shared__ uint64_t bar_acc_full[2];
+  __shared__ uint64_t bar_acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint64_t t0 = global_timer();
+  const uint32_t rank = cluster_ctarank(); // 0 = leader
+  const int64_t cluster_id = blockIdx.x >> 1;
+  const int64_t num_clusters = gridDim.x >> 1;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t staging_base = smem_base + kStages * kStageBytes;
+
+  const int64_t tiles_m = ceil_div(p.M, 2 * kBM);
+  const int64_t tiles_n = ceil_div(p.N, BN);
+  const int64_t num_tiles = tiles_m * tiles_n;
+  const int num_kb = (int)ceil_div(p.K, kBK);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_acc_full[b]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[b]), 16);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1)
+    tmem_alloc_pair(smem_u32(&tmem_base_slot), kTmemCols);
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all(); // both CTAs' barriers exist before anyone signals them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int *abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        const int32_t m0 = (int32_t)((t / tiles_n) * (2 * kBM) + rank * kBM);
+        const int32_t n0 = (int32_t)((t % tiles_n) * BN + rank * (BN / 2));
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, t0)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = mapa_shared(smem_u32(&bar_full[stage]), 0);
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+          if (rank == 0)
+            mbar_expect_tx(smem_u32(&bar_full[stage]), 2 * kStageBytes);
+          tma_load_2d_pair(sa, &map_a, kb * kBK, m0, full_leader);
+          tma_load_2d_pair(sb, &map_b, kb * kBK, n0, full_leader);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int64_t it = 0;
+      for (int64_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+        const int buf = (int)(it & 1);
+        const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
+        if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp, t0)) {
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, t0)) {
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            const uint64_t adesc = make_smem_desc(sa + kk * kUmmaK);
+            const uint64_t bdesc = make_smem_desc(sb + kk * kUmmaK);
+            umma_i8_pair(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok)
+          umma_commit_pair(smem_u32(&bar_acc_full[buf]), 3);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..9 of both CTAs) ----------------
+    const int quad = warp & 3;
+    const int ew = warp - 2;
+    const int c_lo = (ew >> 2) * kHalfCols;
+    const EpiScalars sc = epi_scalars(p);
+    const bool use_slab = p.line_store != 0;
+    const uint32_t slab0 = staging_base + (uint32_t)ew * kSlabBytes;
+    bool ok = true;
+    int64_t it = 0;
+    for (int64_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+      const int buf = (int)(it & 1);
+      const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
+      const int64_t m_warp = (t / tiles_n) * (2 * kBM) + rank * kBM + quad * 32;
+      const int64_t n0 = (t % tiles_n) * BN + c_lo;
+      {
+        const int line = lane & 7, which = lane >> 3;
+        const int64_t nl = n0 + 32 * line;
+        const void *src = nullptr;
+        if (32 * line < kHalfCols && nl < p.N) {
+          if (which == 0 && p.a_zp_len != 0)
+            src = p.colsum + nl;
+          else if (which == 1 && p.bias)
+            src = p.bias + nl;
+          else if (which == 2 && p.sb && p.sb_len != 1)
+            src = p.sb + nl;
+        }
+        if (src)
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
+      }
+      if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase, abortp, t0)) {
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after();
+      float lo = INFINITY, hi = -INFINITY;
+      const uint32_t taddr =
+          tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
+      epilogue_tile<BN, EPI>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi);
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[buf]), 0));
+      if (p.out_range && EPI == OMCUDA_EPI_DEQUANT)
+        epi_range_commit(p.out_range, lo, hi);
+    }
+  }
+
+  // ---------------- teardown ----------------
+  // Neither CTA may leave (or free tensor memory) while its peer can still
+  // signal its barriers or read its shared memory.
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && abort_flag)
     atomicExch(status, 1);
@@ -741,6 +1033,82 @@ int launch_bn(const omcudaGemmArgs &a, cudaStream_t st) {
   }
 }
 
+
+// The 2-CTA kernel: 256 x 256 tiles on clusters of two CTAs.
+constexpr int kPairStages = 6;
+constexpr int kPairSmemBytes =
+    kPairStages * (kBM * kBK + 128 * kBK) + 8 * 32 * 128 + 1024;
+
+template <int EPI>
+int launch_pair_epi(const omcudaGemmArgs &a, cudaStream_t st) {
+  static int max_clusters = 0;
+  if (max_clusters == 0) {
+    OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc2_kernel<EPI>,
+        cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3((unsigned)sm_count() & ~1u, 1, 1);
+    q.blockDim = dim3(kThreads, 1, 1);
+    q.dynamicSmemBytes = kPairSmemBytes;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 2;
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = 1;
+    q.attrs = qa;
+    q.numAttrs = 1;
+    int n = 0;
+    OMCUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_i8_tc2_kernel<EPI>, &q));
+    max_clusters = n > 0 ? n : 1;
+  }
+  CUtensorMap map_a, map_b;
+  int rc = make_map(&map_a, a.A, a.M, a.K, a.K, kBM);
+  if (rc != OMCUDA_OK)
+    return rc;
+  rc = make_map(&map_b, a.B.bt, a.N, a.B.kp, a.B.kp, 128);
+  if (rc != OMCUDA_OK)
+    return rc;
+  EpiParams p = make_epi_params(a);
+  const int esize = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
+  p.line_store = (((uintptr_t)a.Y & 15u) == 0) && ((a.N * esize) % 16 == 0);
+  int *status = status_word();
+  if (!status)
+    return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
+  int64_t tiles = ceil_div(a.M, 2 * kBM) * ceil_div(a.N, 256);
+  int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
+  // M = 256 across the pair (field holds M / 16), N = 256.
+  uint32_t idesc = make_idesc(a.a_signed, a.B.b_signed, 256);
+  idesc = (idesc & ~(0x1fu << 24)) | ((uint32_t)(256 >> 4) << 24);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  OMCUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_i8_tc2_kernel<EPI>, map_a, map_b, p,
+      idesc, status));
+  count_launch();
+  return OMCUDA_OK;
+}
+
+int launch_pair(const omcudaGemmArgs &a, cudaStream_t st) {
+  switch (a.epilogue) {
+  case OMCUDA_EPI_I32:
+    return launch_pair_epi<OMCUDA_EPI_I32>(a, st);
+  case OMCUDA_EPI_DEQUANT:
+    return launch_pair_epi<OMCUDA_EPI_DEQUANT>(a, st);
+  case OMCUDA_EPI_REQUANT:
+    return launch_pair_epi<OMCUDA_EPI_REQUANT>(a, st);
+  default:
+    return fail(OMCUDA_EINVAL, "GemmI8: unknown epilogue %d", a.epilogue);
+  }
+}
+
 } // namespace
 
 bool gemm_tc_supported(const omcudaGemmArgs &a) {
@@ -750,9 +1118,26 @@ bool gemm_tc_supported(const omcudaGemmArgs &a) {
 }
 
 int launch_gemm_tc(const omcudaGemmArgs &a, cudaStream_t st) {
-  // Tile width: the widest tile that still gives every SM work.
+  // Tile width: the widest tile that still gives every SM work
+  // (OMCUDA_GEMM_BN=64|128|256 overrides the choice, 512 selects the 2-CTA
+  // kernel, for experiments).
+  static const int forced_bn = [] {
+    const char *s = getenv("OMCUDA_GEMM_BN");
+    return s ? atoi(s) : 0;
+  }();
+  if (forced_bn == 512)
+    return launch_pair(a, st);
+  if (forced_bn == 256)
+    return launch_bn<256>(a, st);
+  if (forced_bn == 128)
+    return launch_bn<128>(a, st);
+  if (forced_bn == 64)
+    return launch_bn<64>(a, st);
   const int64_t tm = ceil_div(a.M, kBM);
   const int sms = sm_count();
+  // Enough 256 x 256 tiles to occupy every pair of SMs: the 2-CTA kernel.
+  if (a.N > 128 && ceil_div(a.M, 2 * kBM) * ceil_div(a.N, 256) >= sms / 2)
+    return launch_pair(a, st);
   if (a.N > 128 && tm * ceil_div(a.N, 256) >= sms)
     return launch_bn<256>(a, st);
   if (a.N > 64 && tm * ceil_div(a.N, 128) >= sms / 2)

@@ -61,6 +61,23 @@ def test_exact_ties(gpu, orc):
     check_dql(gpu, orc, x)
 
 
+def test_values_crowded_around_ties(gpu, orc):
+    # The kernel avoids the divide on its common path and falls back to the
+    # exact divide near a rounding tie: crowd the input around ties, at every
+    # magnitude of the quantized range and at offsets from far below to far
+    # above the fallback threshold.
+    rng = np.random.default_rng(9)
+    for lo, hi in ((-3.7, 5.1), (-1000.0, 0.3), (-1e-3, 2e-3), (0.0, 7.77)):
+        scale = np.float32((np.float32(hi) - np.float32(lo)) / np.float32(255))
+        k = rng.integers(-300, 300, size=400000).astype(np.float32)
+        off = rng.choice([0.0, 1e-7, -1e-7, 3e-6, -3e-6, 1e-4, -1e-4, 9e-4, -9e-4,
+                          2e-3, -2e-3, 0.25], size=k.size).astype(np.float32)
+        x = ((k + np.float32(0.5) + off) * scale).astype(np.float32)
+        x = np.clip(x, np.float32(lo), np.float32(hi))
+        x[0], x[1] = np.float32(lo), np.float32(hi)      # pins the range
+        check_dql(gpu, orc, x)
+
+
 def test_larger_than_l2(gpu, orc):
     # 48 Mi floats = 192 MiB > the 126 MB L2: the quantize pass re-reads HBM.
     x = np.random.default_rng(5).normal(size=48 * 1024 * 1024).astype(np.float32)
