@@ -31,6 +31,7 @@
 // a non-zero word to *status, releases its tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdio>
 #include <cstdlib>
 
 #include "../runtime/internal.h"
@@ -43,7 +44,24 @@ namespace {
 constexpr int kBM = 128;       // rows of A per tile
 constexpr int kBK = 128;       // bytes (= int8 elements) of K per stage
 constexpr int kUmmaK = 32;     // K of one tcgen05.mma kind::i8
-constexpr int kThreads = 320;  // 10 warps: producer, MMA, 8 epilogue
+// The kernels are built with 8 or 16 epilogue warps (EW).  Sixteen hide the
+// epilogue's latency better, which decides shapes with a short K loop; eight
+// leave shared memory for a deeper operand pipeline, which decides long K.
+// Columns of a tile that one epilogue warp drains: the EW/4 warps that may
+// read a TMEM lane quadrant split the tile's columns, 32 columns at least.
+__host__ __device__ constexpr int epi_cols_per_warp(int bn, int ew) {
+  return bn / (ew / 4) >= 32 ? bn / (ew / 4) : 32;
+}
+__host__ __device__ constexpr int epi_active_warps(int bn, int ew) {
+  return 4 * (bn / epi_cols_per_warp(bn, ew));
+}
+__host__ __device__ constexpr int tc_threads(int ew) { return 32 * (2 + ew); }
+constexpr int kSmemBudget = 232448 - 1024 - 512; // per CTA, minus slack and barriers
+__host__ __device__ constexpr int tc_stages(int stage_bytes, int ew) {
+  return (kSmemBudget - ew * 4096) / stage_bytes < 8
+             ? (kSmemBudget - ew * 4096) / stage_bytes
+             : 8;
+}
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // ---- PTX wrappers -------------------------------------------------------------
@@ -266,16 +284,16 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
       : "memory");
 }
 
-template <int BN>
+template <int BN, int EW>
 struct TcConfig {
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kABytes = kBM * kBK;
   static constexpr int kBBytes = BN * kBK;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = tc_stages(kStageBytes, EW);
   static constexpr int kTmemCols = 2 * BN; // two accumulator buffers
   // Output staging: per epilogue warp one slab of 32 rows x 128 bytes.
   static constexpr int kSlabBytes = 32 * 128;
-  static constexpr int kStagingBytes = 8 * kSlabBytes;
+  static constexpr int kStagingBytes = EW * kSlabBytes;
   static constexpr int kSmemBytes =
       kStages * kStageBytes + kStagingBytes + 1024; // + alignment slack
 };
@@ -318,27 +336,33 @@ template <int EPI>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
     const EpiScalars &sc, const EpiRow &row, int64_t nc, int valid,
     uint32_t (&v)[32], float &lo, float &hi) {
-  if (p.b_zp_len != 0) {
-    // General zero-point form: per-element path.
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < valid) {
-        int32_t a = epi_int(p, row, (int32_t)v[j], nc + j);
-        if (EPI == OMCUDA_EPI_I32) {
-          v[j] = (uint32_t)a;
-        } else if (EPI == OMCUDA_EPI_DEQUANT) {
-          float y = epi_dequant(p, sc, a, nc + j);
-          lo = fminf(lo, y);
-          hi = fmaxf(hi, y);
-          v[j] = __float_as_uint(y);
-        } else {
-          v[j] = epi_requant(p, sc, a, nc + j);
-        }
-      }
-    }
-    return;
-  }
   const bool vec = p.vec_ok != 0;
+  if (p.b_zp_len != 0) {
+    // - bz[n] * rowsum[m] + K * az * bz[n]  =  bz[n] * (K * az - rowsum[m])
+    const uint32_t tr = (uint32_t)p.K * (uint32_t)row.az - (uint32_t)row.rs;
+    if (p.b_zp_len == 1) {
+      const uint32_t bz = (uint32_t)load_zp8(p.b_zp, 0, p.b_signed);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        v[j] += bz * tr;
+    } else if (vec && valid == 32 && (((uintptr_t)p.b_zp + (uintptr_t)nc) & 15u) == 0) {
+      const uint4 *src = reinterpret_cast<const uint4 *>(
+          reinterpret_cast<const uint8_t *>(p.b_zp) + nc);
+      const uint4 q0 = __ldg(src), q1 = __ldg(src + 1);
+      const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t byte = (w[j >> 2] >> (8 * (j & 3))) & 0xffu;
+        const uint32_t bz = p.b_signed ? (uint32_t)(int32_t)(int8_t)byte : byte;
+        v[j] += bz * tr;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < valid)
+          v[j] += (uint32_t)load_zp8(p.b_zp, nc + j, p.b_signed) * tr;
+    }
+  }
   if (p.a_zp_len != 0) {
     int32_t cs[32];
     load_cols32(p.colsum, nc, valid, vec, cs);
@@ -417,12 +441,12 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
 //   m_warp   first output row of this warp's 32 rows
 //   n0       first output column of this warp's column range
 //   slab0    this warp's 4 KiB staging slab in shared memory
-template <int BN, int EPI>
+template <int BN, int EPI, int EW>
 __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
     const EpiScalars &sc, uint32_t taddr, int64_t m_warp, int64_t n0,
     uint32_t slab0, int lane, bool use_slab, float &lo, float &hi) {
   constexpr int kOutBytes = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
-  constexpr int kHalfCols = BN / 2;
+  constexpr int kHalfCols = epi_cols_per_warp(BN, EW);
   constexpr int kSlabCols =
       (128 / kOutBytes) < kHalfCols ? (128 / kOutBytes) : kHalfCols;
   constexpr int kSlabsPerHalf = kHalfCols / kSlabCols;
@@ -537,14 +561,14 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
 
 // ---- the kernel -------------------------------------------------------------------
 
-template <int BN, int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int EPI, int EW>
+__global__ void __launch_bounds__(tc_threads(EW), 1)
     gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a,
         const __grid_constant__ CUtensorMap map_b, EpiParams p, uint32_t idesc,
         int *status) {
-  using Cfg = TcConfig<BN>;
+  using Cfg = TcConfig<BN, EW>;
   constexpr int kStages = Cfg::kStages;
-  constexpr int kHalfCols = BN / 2; // columns per epilogue warp of a lane quadrant
+  constexpr int kHalfCols = epi_cols_per_warp(BN, EW); // columns per epilogue warp of a lane quadrant
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kStages];
@@ -575,7 +599,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_acc_full[b]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[b]), 8); // one arrive per epilogue warp
+      mbar_init(smem_u32(&bar_acc_empty[b]), epi_active_warps(BN, EW)); // one arrive per active epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -658,11 +682,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---------------- epilogue (warps 2..9) ----------------
     const int quad = warp & 3;       // TMEM lanes [32*quad, 32*quad+32)
     const int ew = warp - 2;         // 0..7
-    const int c_lo = (ew >> 2) * kHalfCols; // this warp's half of the columns
+    const int c_lo = (ew >> 2) * kHalfCols; // this warp's share of the columns
+    const bool active = c_lo < BN;          // narrow tiles leave some warps idle
     const EpiScalars sc = epi_scalars(p);
     const bool use_slab = p.line_store != 0;
     const uint32_t slab0 = staging_base + (uint32_t)ew * Cfg::kSlabBytes;
-    bool ok = true;
+    bool ok = active;
     int64_t it = 0;
     for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       const int buf = (int)(it & 1);
@@ -694,7 +719,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       float lo = INFINITY, hi = -INFINITY;
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
-      epilogue_tile<BN, EPI>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi);
+      epilogue_tile<BN, EPI, EW>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi);
       // The accumulator buffer may be overwritten once all eight warps are done.
       tcgen05_fence_before();
       __syncwarp();
@@ -730,19 +755,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 //   empty[s]      (each)    tcgen05.commit to both CTAs when the MMAs are done
 //   acc_full[b]   (each)    tcgen05.commit to both CTAs after the last K step
 //   acc_empty[b]  (leader)  16 arrives: the 8 epilogue warps of both CTAs
-template <int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int EPI, int EW>
+__global__ void __launch_bounds__(tc_threads(EW), 1)
     gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap map_a,
         const __grid_constant__ CUtensorMap map_b, EpiParams p, uint32_t idesc,
         int *status) {
   constexpr int BN = 256;
-  constexpr int kStages = 6;
   constexpr int kABytes = kBM * kBK;
   constexpr int kBHalfBytes = (BN / 2) * kBK;
   constexpr int kStageBytes = kABytes + kBHalfBytes; // 32 KiB per CTA
+  constexpr int kStages = tc_stages(kStageBytes, EW);
   constexpr int kTmemCols = 2 * BN;
   constexpr int kSlabBytes = 32 * 128;
-  constexpr int kHalfCols = BN / 2;
+  constexpr int kHalfCols = epi_cols_per_warp(BN, EW);
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[kStages];
@@ -775,7 +800,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_acc_full[b]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[b]), 16);
+      mbar_init(smem_u32(&bar_acc_empty[b]), 2 * epi_active_warps(BN, EW));
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -861,10 +886,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int quad = warp & 3;
     const int ew = warp - 2;
     const int c_lo = (ew >> 2) * kHalfCols;
+    const bool active = c_lo < BN;
     const EpiScalars sc = epi_scalars(p);
     const bool use_slab = p.line_store != 0;
     const uint32_t slab0 = staging_base + (uint32_t)ew * kSlabBytes;
-    bool ok = true;
+    bool ok = active;
     int64_t it = 0;
     for (int64_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
       const int buf = (int)(it & 1);
@@ -894,7 +920,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       float lo = INFINITY, hi = -INFINITY;
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
-      epilogue_tile<BN, EPI>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi);
+      epilogue_tile<BN, EPI, EW>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0)
@@ -987,12 +1013,12 @@ int *status_word() {
   return g_status_word;
 }
 
-template <int BN, int EPI>
-int launch_bn_epi(const omcudaGemmArgs &a, cudaStream_t st) {
-  using Cfg = TcConfig<BN>;
+template <int BN, int EPI, int EW>
+int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
+  using Cfg = TcConfig<BN, EW>;
   static bool attr_set = false;
   if (!attr_set) {
-    OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, EPI>,
+    OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, EPI, EW>,
         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_set = true;
   }
@@ -1013,10 +1039,20 @@ int launch_bn_epi(const omcudaGemmArgs &a, cudaStream_t st) {
   int64_t tiles = ceil_div(a.M, kBM) * ceil_div(a.N, BN);
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   uint32_t idesc = make_idesc(a.a_signed, a.B.b_signed, BN);
-  gemm_i8_tc_kernel<BN, EPI><<<grid, kThreads, Cfg::kSmemBytes, st>>>(
+  gemm_i8_tc_kernel<BN, EPI, EW><<<grid, tc_threads(EW), Cfg::kSmemBytes, st>>>(
       map_a, map_b, p, idesc, status);
   OMCUDA_CHECK_LAUNCH("gemm_i8_tc_kernel");
   return OMCUDA_OK;
+}
+
+// A long K loop hides the epilogue behind the MMAs and wants pipeline depth;
+// a short one is bounded by the epilogue and wants more warps on it.
+inline bool want_wide_epilogue(const omcudaGemmArgs &a) { return a.K < 2048; }
+
+template <int BN, int EPI>
+int launch_bn_epi(const omcudaGemmArgs &a, cudaStream_t st) {
+  return want_wide_epilogue(a) ? launch_bn_epi_ew<BN, EPI, 16>(a, st)
+                               : launch_bn_epi_ew<BN, EPI, 8>(a, st);
 }
 
 template <int BN>
@@ -1035,15 +1071,15 @@ int launch_bn(const omcudaGemmArgs &a, cudaStream_t st) {
 
 
 // The 2-CTA kernel: 256 x 256 tiles on clusters of two CTAs.
-constexpr int kPairStages = 6;
-constexpr int kPairSmemBytes =
-    kPairStages * (kBM * kBK + 128 * kBK) + 8 * 32 * 128 + 1024;
-
-template <int EPI>
-int launch_pair_epi(const omcudaGemmArgs &a, cudaStream_t st) {
+template <int EPI, int EW>
+int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
+  constexpr int kThreads = tc_threads(EW);
+  constexpr int kPairSmemBytes =
+      tc_stages(kBM * kBK + 128 * kBK, EW) * (kBM * kBK + 128 * kBK) +
+      EW * 32 * 128 + 1024;
   static int max_clusters = 0;
   if (max_clusters == 0) {
-    OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc2_kernel<EPI>,
+    OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc2_kernel<EPI, EW>,
         cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
     cudaLaunchConfig_t q = {};
     q.gridDim = dim3((unsigned)sm_count() & ~1u, 1, 1);
@@ -1057,7 +1093,7 @@ int launch_pair_epi(const omcudaGemmArgs &a, cudaStream_t st) {
     q.attrs = qa;
     q.numAttrs = 1;
     int n = 0;
-    OMCUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_i8_tc2_kernel<EPI>, &q));
+    OMCUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_i8_tc2_kernel<EPI, EW>, &q));
     max_clusters = n > 0 ? n : 1;
   }
   CUtensorMap map_a, map_b;
@@ -1090,10 +1126,16 @@ int launch_pair_epi(const omcudaGemmArgs &a, cudaStream_t st) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  OMCUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_i8_tc2_kernel<EPI>, map_a, map_b, p,
+  OMCUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_i8_tc2_kernel<EPI, EW>, map_a, map_b, p,
       idesc, status));
   count_launch();
   return OMCUDA_OK;
+}
+
+template <int EPI>
+int launch_pair_epi(const omcudaGemmArgs &a, cudaStream_t st) {
+  return want_wide_epilogue(a) ? launch_pair_epi_ew<EPI, 16>(a, st)
+                               : launch_pair_epi_ew<EPI, 8>(a, st);
 }
 
 int launch_pair(const omcudaGemmArgs &a, cudaStream_t st) {
