@@ -53,21 +53,20 @@ __global__ void __launch_bounds__(kDqlThreads)
   if (aligned) {
     const int64_t n4 = n >> 2;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    // Four independent 16-byte loads in flight per thread per trip.
+    // Eight independent 16-byte loads in flight per thread per trip: with all
+    // 2048 threads of an SM resident that is 256 KiB outstanding per SM, well
+    // above what HBM latency times bandwidth asks for.
     int64_t i = tid;
-    for (; i + 3 * nthreads < n4; i += 4 * nthreads) {
-      float4 a = __ldcs(x4 + i);
-      float4 b = __ldcs(x4 + i + nthreads);
-      float4 c = __ldcs(x4 + i + 2 * nthreads);
-      float4 d = __ldcs(x4 + i + 3 * nthreads);
-      lo = fminf(lo, fminf(fminf(a.x, a.y), fminf(a.z, a.w)));
-      hi = fmaxf(hi, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
-      lo = fminf(lo, fminf(fminf(b.x, b.y), fminf(b.z, b.w)));
-      hi = fmaxf(hi, fmaxf(fmaxf(b.x, b.y), fmaxf(b.z, b.w)));
-      lo = fminf(lo, fminf(fminf(c.x, c.y), fminf(c.z, c.w)));
-      hi = fmaxf(hi, fmaxf(fmaxf(c.x, c.y), fmaxf(c.z, c.w)));
-      lo = fminf(lo, fminf(fminf(d.x, d.y), fminf(d.z, d.w)));
-      hi = fmaxf(hi, fmaxf(fmaxf(d.x, d.y), fmaxf(d.z, d.w)));
+    for (; i + 7 * nthreads < n4; i += 8 * nthreads) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        v[u] = __ldcs(x4 + i + u * nthreads);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        lo = fminf(lo, fminf(fminf(v[u].x, v[u].y), fminf(v[u].z, v[u].w)));
+        hi = fmaxf(hi, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+      }
     }
     for (; i < n4; i += nthreads) {
       float4 a = __ldcs(x4 + i);
@@ -210,8 +209,9 @@ __device__ __forceinline__ QuantConsts make_quant_consts(float scale, float zp_f
 //  * round half even by adding and subtracting 1.5 * 2^23 (exact for
 //    |q'| <= 2^22).  Unless q' lies within 1e-3 of a tie, q and q' round to the
 //    same integer; the rare near-tie element is redone with the exact divide.
-//  * after the clip the value is an integer in the output range, so its low
-//    eight bits can be read off the mantissa of (value + 1.5 * 2^23).
+//  * the zero point is added and the clip applied while the value still
+//    carries the 1.5 * 2^23 offset (all quantities are integers below 2^24,
+//    so nothing rounds), and the result is the low byte of the mantissa.
 // NaN quotients come out of the clamp as -512 and end at the lower clip
 // bound, which is where maxnum/minnum send a NaN in the reference as well.
 template <bool kSigned>
@@ -219,13 +219,18 @@ __device__ __forceinline__ uint32_t quantize_one(float x, const QuantConsts &c) 
   if (!c.fast)
     return quantize_one_exact<kSigned>(x, c.scale, c.zp_f);
   const float kMagic = 12582912.0f; // 1.5 * 2^23
-  float q = fminf(fmaxf(__fmul_rn(x, c.rcp), -512.0f), 512.0f);
-  float r = __fsub_rn(__fadd_rn(q, kMagic), kMagic);
-  if (fabsf(__fsub_rn(q, r)) > 0.499f)
-    r = round_even(__fdiv_rn(x, c.scale));
-  float a = __fadd_rn(r, c.zp_f);
-  float s = kSigned ? clipf(a, -128.0f, 127.0f) : clipf(a, 0.0f, 255.0f);
-  return __float_as_uint(__fadd_rn(s, kMagic)) & 0xffu;
+  const float q = fminf(fmaxf(__fmul_rn(x, c.rcp), -512.0f), 512.0f);
+  float t = __fadd_rn(q, kMagic);          // rounds q half-even into the mantissa
+  const float r = __fsub_rn(t, kMagic);    // = rint(q), exact
+  if (fabsf(__fsub_rn(q, r)) > 0.499f)     // near a tie: redo with the real divide
+    t = __fadd_rn(round_even(__fdiv_rn(x, c.scale)), kMagic);
+  // t, the zero point and the clip bounds are integers below 2^24 here, so the
+  // add and the clip are exact in the shifted domain and the low byte of the
+  // mantissa is the result (two's complement for the signed type).
+  const float u = __fadd_rn(t, c.zp_f);
+  const float s = kSigned ? clipf(u, kMagic - 128.0f, kMagic + 127.0f)
+                          : clipf(u, kMagic, kMagic + 255.0f);
+  return __float_as_uint(s) & 0xffu;
 }
 
 template <bool kSigned>

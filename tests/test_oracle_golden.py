@@ -157,3 +157,14 @@ def test_fp32_ops_against_numpy(orc):
     p /= p.sum(-1, keepdims=True)
     want = (p @ vh).transpose(0, 2, 1, 3).reshape(2, 7, 8)
     assert np.allclose(out, want, rtol=1e-5, atol=1e-6)
+
+
+# ---- vectors from executing the reference's expected Krnl IR ------------------------
+
+import lit_ir_cases  # noqa: E402
+
+
+@pytest.mark.parametrize("case", lit_ir_cases.CASES, ids=lit_ir_cases.case_id)
+def test_oracle_matches_executed_lit_ir(orc, case):
+    got, want = lit_ir_cases.run_case(case, lit_ir_cases.OracleBackend(orc))
+    lit_ir_cases.assert_same(got, want)
