@@ -231,7 +231,12 @@ int omcudaDevPrepareB(const void *B, int b_signed, int64_t K, int64_t N,
 typedef enum {
   OMCUDA_EPI_I32 = 0,     /* MatMulInteger: i32 out */
   OMCUDA_EPI_DEQUANT = 1, /* Cast f32, Mul scale(s), Add bias [, Gelu] */
-  OMCUDA_EPI_REQUANT = 2  /* QLinearMatMul: scale, round, +zp, wrap to 8 bit */
+  OMCUDA_EPI_REQUANT = 2, /* QLinearMatMul: scale, round, +zp, wrap to 8 bit */
+  /* The DEQUANT value x (without Gelu) stored as two bf16 planes instead of
+   * f32: Y holds hi = bf16(x) as [M,N] bf16, followed by lo = bf16(x - hi) as
+   * [M,N] bf16 (2*M*N*2 bytes in all): the operand format of
+   * omcudaDevAttentionBf16.  Tensor-core kernel only. */
+  OMCUDA_EPI_DEQUANT_SPLIT = 3
 } omcudaEpilogue;
 
 typedef struct {
@@ -302,6 +307,24 @@ int omcudaDevAttention(const float *Q, const float *K, const float *V,
 int omcudaDevAttentionEx(const float *Q, const float *K, const float *V,
     int64_t B, int64_t S, int64_t heads, int64_t dh, float scale, float *out,
     int64_t ld_in, int64_t ld_out, void *out_range, void *stream);
+
+/* The same attention on the tcgen05 tensor cores, for head size 64 and a
+ * sequence length that is a multiple of 128, over operands already split into
+ * two bf16 planes: hi = bf16(a), lo = bf16(a - hi), each [B*S, ld_planes]
+ * row-major; head h of Q / K / V owns columns [q_col + 64 h, ...), [k_col + 64 h,
+ * ...), [v_col + 64 h, ...) of its row.  omcudaDevSplitBf16 makes the planes
+ * from an fp32 matrix (columns [col0, col0 + cols) of the planes); the QKV
+ * projection's GEMM can write them directly (OMCUDA_EPI_DEQUANT_SPLIT).
+ * These are the two fp32 MatMuls, the Mul and the Softmax of the graph
+ * (Math/MatMul.cpp:488-507, Math/Softmax.cpp:25-134) in one kernel. */
+int omcudaDevSplitBf16(const float *x, int64_t rows, int64_t cols, int64_t ld_x,
+    void *hi, void *lo, int64_t ld_planes, int64_t col0, void *stream);
+int omcudaDevAttentionBf16Supported(int64_t B, int64_t S, int64_t heads,
+    int64_t dh, int64_t ld_planes, int64_t ld_out);
+int omcudaDevAttentionBf16(const void *hi, const void *lo, int64_t ld_planes,
+    int64_t q_col, int64_t k_col, int64_t v_col, int64_t B, int64_t S,
+    int64_t heads, int64_t dh, float scale, float *out, int64_t ld_out,
+    void *out_range, void *stream);
 
 /* Running {min,max} ranges: 8 bytes each, kept by producer kernels (GEMM
  * dequant epilogue, LayerNorm, attention) with integer atomics so that the

@@ -34,6 +34,7 @@ SOURCES = [
     "kernels/gemm_tc.cu",
     "kernels/encoder_ops.cu",
     "kernels/attention_mma.cu",
+    "kernels/attention_tc.cu",
 ]
 
 NVCC_FLAGS = [

@@ -46,9 +46,14 @@ int64_t dtype_bytes(OM_DATA_TYPE t) {
   case ONNX_TYPE_UINT8:
   case ONNX_TYPE_INT8:
     return 1;
+  case ONNX_TYPE_UINT16: // raw bf16 planes of the attention operands
+  case ONNX_TYPE_BFLOAT16:
+    return 2;
   case ONNX_TYPE_FLOAT:
   case ONNX_TYPE_INT32:
     return 4;
+  case ONNX_TYPE_INT64:
+    return 8;
   default:
     return 0;
   }
@@ -952,9 +957,29 @@ void omcudaAttention(OMTensor *y, const OMTensor *q, const OMTensor *k,
   float *dy = (float *)sg.out(y);
   if (!sg.ok())
     return;
-  sg.set(omcudaDevAttention(
-      dq, dk, dv, s[0], s[1], heads, s[2] / heads, (float)scale, dy, st));
-  sg.finish(false);
+  const int64_t B = s[0], S = s[1], H = s[2], dh = H / heads, T = B * S;
+  if (omcudaDevAttentionBf16Supported(B, S, heads, dh, 3 * H, H) &&
+      ((((uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv | (uintptr_t)dy) & 15u) == 0)) {
+    // Tensor-core path: split the operands into bf16 hi/lo planes [T, 3H]
+    // (Q | K | V side by side, the layout the fused QKV projection writes).
+    const size_t plane = (size_t)T * 3 * H * 2;
+    uint8_t *planes = (uint8_t *)sg.scratch(2 * plane);
+    if (planes) {
+      void *hi = planes, *lo = planes + plane;
+      int rc = omcudaDevSplitBf16(dq, T, H, H, hi, lo, 3 * H, 0, st);
+      if (rc == OMCUDA_OK)
+        rc = omcudaDevSplitBf16(dk, T, H, H, hi, lo, 3 * H, H, st);
+      if (rc == OMCUDA_OK)
+        rc = omcudaDevSplitBf16(dv, T, H, H, hi, lo, 3 * H, 2 * H, st);
+      if (rc == OMCUDA_OK)
+        rc = omcudaDevAttentionBf16(hi, lo, 3 * H, 0, H, 2 * H, B, S, heads, dh,
+            (float)scale, dy, H, nullptr, st);
+      sg.set(rc);
+    }
+  } else {
+    sg.set(omcudaDevAttention(dq, dk, dv, B, S, heads, dh, (float)scale, dy, st));
+  }
+  sg.finish(true);
 }
 
 } // extern "C"

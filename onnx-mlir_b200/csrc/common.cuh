@@ -94,6 +94,25 @@ __device__ __forceinline__ float ordered_to_f32(uint32_t u) {
   return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
 }
 
+// Folds a warp's {min,max} into a running range (two ordered uints).  The
+// range only ever widens, so a plain (possibly stale) read that already covers
+// the warp's values makes the atomic unnecessary; after the first few warps of
+// a launch almost none is issued, which matters because they all target one
+// address.  lo > hi (nothing but NaNs seen) commits nothing.
+__device__ __forceinline__ void range_commit_warp(
+    uint32_t *range, float lo, float hi) {
+  lo = warp_min(lo);
+  hi = warp_max(hi);
+  if ((threadIdx.x & 31) == 0 && lo <= hi) {
+    const uint32_t ol = f32_to_ordered(lo), oh = f32_to_ordered(hi);
+    volatile uint32_t *vr = range;
+    if (ol < vr[0])
+      atomicMin(range, ol);
+    if (oh > vr[1])
+      atomicMax(range + 1, oh);
+  }
+}
+
 #endif // __CUDACC__
 
 } // namespace omcuda

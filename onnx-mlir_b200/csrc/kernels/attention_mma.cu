@@ -270,14 +270,8 @@ __global__ void __launch_bounds__(128)
       hi = fmaxf(hi, fmaxf(v.x, v.y));
     }
   }
-  if (out_range) {
-    lo = warp_min(lo);
-    hi = warp_max(hi);
-    if (lane == 0 && lo <= hi) {
-      atomicMin(out_range, f32_to_ordered(lo));
-      atomicMax(out_range + 1, f32_to_ordered(hi));
-    }
-  }
+  if (out_range)
+    range_commit_warp(out_range, lo, hi);
 }
 
 } // namespace

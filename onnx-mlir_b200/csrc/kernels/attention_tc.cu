@@ -1,0 +1,462 @@
+// Attention on the Blackwell tensor cores (tcgen05.mma kind::f16, bf16
+// operands, fp32 accumulators in tensor memory) for the encoder graphs:
+// softmax(Q K^T * scale) V per (batch, head), head size 64, sequence length a
+// multiple of 128.
+//
+// It stands for the chain the reference lowers with CPU loops: two batched
+// fp32 MatMuls (src/Conversion/ONNXToKrnl/Math/MatMul.cpp:488-507), a Mul by a
+// constant and a Softmax over the last axis
+// (src/Conversion/ONNXToKrnl/Math/Softmax.cpp:25-134).
+//
+// Accuracy.  Every fp32 operand a arrives already split as a = hi + lo with
+// hi = bf16(a), lo = bf16(a - hi) (two bf16 planes, written by the QKV GEMM's
+// epilogue or by split_bf16_kernel below), and each product is evaluated as
+// lo*hi + hi*lo + hi*hi, which leaves a relative error of about 2^-16 per
+// product, far inside the 1e-3 tolerance of the fp32 ops; accumulation is
+// fp32.  The softmax runs online over key blocks (running maximum and sum),
+// the same function as the reference's three-loop form up to fp32 rounding.
+//
+// Layout in HBM: the planes are [T, ld] bf16 row-major (T = batch*seq tokens);
+// head h of Q / K / V owns columns [col + 64 h, col + 64 h + 64) of its rows.
+// out is [T, ld_out] fp32.
+//
+// One CTA = 128 query rows of one (batch, head); two CTAs share an SM so that
+// one's softmax (CUDA cores) overlaps the other's matrix products (tensor
+// pipe).  Per block of 128 keys:
+//   thread 0   waits for the K tiles (TMA, 128-byte swizzle), issues
+//              S = Q K^T as 12 MMAs (3 split terms x 4 k-steps) into tensor
+//              memory, commits to an mbarrier, refills the K buffers;
+//   4 warps    each thread owns one query row (its TMEM lane): row maximum,
+//              p = 2^(s*c - m), running sum, p split into bf16 hi/lo and
+//              stored back over the scores in tensor memory;
+//   thread 0   issues O_j = P V as 24 MMAs with P read from tensor memory and
+//              V (keys x 64, MN-major) from shared memory; refills V;
+//   4 warps    o = o * 2^(m_old - m_new) + O_j in registers.
+// Every wait on an mbarrier is bounded (tc_ptx.cuh); a timeout raises the
+// CTA's abort flag, the CTA frees its tensor memory, writes the status word
+// and returns.
+#include <cuda_bf16.h>
+
+#include <cstdlib>
+#include <cstring>
+
+#include "../common.cuh"
+#include "../runtime/internal.h"
+#include "tc_ptx.cuh"
+
+namespace omcuda {
+
+namespace {
+
+constexpr int kTQ = 128;            // query rows per CTA
+constexpr int kTK = 128;            // keys per block
+constexpr int kTDh = 64;            // head size
+constexpr int kTile = 128 * 128;    // bytes of one 128-row x 64-bf16 tile
+constexpr int kTcAttSmem = 6 * kTile + 1024;
+constexpr uint32_t kTmemColsAtt = 256; // S/P: 0..127, O_j: 128..191
+
+// D = A * B (+ D) with A from shared memory.
+__device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t adesc,
+    uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+               "}" ::"r"(d_tmem),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+// D = A * B (+ D) with A (128 rows x 16 bf16 = 8 columns) from tensor memory.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem,
+    uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+               "}" ::"r"(d_tmem),
+               "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(
+          taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]),
+      "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]),
+      "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// {hi(b), hi(a)} as packed bf16 (a in the low half), round to nearest even.
+__device__ __forceinline__ uint32_t cvt_bf16x2(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16 with bf16 operands and an
+// fp32 accumulator, M = 128; b_mn_major selects an MN-major (transposed) B.
+__host__ __device__ constexpr uint32_t att_idesc(int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(128, 2)
+    attention_tc_kernel(const __grid_constant__ CUtensorMap map_hi,
+        const __grid_constant__ CUtensorMap map_lo, int32_t q_col, int32_t k_col,
+        int32_t v_col, int64_t S, int64_t heads, float scale_log2e,
+        float *__restrict__ out, int64_t ld_out, uint32_t *__restrict__ out_range,
+        int *status) {
+  extern __shared__ uint8_t att_tc_smem[];
+  __shared__ uint64_t bar_q, bar_k, bar_v, bar_s, bar_o;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint64_t t0 = global_timer();
+  const int64_t bh = blockIdx.y;
+  const int64_t b = bh / heads, h = bh % heads;
+  const int32_t row_q = (int32_t)(b * S + (int64_t)blockIdx.x * kTQ);
+  const int32_t row_kv = (int32_t)(b * S);
+  const int32_t cq = q_col + (int32_t)h * kTDh, ck = k_col + (int32_t)h * kTDh,
+                cv = v_col + (int32_t)h * kTDh;
+  const int nkb = (int)(S / kTK);
+
+  const uint32_t smem0 = (smem_u32(att_tc_smem) + 1023u) & ~1023u;
+  const uint32_t s_qh = smem0, s_ql = smem0 + kTile, s_kh = smem0 + 2 * kTile,
+                 s_kl = smem0 + 3 * kTile, s_vh = smem0 + 4 * kTile,
+                 s_vl = smem0 + 5 * kTile;
+
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar_q), 1);
+    mbar_init(smem_u32(&bar_k), 1);
+    mbar_init(smem_u32(&bar_v), 1);
+    mbar_init(smem_u32(&bar_s), 1);
+    mbar_init(smem_u32(&bar_o), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0)
+    tmem_alloc(smem_u32(&tmem_slot), kTmemColsAtt);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t t_s = tmem;          // scores, then P, columns 0..127
+  const uint32_t t_o = tmem + 128u;   // P V of the current key block
+  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  volatile int *abortp = &abort_flag;
+
+  if (tid == 0) {
+    mbar_expect_tx(smem_u32(&bar_q), 2 * kTile);
+    tma_load_2d(s_qh, &map_hi, cq, row_q, smem_u32(&bar_q));
+    tma_load_2d(s_ql, &map_lo, cq, row_q, smem_u32(&bar_q));
+    mbar_expect_tx(smem_u32(&bar_k), 2 * kTile);
+    tma_load_2d(s_kh, &map_hi, ck, row_kv, smem_u32(&bar_k));
+    tma_load_2d(s_kl, &map_lo, ck, row_kv, smem_u32(&bar_k));
+    mbar_expect_tx(smem_u32(&bar_v), 2 * kTile);
+    tma_load_2d(s_vh, &map_hi, cv, row_kv, smem_u32(&bar_v));
+    tma_load_2d(s_vl, &map_lo, cv, row_kv, smem_u32(&bar_v));
+  }
+
+  constexpr uint32_t kIdescQK = att_idesc(kTK, 0);
+  constexpr uint32_t kIdescPV = att_idesc(kTDh, 1);
+
+  float o[kTDh];
+#pragma unroll
+  for (int i = 0; i < kTDh; ++i)
+    o[i] = 0.0f;
+  float m_run = -INFINITY; // running maximum of s * scale * log2(e)
+  float l_run = 0.0f;      // running sum of p
+  bool ok = true;
+
+  for (int j = 0; j < nkb; ++j) {
+    const uint32_t ph = (uint32_t)(j & 1);
+    // ---- S = Q K_j^T ----
+    if (tid == 0) {
+      if (j == 0)
+        ok = mbar_wait(smem_u32(&bar_q), 0, abortp, t0);
+      ok = ok && mbar_wait(smem_u32(&bar_k), ph, abortp, t0);
+      if (ok) {
+        tcgen05_fence_after();
+        // small terms first: Ql Kh, Qh Kl, then Qh Kh
+        const uint32_t qa[3] = {s_ql, s_qh, s_qh};
+        const uint32_t kb[3] = {s_kh, s_kl, s_kh};
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+#pragma unroll
+          for (int kk = 0; kk < kTDh / 16; ++kk)
+            umma_bf16_ss(t_s, make_smem_desc(qa[t] + kk * 32),
+                make_smem_desc(kb[t] + kk * 32), kIdescQK, (t | kk) != 0 ? 1u : 0u);
+        umma_commit(smem_u32(&bar_s));
+        ok = mbar_wait(smem_u32(&bar_s), ph, abortp, t0);
+        if (ok && j + 1 < nkb) { // the K buffers are free again
+          mbar_expect_tx(smem_u32(&bar_k), 2 * kTile);
+          tma_load_2d(s_kh, &map_hi, ck, row_kv + (j + 1) * kTK, smem_u32(&bar_k));
+          tma_load_2d(s_kl, &map_lo, ck, row_kv + (j + 1) * kTK, smem_u32(&bar_k));
+        }
+      }
+    }
+    ok = __syncthreads_and(ok) != 0;
+    if (!ok)
+      break;
+    tcgen05_fence_after();
+
+    // ---- online softmax of this thread's row ----
+    __syncwarp(); // tcgen05.ld / st are warp-collective: enter them converged
+    float mx = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < kTK; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(t_s + lane_base + (uint32_t)c, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        mx = fmaxf(mx, __uint_as_float(v[i]));
+    }
+    const float m_new = fmaxf(m_run, __fmul_rn(mx, scale_log2e));
+    const float resc = ex2_approx(__fsub_rn(m_run, m_new)); // 0 on the first block
+    m_run = m_new;
+    const float neg_m = -m_new;
+    float psum = 0.0f;
+#pragma unroll 1
+    for (int c = 0; c < kTK; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(t_s + lane_base + (uint32_t)c, v);
+      tmem_ld_wait();
+      uint32_t whi[16], wlo[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float p0 =
+            ex2_approx(__fmaf_rn(__uint_as_float(v[2 * i]), scale_log2e, neg_m));
+        const float p1 = ex2_approx(
+            __fmaf_rn(__uint_as_float(v[2 * i + 1]), scale_log2e, neg_m));
+        psum = __fadd_rn(psum, __fadd_rn(p0, p1));
+        const uint32_t hi = cvt_bf16x2(p0, p1);
+        const float r0 = __fsub_rn(p0, __uint_as_float(hi << 16));
+        const float r1 = __fsub_rn(p1, __uint_as_float(hi & 0xffff0000u));
+        whi[i] = hi;
+        wlo[i] = cvt_bf16x2(r0, r1);
+      }
+      // P of keys c..c+31: hi in columns c..c+15, lo in c+16..c+31 (the
+      // scores of those columns are already consumed).
+      tmem_st16(t_s + lane_base + (uint32_t)c, whi);
+      tmem_st16(t_s + lane_base + (uint32_t)c + 16u, wlo);
+    }
+    l_run = __fadd_rn(__fmul_rn(l_run, resc), psum);
+    tmem_st_wait();
+    tcgen05_fence_before();
+    __syncthreads(); // every row of P is in tensor memory
+
+    // ---- O_j = P V_j ----
+    if (tid == 0) {
+      tcgen05_fence_after();
+      ok = mbar_wait(smem_u32(&bar_v), ph, abortp, t0);
+      if (ok) {
+        tcgen05_fence_after();
+        // small terms first: Pl Vh, Ph Vl, then Ph Vh
+        const uint32_t pa[3] = {16u, 0u, 0u}; // column offset of lo / hi inside a chunk
+        const uint32_t vb[3] = {s_vh, s_vl, s_vh};
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+#pragma unroll
+          for (int kk = 0; kk < kTK / 16; ++kk) {
+            const uint32_t a_col = (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8) + pa[t];
+            umma_bf16_ts(t_o, t_s + a_col, make_smem_desc(vb[t] + kk * 2048),
+                kIdescPV, (t | kk) != 0 ? 1u : 0u);
+          }
+        umma_commit(smem_u32(&bar_o));
+        ok = mbar_wait(smem_u32(&bar_o), ph, abortp, t0);
+        if (ok && j + 1 < nkb) { // the V buffers are free again
+          mbar_expect_tx(smem_u32(&bar_v), 2 * kTile);
+          tma_load_2d(s_vh, &map_hi, cv, row_kv + (j + 1) * kTK, smem_u32(&bar_v));
+          tma_load_2d(s_vl, &map_lo, cv, row_kv + (j + 1) * kTK, smem_u32(&bar_v));
+        }
+      }
+    }
+    ok = __syncthreads_and(ok) != 0;
+    if (!ok)
+      break;
+    tcgen05_fence_after();
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < kTDh; c += 32) {
+      uint32_t v[32];
+      tmem_ld32(t_o + lane_base + (uint32_t)c, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        o[c + i] = __fmaf_rn(o[c + i], resc, __uint_as_float(v[i]));
+    }
+    tcgen05_fence_before();
+  }
+
+  if (ok) {
+    // Normalise, store this thread's row, fold it into the running range.
+    const float inv = __fdiv_rn(1.0f, l_run);
+    float *dst = out + ((int64_t)row_q + tid) * ld_out + h * kTDh;
+    float lo = INFINITY, hi = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kTDh; i += 4) {
+      float4 v = make_float4(__fmul_rn(o[i], inv), __fmul_rn(o[i + 1], inv),
+          __fmul_rn(o[i + 2], inv), __fmul_rn(o[i + 3], inv));
+      *reinterpret_cast<float4 *>(dst + i) = v;
+      lo = fminf(lo, fminf(fminf(v.x, v.y), fminf(v.z, v.w)));
+      hi = fmaxf(hi, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+    }
+    if (out_range)
+      range_commit_warp(out_range, lo, hi);
+  }
+
+  // ---- teardown ----
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tcgen05_fence_after();
+    tmem_dealloc(tmem, kTmemColsAtt);
+  }
+  if (tid == 0 && abort_flag)
+    atomicExch(status, 1);
+}
+
+// x [rows, cols] fp32 with row pitch ld_x -> bf16 planes hi, lo [rows, ld_p]
+// at column offset col0: hi = bf16(x), lo = bf16(x - hi).
+__global__ void __launch_bounds__(256)
+    split_bf16_kernel(const float *__restrict__ x, int64_t rows, int64_t cols,
+        int64_t ld_x, __nv_bfloat16 *__restrict__ hi, __nv_bfloat16 *__restrict__ lo,
+        int64_t ld_p, int64_t col0) {
+  const int64_t c4n = cols >> 2;
+  const int64_t total = rows * c4n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / c4n, c = (i % c4n) * 4;
+    const float4 v = *reinterpret_cast<const float4 *>(x + r * ld_x + c);
+    const uint32_t h0 = cvt_bf16x2(v.x, v.y), h1 = cvt_bf16x2(v.z, v.w);
+    const uint32_t l0 = cvt_bf16x2(__fsub_rn(v.x, __uint_as_float(h0 << 16)),
+        __fsub_rn(v.y, __uint_as_float(h0 & 0xffff0000u)));
+    const uint32_t l1 = cvt_bf16x2(__fsub_rn(v.z, __uint_as_float(h1 << 16)),
+        __fsub_rn(v.w, __uint_as_float(h1 & 0xffff0000u)));
+    *reinterpret_cast<uint2 *>(hi + r * ld_p + col0 + c) = make_uint2(h0, h1);
+    *reinterpret_cast<uint2 *>(lo + r * ld_p + col0 + c) = make_uint2(l0, l1);
+  }
+}
+
+} // namespace
+
+bool attention_tc_supported(int64_t B, int64_t S, int64_t heads, int64_t dh,
+    int64_t ld_planes, int64_t ld_out, const void *hi, const void *lo,
+    const float *out) {
+  // OMCUDA_ATTENTION=mma|simt keeps the older kernels, to cross-check them.
+  static const bool disabled = [] {
+    const char *s = getenv("OMCUDA_ATTENTION");
+    return s && (strcmp(s, "mma") == 0 || strcmp(s, "simt") == 0);
+  }();
+  if (disabled)
+    return false;
+  return dh == kTDh && S > 0 && S % kTK == 0 && B * heads <= 65535 &&
+         B * S < (int64_t(1) << 31) && ld_planes % 8 == 0 && ld_out % 4 == 0 &&
+         ((((uintptr_t)hi | (uintptr_t)lo | (uintptr_t)out) & 15u) == 0);
+}
+
+int launch_attention_tc(const void *hi, const void *lo, int64_t ld_planes,
+    int64_t q_col, int64_t k_col, int64_t v_col, int64_t B, int64_t S,
+    int64_t heads, float scale, float *out, int64_t ld_out, void *out_range,
+    cudaStream_t st) {
+  if ((q_col | k_col | v_col) % 8 != 0)
+    return fail(OMCUDA_EINVAL, "Attention: column offsets must be multiples of 8");
+  static bool attr_set = false;
+  if (!attr_set) {
+    OMCUDA_CHECK(cudaFuncSetAttribute(attention_tc_kernel,
+        cudaFuncAttributeMaxDynamicSharedMemorySize, kTcAttSmem));
+    attr_set = true;
+  }
+  const int64_t T = B * S;
+  CUtensorMap map_hi, map_lo;
+  int rc = make_tma_map_2d(&map_hi, hi, T, ld_planes, ld_planes * 2, kTDh, kTK, 2);
+  if (rc != OMCUDA_OK)
+    return rc;
+  rc = make_tma_map_2d(&map_lo, lo, T, ld_planes, ld_planes * 2, kTDh, kTK, 2);
+  if (rc != OMCUDA_OK)
+    return rc;
+  int *status = tc_status_word();
+  if (!status)
+    return fail(OMCUDA_ENOMEM, "Attention: cannot allocate the status word");
+  dim3 grid((unsigned)(S / kTQ), (unsigned)(B * heads));
+  const float scale_log2e = scale * 1.4426950408889634f;
+  attention_tc_kernel<<<grid, 128, kTcAttSmem, st>>>(map_hi, map_lo, (int32_t)q_col,
+      (int32_t)k_col, (int32_t)v_col, S, heads, scale_log2e, out, ld_out,
+      (uint32_t *)out_range, status);
+  OMCUDA_CHECK_LAUNCH("attention_tc_kernel");
+  return OMCUDA_OK;
+}
+
+int launch_split_bf16(const float *x, int64_t rows, int64_t cols, int64_t ld_x,
+    void *hi, void *lo, int64_t ld_p, int64_t col0, cudaStream_t st) {
+  if (cols % 4 != 0 || ld_x % 4 != 0 || ld_p % 4 != 0 || col0 % 4 != 0 ||
+      (((uintptr_t)x & 15u) != 0) || ((((uintptr_t)hi | (uintptr_t)lo) & 7u) != 0))
+    return fail(OMCUDA_EINVAL, "SplitBf16: rows must be 16-byte aligned");
+  const int64_t total = rows * (cols >> 2);
+  if (total == 0)
+    return OMCUDA_OK;
+  int64_t want = ceil_div(total, 256 * 4);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  split_bf16_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, st>>>(x, rows,
+      cols, ld_x, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, ld_p, col0);
+  OMCUDA_CHECK_LAUNCH("split_bf16_kernel");
+  return OMCUDA_OK;
+}
+
+} // namespace omcuda
+
+using namespace omcuda;
+
+extern "C" int omcudaDevSplitBf16(const float *x, int64_t rows, int64_t cols,
+    int64_t ld_x, void *hi, void *lo, int64_t ld_planes, int64_t col0,
+    void *stream) {
+  if (rows < 0 || cols < 0 || ld_x < cols || ld_planes < col0 + cols ||
+      (rows > 0 && cols > 0 && (!x || !hi || !lo)))
+    return fail(OMCUDA_EINVAL, "SplitBf16: bad argument");
+  return launch_split_bf16(x, rows, cols, ld_x, hi, lo, ld_planes, col0,
+      (cudaStream_t)stream);
+}
+
+extern "C" int omcudaDevAttentionBf16Supported(int64_t B, int64_t S,
+    int64_t heads, int64_t dh, int64_t ld_planes, int64_t ld_out) {
+  return attention_tc_supported(B, S, heads, dh, ld_planes, ld_out, nullptr,
+             nullptr, nullptr)
+             ? 1
+             : 0;
+}
+
+extern "C" int omcudaDevAttentionBf16(const void *hi, const void *lo,
+    int64_t ld_planes, int64_t q_col, int64_t k_col, int64_t v_col, int64_t B,
+    int64_t S, int64_t heads, int64_t dh, float scale, float *out,
+    int64_t ld_out, void *out_range, void *stream) {
+  if (B < 0 || S <= 0 || heads <= 0 || !hi || !lo || !out || q_col < 0 ||
+      k_col < 0 || v_col < 0 || ld_out < heads * dh ||
+      ld_planes < heads * dh + (q_col > k_col ? (q_col > v_col ? q_col : v_col)
+                                               : (k_col > v_col ? k_col : v_col)))
+    return fail(OMCUDA_EINVAL, "AttentionBf16: bad argument");
+  if (B == 0)
+    return OMCUDA_OK;
+  if (!attention_tc_supported(B, S, heads, dh, ld_planes, ld_out, hi, lo, out))
+    return fail(OMCUDA_ENOTSUP,
+        "AttentionBf16: needs head size 64, a sequence length that is a "
+        "multiple of 128 and 16-byte aligned rows");
+  return launch_attention_tc(hi, lo, ld_planes, q_col, k_col, v_col, B, S, heads,
+      scale, out, ld_out, out_range, (cudaStream_t)stream);
+}

@@ -20,6 +20,7 @@ namespace omcuda {
 
 static constexpr int kDqlThreads = 256;
 static constexpr int kDqlMaxBlocks = 2048;
+static constexpr int kQuantUnroll = 8;
 
 struct DqlScratch {
   unsigned int ticket;
@@ -203,30 +204,33 @@ __device__ __forceinline__ QuantConsts make_quant_consts(float scale, float zp_f
 // Same result as quantize_one_exact with no divide or convert instruction on
 // the common path (those run on the quarter-rate special-function pipe and
 // would bound the kernel instead of HBM):
-//  * q' = x * RN(1/scale) is within 2.5 ulp of the IEEE quotient q.  Values
-//    with |q| > 512 saturate whatever their rounding, so q' is clamped to
-//    [-512, 512], where 2.5 ulp < 2e-4.
-//  * round half even by adding and subtracting 1.5 * 2^23 (exact for
-//    |q'| <= 2^22).  Unless q' lies within 1e-3 of a tie, q and q' round to the
-//    same integer; the rare near-tie element is redone with the exact divide.
+//  * t = fma(x, RN(1/scale), 1.5 * 2^23) rounds the product half-even to an
+//    integer held in the mantissa (exact while |product| < 2^22); r = t - 1.5 *
+//    2^23 is that integer and d = fma(x, RN(1/scale), -r) the exact distance
+//    of the product from it.
+//  * x * RN(1/scale) is within 2.5 ulp of the IEEE quotient q = x / scale.
+//    Where |q| <= 512 that is below 2e-4, so unless |d| > 0.499 (the product
+//    lies within 1e-3 of a tie) q rounds to the same integer r; the rare
+//    near-tie element is redone with the exact divide.  Where |q| > 512 the
+//    result saturates whatever the rounding (zero point and bounds lie in
+//    [-128, 255]), and |d| <= 0.499 still holds or the exact path runs.
 //  * the zero point is added and the clip applied while the value still
-//    carries the 1.5 * 2^23 offset (all quantities are integers below 2^24,
-//    so nothing rounds), and the result is the low byte of the mantissa.
-// NaN quotients come out of the clamp as -512 and end at the lower clip
-// bound, which is where maxnum/minnum send a NaN in the reference as well.
+//    carries the 1.5 * 2^23 offset (integers below 2^24, or large values that
+//    the clip cuts off either way), and the result is the low byte of the
+//    mantissa (two's complement for the signed type).
+// +-inf saturate through the clip; a NaN product fails the |d| test, passes
+// through fmaxf as the lower clip bound, which is where maxnum/minnum send a
+// NaN in the reference as well.
 template <bool kSigned>
 __device__ __forceinline__ uint32_t quantize_one(float x, const QuantConsts &c) {
   if (!c.fast)
     return quantize_one_exact<kSigned>(x, c.scale, c.zp_f);
   const float kMagic = 12582912.0f; // 1.5 * 2^23
-  const float q = fminf(fmaxf(__fmul_rn(x, c.rcp), -512.0f), 512.0f);
-  float t = __fadd_rn(q, kMagic);          // rounds q half-even into the mantissa
-  const float r = __fsub_rn(t, kMagic);    // = rint(q), exact
-  if (fabsf(__fsub_rn(q, r)) > 0.499f)     // near a tie: redo with the real divide
+  float t = __fmaf_rn(x, c.rcp, kMagic);
+  const float r = __fsub_rn(t, kMagic);
+  const float d = __fmaf_rn(x, c.rcp, -r);
+  if (fabsf(d) > 0.499f) // near a tie, or too large for the mantissa trick
     t = __fadd_rn(round_even(__fdiv_rn(x, c.scale)), kMagic);
-  // t, the zero point and the clip bounds are integers below 2^24 here, so the
-  // add and the clip are exact in the shifted domain and the low byte of the
-  // mantissa is the result (two's complement for the signed type).
   const float u = __fadd_rn(t, c.zp_f);
   const float s = kSigned ? clipf(u, kMagic - 128.0f, kMagic + 127.0f)
                           : clipf(u, kMagic, kMagic + 255.0f);
@@ -270,17 +274,16 @@ __global__ void __launch_bounds__(kDqlThreads)
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     uint32_t *y4 = reinterpret_cast<uint32_t *>(y);
     int64_t i = tid;
-    // Four float4 loads in flight per thread; each is a fully coalesced
-    // 512-byte warp access, each store a 128-byte one.
-    for (; i + 3 * nthreads < n4; i += 4 * nthreads) {
-      float4 a = __ldcs(x4 + i);
-      float4 b = __ldcs(x4 + i + nthreads);
-      float4 c = __ldcs(x4 + i + 2 * nthreads);
-      float4 d = __ldcs(x4 + i + 3 * nthreads);
-      y4[i] = quantize_four<kSigned>(a, qc);
-      y4[i + nthreads] = quantize_four<kSigned>(b, qc);
-      y4[i + 2 * nthreads] = quantize_four<kSigned>(c, qc);
-      y4[i + 3 * nthreads] = quantize_four<kSigned>(d, qc);
+    // kQuantUnroll float4 loads in flight per thread; each is a fully
+    // coalesced 512-byte warp access, each store a 128-byte one.
+    for (; i + (kQuantUnroll - 1) * nthreads < n4; i += kQuantUnroll * nthreads) {
+      float4 v[kQuantUnroll];
+#pragma unroll
+      for (int u = 0; u < kQuantUnroll; ++u)
+        v[u] = __ldcs(x4 + i + u * nthreads);
+#pragma unroll
+      for (int u = 0; u < kQuantUnroll; ++u)
+        __stcs(y4 + i + u * nthreads, quantize_four<kSigned>(v[u], qc));
     }
     for (; i < n4; i += nthreads)
       y4[i] = quantize_four<kSigned>(__ldcs(x4 + i), qc);

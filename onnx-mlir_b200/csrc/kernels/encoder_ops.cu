@@ -83,14 +83,79 @@ __global__ void __launch_bounds__(256)
       hi = fmaxf(hi, o);
     }
   }
-  if (out_range) {
-    lo = warp_min(lo);
-    hi = warp_max(hi);
-    if (lane == 0 && lo <= hi) {
-      atomicMin(out_range, f32_to_ordered(lo));
-      atomicMax(out_range + 1, f32_to_ordered(hi));
+  if (out_range)
+    range_commit_warp(out_range, lo, hi);
+}
+
+// Same function for rows of NV * 128 floats (hidden sizes 768 and 1024): one
+// warp per row, the row held in registers as NV float4 per lane, so x and the
+// residual are read from HBM exactly once, with 16-byte accesses.
+template <int NV>
+__global__ void __launch_bounds__(256)
+    layernorm_rows_vec_kernel(const float *__restrict__ x,
+        const float *__restrict__ residual, int64_t rows,
+        const float *__restrict__ gamma, const float *__restrict__ beta,
+        float eps, float *__restrict__ y, uint32_t *__restrict__ out_range) {
+  constexpr int64_t cols = (int64_t)NV * 128;
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  float lo = INFINITY, hi = -INFINITY;
+  if (r < rows) {
+    const float4 *xr = reinterpret_cast<const float4 *>(x + r * cols);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      v[i] = __ldcs(xr + lane + 32 * i);
+    if (residual) {
+      const float4 *rr = reinterpret_cast<const float4 *>(residual + r * cols);
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const float4 q = __ldcs(rr + lane + 32 * i);
+        v[i].x = __fadd_rn(v[i].x, q.x);
+        v[i].y = __fadd_rn(v[i].y, q.y);
+        v[i].z = __fadd_rn(v[i].z, q.z);
+        v[i].w = __fadd_rn(v[i].w, q.w);
+      }
+    }
+    float s = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      s2 += (__fmul_rn(v[i].x, v[i].x) + __fmul_rn(v[i].y, v[i].y)) +
+            (__fmul_rn(v[i].z, v[i].z) + __fmul_rn(v[i].w, v[i].w));
+    }
+    s = warp_sum(s);
+    s2 = warp_sum(s2);
+    const float nf = (float)cols;
+    const float mean = __fdiv_rn(s, nf);
+    const float mean2 = __fdiv_rn(s2, nf);
+    const float var = __fsub_rn(mean2, __fmul_rn(mean, mean));
+    const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+    const float4 *g4 = reinterpret_cast<const float4 *>(gamma);
+    const float4 *b4 = reinterpret_cast<const float4 *>(beta);
+    float4 *yr = reinterpret_cast<float4 *>(y + r * cols);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const float4 g = __ldg(g4 + lane + 32 * i);
+      float4 o;
+      o.x = __fmul_rn(__fmul_rn(__fsub_rn(v[i].x, mean), inv), g.x);
+      o.y = __fmul_rn(__fmul_rn(__fsub_rn(v[i].y, mean), inv), g.y);
+      o.z = __fmul_rn(__fmul_rn(__fsub_rn(v[i].z, mean), inv), g.z);
+      o.w = __fmul_rn(__fmul_rn(__fsub_rn(v[i].w, mean), inv), g.w);
+      if (beta) {
+        const float4 bb = __ldg(b4 + lane + 32 * i);
+        o.x = __fadd_rn(o.x, bb.x);
+        o.y = __fadd_rn(o.y, bb.y);
+        o.z = __fadd_rn(o.z, bb.z);
+        o.w = __fadd_rn(o.w, bb.w);
+      }
+      yr[lane + 32 * i] = o;
+      lo = fminf(lo, fminf(fminf(o.x, o.y), fminf(o.z, o.w)));
+      hi = fmaxf(hi, fmaxf(fmaxf(o.x, o.y), fmaxf(o.z, o.w)));
     }
   }
+  if (out_range)
+    range_commit_warp(out_range, lo, hi);
 }
 
 // ---- elementwise -------------------------------------------------------------------
@@ -331,14 +396,8 @@ __global__ void __launch_bounds__(kAttWarps * 32)
       }
     }
   }
-  if (out_range) {
-    lo = warp_min(lo);
-    hi = warp_max(hi);
-    if (lane == 0 && lo <= hi) {
-      atomicMin(out_range, f32_to_ordered(lo));
-      atomicMax(out_range + 1, f32_to_ordered(hi));
-    }
-  }
+  if (out_range)
+    range_commit_warp(out_range, lo, hi);
 }
 
 // Arms running {min,max} ranges (ordered-uint encoding): min side all ones,
@@ -382,9 +441,20 @@ extern "C" int omcudaDevLayerNorm(const float *x, const float *residual,
     return fail(OMCUDA_EINVAL, "LayerNormalization: bad argument");
   if (rows == 0)
     return OMCUDA_OK;
-  layernorm_rows_kernel<<<(unsigned)ceil_div(rows, 8), 256, 0,
-      (cudaStream_t)stream>>>(x, residual, rows, cols, gamma, beta, eps, y,
-      reinterpret_cast<uint32_t *>(out_minmax));
+  const bool vec_ok = ((((uintptr_t)x | (uintptr_t)residual | (uintptr_t)gamma |
+                            (uintptr_t)beta | (uintptr_t)y) & 15u) == 0);
+  const unsigned grid = (unsigned)ceil_div(rows, 8);
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t *rng = reinterpret_cast<uint32_t *>(out_minmax);
+  if (vec_ok && cols == 768)
+    layernorm_rows_vec_kernel<6><<<grid, 256, 0, st>>>(
+        x, residual, rows, gamma, beta, eps, y, rng);
+  else if (vec_ok && cols == 1024)
+    layernorm_rows_vec_kernel<8><<<grid, 256, 0, st>>>(
+        x, residual, rows, gamma, beta, eps, y, rng);
+  else
+    layernorm_rows_kernel<<<grid, 256, 0, st>>>(
+        x, residual, rows, cols, gamma, beta, eps, y, rng);
   OMCUDA_CHECK_LAUNCH("layernorm_rows_kernel");
   return OMCUDA_OK;
 }

@@ -14,6 +14,9 @@
 //   DEQUANT  Cast(i32->f32) -> Mul -> [Mul] -> [Add] [-> Gelu]
 //            (src/Conversion/ONNXToKrnl/Math/Elementwise.cpp:477-486, 358-388);
 //            each fp32 op is rounded on its own (no fma).
+//   DEQUANT_SPLIT  the DEQUANT value x written as two bf16 planes,
+//            hi = bf16(x) and lo = bf16(x - hi): the operand format of the
+//            tensor-core attention kernel (tensor-core GEMM only).
 //   REQUANT  QLinearMatMul: f32(acc) * S[n], round half even, fptosi,
 //            + y zero point, truncate to 8 bits
 //            (src/Conversion/ONNXToKrnl/Math/QLinearMatMul.cpp:123-138).
@@ -86,7 +89,7 @@ __device__ __forceinline__ EpiScalars epi_scalars(const EpiParams &p) {
   EpiScalars s;
   s.sa = 1.0f;
   s.s0 = 1.0f;
-  if (p.kind == OMCUDA_EPI_DEQUANT) {
+  if (p.kind == OMCUDA_EPI_DEQUANT || p.kind == OMCUDA_EPI_DEQUANT_SPLIT) {
     s.sa = __ldg(p.sa);
     if (p.sb_len == 1)
       s.s0 = __fmul_rn(s.sa, __ldg(p.sb)); // onnx.Mul of the two scalars
@@ -147,14 +150,7 @@ __device__ __forceinline__ uint32_t epi_requant(const EpiParams &p,
 // Folds a thread's {min,max} of the fp32 outputs into the running range.
 __device__ __forceinline__ void epi_range_commit(
     uint32_t *range, float lo, float hi) {
-  lo = warp_min(lo);
-  hi = warp_max(hi);
-  if ((threadIdx.x & 31) == 0) {
-    if (lo <= hi) { // false when the warp produced no finite-or-inf value
-      atomicMin(range, f32_to_ordered(lo));
-      atomicMax(range + 1, f32_to_ordered(hi));
-    }
-  }
+  range_commit_warp(range, lo, hi);
 }
 
 #endif // __CUDACC__

@@ -330,7 +330,8 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
     return fail(OMCUDA_EINVAL, "GemmI8: b_zp needs the row sums of A");
   if (a.a_zp && a.a_zp_len != 0 && !a.B.colsum)
     return fail(OMCUDA_EINVAL, "GemmI8: a_zp needs the column sums of B");
-  if (a.epilogue == OMCUDA_EPI_DEQUANT && (!a.sa || !a.sb))
+  if ((a.epilogue == OMCUDA_EPI_DEQUANT || a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT) &&
+      (!a.sa || !a.sb))
     return fail(OMCUDA_EINVAL, "GemmI8: dequant epilogue needs both scales");
   if (a.epilogue == OMCUDA_EPI_REQUANT && !a.sb)
     return fail(OMCUDA_EINVAL, "GemmI8: requant epilogue needs S");
@@ -341,7 +342,11 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
   if (a.kernel_choice == 1 && !tc_ok)
     return fail(OMCUDA_ENOTSUP,
         "GemmI8: tensor-core kernel needs K %% 16 == 0 and 16-byte aligned A");
-  bool use_tc = (a.kernel_choice == 1) ||
+  if (a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT && (!tc_ok || a.kernel_choice == 2))
+    return fail(OMCUDA_ENOTSUP,
+        "GemmI8: the split-bf16 tail exists on the tensor-core kernel only "
+        "(K %% 16 == 0, 16-byte aligned A)");
+  bool use_tc = (a.kernel_choice == 1) || a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT ||
                 (a.kernel_choice == 0 && tc_ok && a.M > 16);
   return use_tc ? launch_gemm_tc(a, st) : launch_gemm_simt(a, st);
 }

@@ -36,6 +36,7 @@
 
 #include "../runtime/internal.h"
 #include "gemm_epilogue.cuh"
+#include "tc_ptx.cuh"
 
 namespace omcuda {
 
@@ -61,227 +62,6 @@ __host__ __device__ constexpr int tc_stages(int stage_bytes, int ew) {
   return (kSmemBudget - ew * 4096) / stage_bytes < 8
              ? (kSmemBudget - ew * 4096) / stage_bytes
              : 8;
-}
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
-
-// ---- PTX wrappers -------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-__device__ __forceinline__ uint64_t global_timer() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-               "r"(bytes)
-               : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t"
-               ".reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-               "selp.u32 %0, 1, 0, p;\n\t"
-               "}"
-               : "=r"(ok)
-               : "r"(bar), "r"(parity)
-               : "memory");
-  return ok != 0;
-}
-
-// Bounded wait.  Returns false when the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(
-    uint32_t bar, uint32_t parity, volatile int *abort_flag, uint64_t t0) {
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xffu) == 0) {
-      if (*abort_flag)
-        return false;
-      if (global_timer() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map,
-    int32_t x, int32_t y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                   smem_dst),
-               "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::
-                   : "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr),
-               "r"(ncols)
-               : "memory");
-}
-
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc,
-    uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t"
-               ".reg .pred p;\n\t"
-               "setp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
-               "}" ::"r"(d_tmem),
-               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
-
-// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread
-// has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile(
-      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-          bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
-      "%30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]),
-        "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]),
-        "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
-        "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]),
-        "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor for a K-major tile stored as rows of 128
-// bytes with the 128-byte swizzle (what the TMA loads above write): eight rows
-// form one 1024-byte swizzle atom, so the stride between 8-row groups is 1024
-// bytes; the leading-dimension offset is not used by swizzled K-major layouts.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);  // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                    // leading byte offset (unused)
-  d |= (uint64_t)(1024u >> 4) << 32;         // stride byte offset
-  d |= (uint64_t)1 << 46;                    // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;                    // layout: 128-byte swizzle
-  return d;
-}
-
-
-// ---- thread-block-cluster helpers (2-CTA kernel) -------------------------------------
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-
-// Address of the same shared-memory location in another CTA of the cluster.
-__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta_rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta_rank));
-  return r;
-}
-
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// Arrive on an mbarrier that may live in the peer CTA (cluster address).
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(
-                   cluster_addr)
-               : "memory");
-}
-
-// TMA load of one CTA of a pair; completion bytes go to the mbarrier at
-// cluster address `bar` (the leader CTA's).  Plain load: every CTA fetches
-// its own tile, nothing is multicast.
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst,
-    const CUtensorMap *map, int32_t x, int32_t y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                   smem_dst),
-               "r"(ncols)
-               : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::
-                   : "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr),
-               "r"(ncols)
-               : "memory");
-}
-
-// One MMA over both CTAs of the pair: M = 256 (128 rows from each CTA's A
-// tile), N = BN (each CTA's shared memory holds half of the B tile), K = 32.
-__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc,
-    uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n\t"
-               ".reg .pred p;\n\t"
-               "setp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
-               "}" ::"r"(d_tmem),
-               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
-
-// Arrives, once the MMAs issued so far have completed, on the mbarrier at this
-// shared-memory offset in every CTA whose bit is set in cta_mask.  (This is a
-// barrier signal, not a data load.)
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
-      "[%0], %1;" ::"r"(bar),
-      "h"(cta_mask)
-      : "memory");
 }
 
 template <int BN, int EW>
@@ -331,7 +111,8 @@ __device__ __forceinline__ void load_cols32(
 }
 
 // Turns 32 raw accumulators of one row into 32 output words (EPI_I32: the
-// corrected i32; EPI_DEQUANT: f32 bits; EPI_REQUANT: one byte per word).
+// corrected i32; EPI_DEQUANT and EPI_DEQUANT_SPLIT: f32 bits; EPI_REQUANT: one
+// byte per word).
 template <int EPI>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
     const EpiScalars &sc, const EpiRow &row, int64_t nc, int valid,
@@ -372,7 +153,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
   }
   if (EPI == OMCUDA_EPI_I32)
     return;
-  if (EPI == OMCUDA_EPI_DEQUANT) {
+  if (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT) {
     float f[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j)
@@ -436,6 +217,30 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
   }
 }
 
+// 32 f32 words -> words 0..15: bf16 hi of the pairs (v0,v1), (v2,v3), ...;
+// words 16..31: bf16 lo, with hi = bf16(x), lo = bf16(x - hi), round to
+// nearest even (the operand format of the tcgen05 attention kernel).
+__device__ __forceinline__ void split_words_bf16(uint32_t (&v)[32]) {
+  uint32_t h[16], l[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float a = __uint_as_float(v[2 * i]), b = __uint_as_float(v[2 * i + 1]);
+    uint32_t hw;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hw) : "f"(b), "f"(a));
+    const float ra = __fsub_rn(a, __uint_as_float(hw << 16));
+    const float rb = __fsub_rn(b, __uint_as_float(hw & 0xffff0000u));
+    uint32_t lw;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lw) : "f"(rb), "f"(ra));
+    h[i] = hw;
+    l[i] = lw;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v[i] = h[i];
+    v[16 + i] = l[i];
+  }
+}
+
 // Drains one accumulator tile half (this warp's 32 TMEM lanes x kHalfCols
 // columns starting at taddr) through the epilogue into Y.
 //   m_warp   first output row of this warp's 32 rows
@@ -445,6 +250,9 @@ template <int BN, int EPI, int EW>
 __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
     const EpiScalars &sc, uint32_t taddr, int64_t m_warp, int64_t n0,
     uint32_t slab0, int lane, bool use_slab, float &lo, float &hi) {
+  // EPI_DEQUANT_SPLIT stages like the 4-byte tails (32 columns per 128-byte
+  // slab row: 16 words of bf16 hi pairs, then 16 words of lo pairs).
+  constexpr bool kSplit = EPI == OMCUDA_EPI_DEQUANT_SPLIT;
   constexpr int kOutBytes = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
   constexpr int kHalfCols = epi_cols_per_warp(BN, EW);
   constexpr int kSlabCols =
@@ -480,6 +288,8 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
         const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
         if (row_ok && valid > 0)
           epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
+        if (kSplit)
+          split_words_bf16(v);
         if (kOutBytes == 4) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -500,8 +310,14 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
       __syncwarp();
       // Lane l serves 16-byte piece (l & 7) of rows (l >> 3) + 4*i.
       const uint32_t piece = (uint32_t)(lane & 7);
-      const int64_t col_b = ng * kOutBytes + piece * 16; // byte column in Y
-      const bool col_ok = (col_b < p.N * kOutBytes) &&
+      // Byte column in Y (kSplit: in the hi plane for pieces 0-3, in the lo
+      // plane, M*N bf16 further on, for pieces 4-7), row pitch in bytes.
+      const int64_t pitch_b = p.N * (kSplit ? 2 : kOutBytes);
+      const int64_t col_b = kSplit ? ng * 2 + (piece & 3u) * 16
+                                   : ng * kOutBytes + piece * 16;
+      uint8_t *ybase = reinterpret_cast<uint8_t *>(p.Y) +
+                       ((kSplit && piece >= 4) ? p.M * pitch_b : 0);
+      const bool col_ok = (col_b < pitch_b) &&
                           ((int)piece * 16 < kSlabCols * kOutBytes);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -513,8 +329,7 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
                            ((piece ^ (uint32_t)(r & 7)) << 4)));
         const int64_t mr = m_warp + r;
         if (col_ok && mr < p.M)
-          *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(p.Y) +
-                                     mr * p.N * kOutBytes + col_b) =
+          *reinterpret_cast<uint4 *>(ybase + mr * pitch_b + col_b) =
               make_uint4(q0, q1, q2, q3);
       }
       __syncwarp(); // slab is rewritten by the next group
@@ -533,7 +348,17 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
       if (!row_ok || valid <= 0)
         continue;
       epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
-      if (kOutBytes == 4) {
+      if (kSplit) {
+        split_words_bf16(v);
+        uint16_t *dhi = reinterpret_cast<uint16_t *>(p.Y) + m * p.N + nc;
+        uint16_t *dlo = dhi + p.M * p.N;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < valid) {
+            dhi[j] = (uint16_t)(v[j >> 1] >> (16 * (j & 1)));
+            dlo[j] = (uint16_t)(v[16 + (j >> 1)] >> (16 * (j & 1)));
+          }
+      } else if (kOutBytes == 4) {
         uint32_t *dst = reinterpret_cast<uint32_t *>(p.Y) + m * p.N + nc;
         if (y4_ok && valid == 32) {
 #pragma unroll
@@ -725,7 +550,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       __syncwarp();
       if (lane == 0)
         mbar_arrive(smem_u32(&bar_acc_empty[buf]));
-      if (p.out_range && EPI == OMCUDA_EPI_DEQUANT)
+      if (p.out_range && (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT))
         epi_range_commit(p.out_range, lo, hi);
     }
   }
@@ -925,7 +750,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       __syncwarp();
       if (lane == 0)
         mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[buf]), 0));
-      if (p.out_range && EPI == OMCUDA_EPI_DEQUANT)
+      if (p.out_range && (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT))
         epi_range_commit(p.out_range, lo, hi);
     }
   }
@@ -946,14 +771,16 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 
 // ---- host side ----------------------------------------------------------------------
 
-namespace {
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
-    void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
+// 2-D tensor map over a row-major [rows, cols] matrix of esize-byte elements
+// (1: u8, 2: bf16, 4: i32) whose row pitch is pitch bytes; box = box_cols x
+// box_rows elements, 128-byte swizzle (box_cols * esize must be 128), zero fill
+// outside the matrix.
+int make_tma_map_2d(CUtensorMap *map, const void *base, int64_t rows,
+    int64_t cols, int64_t pitch, int box_cols, int box_rows, int esize) {
+  typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
+      void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+      const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
   static EncodeTiledFn fn = nullptr;
   static bool tried = false;
   if (!tried) {
@@ -965,29 +792,42 @@ EncodeTiledFn get_encode_fn() {
         qres == cudaDriverEntryPointSuccess)
       fn = (EncodeTiledFn)sym;
   }
-  return fn;
-}
-
-// 2-D map over a row-major [rows, cols] matrix of esize-byte elements whose row
-// pitch is pitch bytes; box = 128 bytes x box_rows, 128-byte swizzle, zero
-// fill (loads) / clipping (stores) outside.
-int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t cols,
-    int64_t pitch, int box_rows, int esize = 1) {
-  EncodeTiledFn fn = get_encode_fn();
   if (!fn)
     return fail(OMCUDA_ECUDA, "cuTensorMapEncodeTiled is not available");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)pitch};
-  cuuint32_t box[2] = {(cuuint32_t)(kBK / esize), (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map,
-      esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
-      2, const_cast<void *>(base), dims, strides, box, estr,
+  const CUtensorMapDataType dt = esize == 4   ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                                 : esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                              : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(OMCUDA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
   return OMCUDA_OK;
+}
+
+// One device word shared by the tensor-core kernels: set to non-zero by a CTA
+// whose bounded wait gave up.
+static int *g_status_word = nullptr;
+
+int *tc_status_word() {
+  if (!g_status_word) {
+    if (cudaMalloc(&g_status_word, sizeof(int)) != cudaSuccess)
+      return nullptr;
+    cudaMemset(g_status_word, 0, sizeof(int));
+  }
+  return g_status_word;
+}
+
+namespace {
+
+// 2-D map for the GEMM operands: box = 128 bytes x box_rows.
+int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t cols,
+    int64_t pitch, int box_rows, int esize = 1) {
+  return make_tma_map_2d(map, base, rows, cols, pitch, kBK / esize, box_rows, esize);
 }
 
 // Instruction descriptor of tcgen05.mma kind::i8: s32 accumulator, operand
@@ -1000,17 +840,6 @@ uint32_t make_idesc(int a_signed, int b_signed, int n) {
   d |= (uint32_t)(n >> 3) << 17;       // N / 8
   d |= (uint32_t)(kBM >> 4) << 24;     // M / 16
   return d;
-}
-
-int *g_status_word = nullptr;
-
-int *status_word() {
-  if (!g_status_word) {
-    if (cudaMalloc(&g_status_word, sizeof(int)) != cudaSuccess)
-      return nullptr;
-    cudaMemset(g_status_word, 0, sizeof(int));
-  }
-  return g_status_word;
 }
 
 template <int BN, int EPI, int EW>
@@ -1031,9 +860,9 @@ int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
     return rc;
   EpiParams p = make_epi_params(a);
   // 16-byte stores of whole lines need an aligned base and row pitch.
-  const int esize = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
+  const int esize = (EPI == OMCUDA_EPI_REQUANT) ? 1 : (EPI == OMCUDA_EPI_DEQUANT_SPLIT ? 2 : 4);
   p.line_store = (((uintptr_t)a.Y & 15u) == 0) && ((a.N * esize) % 16 == 0);
-  int *status = status_word();
+  int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
   int64_t tiles = ceil_div(a.M, kBM) * ceil_div(a.N, BN);
@@ -1064,6 +893,8 @@ int launch_bn(const omcudaGemmArgs &a, cudaStream_t st) {
     return launch_bn_epi<BN, OMCUDA_EPI_DEQUANT>(a, st);
   case OMCUDA_EPI_REQUANT:
     return launch_bn_epi<BN, OMCUDA_EPI_REQUANT>(a, st);
+  case OMCUDA_EPI_DEQUANT_SPLIT:
+    return launch_bn_epi<BN, OMCUDA_EPI_DEQUANT_SPLIT>(a, st);
   default:
     return fail(OMCUDA_EINVAL, "GemmI8: unknown epilogue %d", a.epilogue);
   }
@@ -1104,9 +935,9 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   if (rc != OMCUDA_OK)
     return rc;
   EpiParams p = make_epi_params(a);
-  const int esize = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
+  const int esize = (EPI == OMCUDA_EPI_REQUANT) ? 1 : (EPI == OMCUDA_EPI_DEQUANT_SPLIT ? 2 : 4);
   p.line_store = (((uintptr_t)a.Y & 15u) == 0) && ((a.N * esize) % 16 == 0);
-  int *status = status_word();
+  int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
   int64_t tiles = ceil_div(a.M, 2 * kBM) * ceil_div(a.N, 256);
@@ -1146,6 +977,8 @@ int launch_pair(const omcudaGemmArgs &a, cudaStream_t st) {
     return launch_pair_epi<OMCUDA_EPI_DEQUANT>(a, st);
   case OMCUDA_EPI_REQUANT:
     return launch_pair_epi<OMCUDA_EPI_REQUANT>(a, st);
+  case OMCUDA_EPI_DEQUANT_SPLIT:
+    return launch_pair_epi<OMCUDA_EPI_DEQUANT_SPLIT>(a, st);
   default:
     return fail(OMCUDA_EINVAL, "GemmI8: unknown epilogue %d", a.epilogue);
   }

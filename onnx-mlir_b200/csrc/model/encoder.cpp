@@ -143,8 +143,8 @@ __global__ void fill_kernel(float *dst, int64_t n, float v) {
 
 int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
     const float *a_scale, const omcudaPreparedB &B, int64_t M,
-    const float *w_scale, int64_t ws_len, const float *bias, int gelu, float *Y,
-    void *out_range, cudaStream_t st) {
+    const float *w_scale, int64_t ws_len, const float *bias, int gelu, void *Y,
+    void *out_range, cudaStream_t st, int epilogue = OMCUDA_EPI_DEQUANT) {
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (e->profiling) {
     while (e->ev.size() < e->ev_used + 2) {
@@ -171,7 +171,7 @@ int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
   g.B = B;
   g.a_zp = a_zp;
   g.a_zp_len = 1;
-  g.epilogue = OMCUDA_EPI_DEQUANT;
+  g.epilogue = epilogue;
   g.Y = Y;
   g.sa = a_scale;
   g.sb = w_scale;
@@ -356,6 +356,13 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
   uint8_t *ranges = (uint8_t *)e->ranges.p;
   float *params = (float *)e->params.p;
   uint8_t *xq = (uint8_t *)e->xq.p;
+  // Head size 64 and a sequence that is a multiple of 128 take the tcgen05
+  // attention kernel, which reads Q, K, V as bf16 hi/lo planes.
+  const bool use_tc_attention =
+      omcudaDevAttentionBf16Supported(batch, seq, heads, dh, 3 * H, H) != 0;
+  // (the f32 [T,3H] buffer holds the two bf16 [T,3H] planes instead)
+  void *planes_hi = e->qkv.p;
+  void *planes_lo = (uint8_t *)e->qkv.p + (size_t)(T * 3 * H) * 2;
 #define RUN(call)                                                              \
   do {                                                                         \
     rc = (call);                                                               \
@@ -385,12 +392,22 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
     if (l > 0)
       RUN(omcudaDevQuantizeFromRange(cur, T * H, r_x, xq, p_x, p_x + 2,
           (uint8_t *)(p_x + 3), st));
-    RUN(gemm(e, xq, (const uint8_t *)(p_x + 3), p_x + 2, L.wqkv, T,
-        (const float *)L.qkv_scale.p, 3 * H, (const float *)L.bqkv.p, 0,
-        (float *)e->qkv.p, nullptr, st));
-    const float *q = (const float *)e->qkv.p;
-    RUN(omcudaDevAttentionEx(q, q + H, q + 2 * H, batch, seq, heads, dh,
-        att_scale, (float *)e->ctx.p, 3 * H, H, r_ctx, st));
+    if (use_tc_attention) {
+      // The projection writes q | k | v straight into the bf16 hi/lo planes
+      // the attention kernel reads; the f32 values never reach HBM.
+      RUN(gemm(e, xq, (const uint8_t *)(p_x + 3), p_x + 2, L.wqkv, T,
+          (const float *)L.qkv_scale.p, 3 * H, (const float *)L.bqkv.p, 0,
+          planes_hi, nullptr, st, OMCUDA_EPI_DEQUANT_SPLIT));
+      RUN(omcudaDevAttentionBf16(planes_hi, planes_lo, 3 * H, 0, H, 2 * H, batch,
+          seq, heads, dh, att_scale, (float *)e->ctx.p, H, r_ctx, st));
+    } else {
+      RUN(gemm(e, xq, (const uint8_t *)(p_x + 3), p_x + 2, L.wqkv, T,
+          (const float *)L.qkv_scale.p, 3 * H, (const float *)L.bqkv.p, 0,
+          (float *)e->qkv.p, nullptr, st));
+      const float *q = (const float *)e->qkv.p;
+      RUN(omcudaDevAttentionEx(q, q + H, q + 2 * H, batch, seq, heads, dh,
+          att_scale, (float *)e->ctx.p, 3 * H, H, r_ctx, st));
+    }
     RUN(omcudaDevQuantizeFromRange((const float *)e->ctx.p, T * H, r_ctx, xq,
         p_ctx, p_ctx + 2, (uint8_t *)(p_ctx + 3), st));
     RUN(gemm(e, xq, (const uint8_t *)(p_ctx + 3), p_ctx + 2, L.wo, T,

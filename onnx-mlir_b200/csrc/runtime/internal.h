@@ -34,4 +34,16 @@ int launch_attention_mma(const float *Q, const float *K, const float *V,
     int64_t B, int64_t S, int64_t heads, int64_t dh, float scale, float *out,
     int64_t ld_in, int64_t ld_out, void *out_range, cudaStream_t st);
 
+// attention_tc.cu: tcgen05 attention over bf16 hi/lo planes [T, ld_planes]
+// (head size 64, sequence a multiple of 128), and the fp32 -> planes split.
+bool attention_tc_supported(int64_t B, int64_t S, int64_t heads, int64_t dh,
+    int64_t ld_planes, int64_t ld_out, const void *hi, const void *lo,
+    const float *out);
+int launch_attention_tc(const void *hi, const void *lo, int64_t ld_planes,
+    int64_t q_col, int64_t k_col, int64_t v_col, int64_t B, int64_t S,
+    int64_t heads, float scale, float *out, int64_t ld_out, void *out_range,
+    cudaStream_t st);
+int launch_split_bf16(const float *x, int64_t rows, int64_t cols, int64_t ld_x,
+    void *hi, void *lo, int64_t ld_p, int64_t col0, cudaStream_t st);
+
 } // namespace omcuda

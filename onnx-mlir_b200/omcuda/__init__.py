@@ -18,11 +18,12 @@ LIB_PATH = os.path.join(_PKG, "lib", "libomcuda.so")
 
 # ONNX TensorProto.DataType values used by OMTensor
 # (include/onnx-mlir/Runtime/OnnxDataTypeMetaData.inc:24-45 in onnx-mlir).
-ONNX_FLOAT, ONNX_UINT8, ONNX_INT8, ONNX_INT32, ONNX_INT64 = 1, 2, 3, 6, 7
+ONNX_FLOAT, ONNX_UINT8, ONNX_INT8, ONNX_UINT16, ONNX_INT32, ONNX_INT64 = 1, 2, 3, 4, 6, 7
 _NP2OM = {
     np.dtype(np.float32): ONNX_FLOAT,
     np.dtype(np.uint8): ONNX_UINT8,
     np.dtype(np.int8): ONNX_INT8,
+    np.dtype(np.uint16): ONNX_UINT16,
     np.dtype(np.int32): ONNX_INT32,
     np.dtype(np.int64): ONNX_INT64,
 }

@@ -7,7 +7,7 @@ import ctypes
 
 from . import OmcudaError, check, lib
 
-EPI_I32, EPI_DEQUANT, EPI_REQUANT = 0, 1, 2
+EPI_I32, EPI_DEQUANT, EPI_REQUANT, EPI_DEQUANT_SPLIT = 0, 1, 2, 3
 KERNEL_AUTO, KERNEL_TENSOR_CORE, KERNEL_SIMT = 0, 1, 2
 
 _vp, _i64, _i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
@@ -68,6 +68,10 @@ def _bind():
     L.omcudaDevMatMulF32.argtypes = [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _vp]
     L.omcudaDevAttention.argtypes = [_vp, _vp, _vp, _i64, _i64, _i64, _i64,
                                      ctypes.c_float, _vp, _vp]
+    L.omcudaDevSplitBf16.argtypes = [_vp, _i64, _i64, _i64, _vp, _vp, _i64, _i64, _vp]
+    L.omcudaDevAttentionBf16Supported.argtypes = [_i64] * 6
+    L.omcudaDevAttentionBf16.argtypes = [_vp, _vp] + [_i64] * 8 + [
+        ctypes.c_float, _vp, _i64, _vp, _vp]
     _bound = True
     return L
 
@@ -132,3 +136,15 @@ def add(a, b, n, y, stream):
 
 def attention(q, k, v, B, S, heads, dh, scale, out, stream):
     _ok(_bind().omcudaDevAttention(q, k, v, B, S, heads, dh, scale, out, stream))
+
+
+def split_bf16(x, rows, cols, ld_x, hi, lo, ld_planes, col0, stream):
+    _ok(_bind().omcudaDevSplitBf16(x, rows, cols, ld_x, hi, lo, ld_planes, col0,
+                                   stream))
+
+
+def attention_bf16(hi, lo, ld_planes, q_col, k_col, v_col, B, S, heads, dh, scale,
+                   out, ld_out, out_range, stream):
+    _ok(_bind().omcudaDevAttentionBf16(hi, lo, ld_planes, q_col, k_col, v_col, B,
+                                       S, heads, dh, scale, out, ld_out,
+                                       out_range, stream))

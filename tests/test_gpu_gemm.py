@@ -229,3 +229,56 @@ def test_config3_sweep_members(gpu, orc, M, K, N):
     want = orc.dequant_tail(acc, xs * w_scale, 0.0, 0, None)
     assert np.allclose(Y[rows], want, rtol=1e-5, atol=0)
     assert Y[rows].tobytes() == want.tobytes()
+
+
+def bf16_split(x):
+    """hi = bf16(x), lo = bf16(x - hi), round to nearest even, as uint16 bit
+    patterns (numpy has no bfloat16)."""
+    def to_bf16_bits(f):
+        u = f.astype(np.float32).view(np.uint32).astype(np.uint64)
+        r = (u + 0x7fff + ((u >> 16) & 1)) >> 16
+        return r.astype(np.uint16)
+    hi = to_bf16_bits(x)
+    hi_f = (hi.astype(np.uint32) << 16).view(np.float32)
+    lo = to_bf16_bits((x - hi_f).astype(np.float32))
+    return hi, lo
+
+
+@pytest.mark.parametrize("M,K,N", [(300, 256, 192), (512, 1024, 3072), (33, 64, 72)])
+def test_dequant_split_epilogue_equals_split_of_dequant(gpu, M, K, N):
+    # The tail that writes bf16 hi/lo planes (operands of the tensor-core
+    # attention kernel) must hold exactly the split of the f32 dequant tail.
+    from gpu_util import DevGemm
+    rng = np.random.default_rng(M + N)
+    dg = DevGemm(gpu)
+    A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    pb, keep = dg.prepare(B)
+    dA = dg.dtensor(A)
+    az = dg.dtensor(np.array([131], np.uint8))
+    sa = dg.dtensor(np.array([0.013], np.float32))
+    sb = dg.dtensor(rng.uniform(0.001, 0.01, N).astype(np.float32))
+    bias = dg.dtensor(rng.normal(0, 0.5, N).astype(np.float32))
+    g = dg.dev.GemmArgs()
+    g.M, g.N, g.K = M, N, K
+    g.A, g.a_signed, g.B = dA.data_ptr, 0, pb
+    g.a_zp, g.a_zp_len = az.data_ptr, 1
+    g.sa, g.sb, g.sb_len, g.bias = sa.data_ptr, sb.data_ptr, N, bias.data_ptr
+    g.kernel_choice = dg.dev.KERNEL_TENSOR_CORE
+    Y = gpu.Tensor.device_empty((M, N), np.float32)
+    g.epilogue, g.Y = dg.dev.EPI_DEQUANT, Y.data_ptr
+    dg.dev.gemm_i8(g, dg.stream)
+    P = gpu.Tensor.device_empty((2, M, N), np.uint16)
+    g.epilogue, g.Y = dg.dev.EPI_DEQUANT_SPLIT, P.data_ptr
+    dg.dev.gemm_i8(g, dg.stream)
+    y, planes = Y.numpy(), P.numpy()
+    gpu.synchronize()
+    hi, lo = bf16_split(y)
+    assert np.array_equal(planes[0], hi)
+    assert np.array_equal(planes[1], lo)
+    # and the standalone split kernel writes the same planes
+    P2 = gpu.Tensor.device_empty((2, M, N), np.uint16)
+    if N % 4 == 0:
+        dg.dev.split_bf16(Y.data_ptr, M, N, N, P2.data_ptr, P2.data_ptr + 2 * M * N,
+                          N, 0, dg.stream)
+        assert np.array_equal(P2.numpy(), planes)
