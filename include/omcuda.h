@@ -373,6 +373,13 @@ int omcudaEncoderSetLayer(
  * output of the same shape and on the same side.  Returns NULL and sets errno
  * on failure. */
 OMTensorList *omcudaEncoderRun(omcudaEncoder *enc, OMTensorList *inputs);
+/* The same with the output tensor supplied by the caller, as a krnl.call
+ * callee receives it (outputs first, preallocated; src/Dialect/Krnl/Krnl.td:52-96):
+ * x and y are f32 [batch, seq, hidden], each in host or device memory.  Host
+ * tensors are staged through HBM buffers the encoder keeps; give pinned host
+ * memory (omcudaHostAlloc) for full-speed copies.  Returns when y is complete
+ * (host y) or with the work queued on the calling thread's stream (device y). */
+int omcudaEncoderRunInto(omcudaEncoder *enc, OMTensor *y, const OMTensor *x);
 /* Device-pointer form: x, y are device f32 [batch*seq, hidden]. */
 int omcudaEncoderRunDev(omcudaEncoder *enc, const float *x, int64_t batch,
     int64_t seq, float *y, void *stream);

@@ -386,10 +386,10 @@ int launch_attention_tc(const void *hi, const void *lo, int64_t ld_planes,
   }
   const int64_t T = B * S;
   CUtensorMap map_hi, map_lo;
-  int rc = make_tma_map_2d(&map_hi, hi, T, ld_planes, ld_planes * 2, kTDh, kTK, 2);
+  int rc = make_tma_map_2d(&map_hi, hi, T, ld_planes, ld_planes * 2, kTDh, kTK, 2, 128);
   if (rc != OMCUDA_OK)
     return rc;
-  rc = make_tma_map_2d(&map_lo, lo, T, ld_planes, ld_planes * 2, kTDh, kTK, 2);
+  rc = make_tma_map_2d(&map_lo, lo, T, ld_planes, ld_planes * 2, kTDh, kTK, 2, 128);
   if (rc != OMCUDA_OK)
     return rc;
   int *status = tc_status_word();

@@ -33,6 +33,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 #include "../runtime/internal.h"
 #include "gemm_epilogue.cuh"
@@ -189,14 +190,25 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
       for (int j = 0; j < 32; ++j)
         f[j] = gelu_erf(f[j]);
     }
+    if (p.out_range) {
+      if (valid == 32) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      if (j < valid) {
-        lo = fminf(lo, f[j]);
-        hi = fmaxf(hi, f[j]);
+        for (int j = 0; j < 32; ++j) {
+          lo = fminf(lo, f[j]);
+          hi = fmaxf(hi, f[j]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < valid) {
+            lo = fminf(lo, f[j]);
+            hi = fmaxf(hi, f[j]);
+          }
       }
-      v[j] = __float_as_uint(f[j]);
     }
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      v[j] = __float_as_uint(f[j]);
     return;
   }
   // EPI_REQUANT
@@ -249,7 +261,8 @@ __device__ __forceinline__ void split_words_bf16(uint32_t (&v)[32]) {
 template <int BN, int EPI, int EW>
 __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
     const EpiScalars &sc, uint32_t taddr, int64_t m_warp, int64_t n0,
-    uint32_t slab0, int lane, bool use_slab, float &lo, float &hi) {
+    uint32_t slab0, int lane, bool use_slab, float &lo, float &hi,
+    const CUtensorMap *map_y, const CUtensorMap *map_y2) {
   // EPI_DEQUANT_SPLIT stages like the 4-byte tails (32 columns per 128-byte
   // slab row: 16 words of bf16 hi pairs, then 16 words of lo pairs).
   constexpr bool kSplit = EPI == OMCUDA_EPI_DEQUANT_SPLIT;
@@ -260,8 +273,6 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
   constexpr int kSlabsPerHalf = kHalfCols / kSlabCols;
   static_assert(kHalfCols % 32 == 0 && kHalfCols % kSlabCols == 0, "tile shape");
   const int64_t m = m_warp + lane;
-  const uint32_t my_row = slab0 + (uint32_t)lane * 128u;
-  const uint32_t swz = (uint32_t)(lane & 7);
   const bool y4_ok = ((p.N & 3) == 0) && (((uintptr_t)p.Y & 15u) == 0);
   const bool row_ok = m < p.M;
   EpiRow row;
@@ -270,11 +281,19 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
   if (row_ok)
     row = epi_row(p, m);
   if (use_slab) {
-    // Results pass through a swizzled shared-memory slab (32 rows x 128
-    // bytes per warp) so that the global stores are whole 128-byte lines:
-    // each thread writes its own row into the slab, then the warp reads
-    // the slab back eight 16-byte pieces per row and stores four full
-    // rows per instruction.
+    // Results pass through a shared-memory slab (32 rows per warp, rows of
+    // kRowB bytes in the 128-byte-swizzle pattern) and leave with one TMA
+    // store per slab, which writes whole lines and clips rows and columns
+    // beyond the matrix.  EPI_DEQUANT_SPLIT uses the two halves of the slab
+    // for the hi and the lo plane.
+    constexpr int kRowB = kSplit ? 64 : kSlabCols * kOutBytes;
+    static_assert(kRowB == 32 || kRowB == 64 || kRowB == 128,
+        "slab rows span one swizzle width");
+    // 16-byte piece index XOR address bits 7.. (3, 2 or 1 bits for the 128-,
+    // 64- and 32-byte swizzle), as the store's tensor map expects.
+    constexpr uint32_t kSwzMask = (uint32_t)kRowB / 16u - 1u;
+    const uint32_t row_off = (uint32_t)lane * kRowB;
+    const bool warp_in = m_warp < p.M;
 #pragma unroll 1
     for (int g = 0; g < kSlabsPerHalf; ++g) {
       const int64_t ng = n0 + (int64_t)g * kSlabCols;
@@ -290,49 +309,48 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
           epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
         if (kSplit)
           split_words_bf16(v);
-        if (kOutBytes == 4) {
+        if (cc == 0) {
+          // The previous store must have read the slab before it is rewritten.
+          if (lane == 0)
+            tma_store_wait_read();
+          __syncwarp();
+        }
+        if (kSplit) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            st_shared_v4(my_row + (((uint32_t)j ^ swz) << 4), v[4 * j],
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t off = row_off + (uint32_t)j * 16u;
+            const uint32_t so = off ^ (((off >> 7) & kSwzMask) << 4);
+            st_shared_v4(slab0 + so, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            st_shared_v4(slab0 + 2048u + so, v[16 + 4 * j], v[17 + 4 * j],
+                v[18 + 4 * j], v[19 + 4 * j]);
+          }
+        } else if (kOutBytes == 4) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t off = row_off + (uint32_t)j * 16u;
+            st_shared_v4(slab0 + (off ^ (((off >> 7) & kSwzMask) << 4)), v[4 * j],
                 v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
         } else {
           uint32_t w[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             w[j] = v[4 * j] | (v[4 * j + 1] << 8) | (v[4 * j + 2] << 16) |
                    (v[4 * j + 3] << 24);
-          const uint32_t c16 = (uint32_t)(cc >> 4);
-          st_shared_v4(my_row + (((c16) ^ swz) << 4), w[0], w[1], w[2], w[3]);
-          st_shared_v4(my_row + (((c16 + 1) ^ swz) << 4), w[4], w[5], w[6],
-              w[7]);
+          const uint32_t off0 = row_off + (uint32_t)cc;
+          const uint32_t off1 = off0 + 16u;
+          st_shared_v4(slab0 + (off0 ^ (((off0 >> 7) & kSwzMask) << 4)), w[0], w[1], w[2], w[3]);
+          st_shared_v4(slab0 + (off1 ^ (((off1 >> 7) & kSwzMask) << 4)), w[4], w[5], w[6], w[7]);
         }
       }
+      fence_proxy_async_smem(); // the slab was written through the generic proxy
       __syncwarp();
-      // Lane l serves 16-byte piece (l & 7) of rows (l >> 3) + 4*i.
-      const uint32_t piece = (uint32_t)(lane & 7);
-      // Byte column in Y (kSplit: in the hi plane for pieces 0-3, in the lo
-      // plane, M*N bf16 further on, for pieces 4-7), row pitch in bytes.
-      const int64_t pitch_b = p.N * (kSplit ? 2 : kOutBytes);
-      const int64_t col_b = kSplit ? ng * 2 + (piece & 3u) * 16
-                                   : ng * kOutBytes + piece * 16;
-      uint8_t *ybase = reinterpret_cast<uint8_t *>(p.Y) +
-                       ((kSplit && piece >= 4) ? p.M * pitch_b : 0);
-      const bool col_ok = (col_b < pitch_b) &&
-                          ((int)piece * 16 < kSlabCols * kOutBytes);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int r = 4 * i + (lane >> 3);
-        uint32_t q0, q1, q2, q3;
-        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(q0), "=r"(q1), "=r"(q2), "=r"(q3)
-                     : "r"(slab0 + (uint32_t)r * 128u +
-                           ((piece ^ (uint32_t)(r & 7)) << 4)));
-        const int64_t mr = m_warp + r;
-        if (col_ok && mr < p.M)
-          *reinterpret_cast<uint4 *>(ybase + mr * pitch_b + col_b) =
-              make_uint4(q0, q1, q2, q3);
+      if (lane == 0 && warp_in && ng < p.N) {
+        tma_store_2d(map_y, slab0, (int32_t)ng, (int32_t)m_warp);
+        if (kSplit)
+          tma_store_2d(map_y2, slab0 + 2048u, (int32_t)ng, (int32_t)m_warp);
+        tma_store_commit();
       }
-      __syncwarp(); // slab is rewritten by the next group
     }
   } else {
     // Fallback when the row pitch of Y is not a multiple of 16 bytes:
@@ -389,7 +407,9 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
 template <int BN, int EPI, int EW>
 __global__ void __launch_bounds__(tc_threads(EW), 1)
     gemm_i8_tc_kernel(const __grid_constant__ CUtensorMap map_a,
-        const __grid_constant__ CUtensorMap map_b, EpiParams p, uint32_t idesc,
+        const __grid_constant__ CUtensorMap map_b,
+        const __grid_constant__ CUtensorMap map_y,
+        const __grid_constant__ CUtensorMap map_y2, EpiParams p, uint32_t idesc,
         int *status) {
   using Cfg = TcConfig<BN, EW>;
   constexpr int kStages = Cfg::kStages;
@@ -514,6 +534,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
     const uint32_t slab0 = staging_base + (uint32_t)ew * Cfg::kSlabBytes;
     bool ok = active;
     int64_t it = 0;
+    float lo = INFINITY, hi = -INFINITY; // range of this warp's f32 outputs
     for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
       const int buf = (int)(it & 1);
       const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
@@ -541,18 +562,23 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         break;
       }
       tcgen05_fence_after();
-      float lo = INFINITY, hi = -INFINITY;
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
-      epilogue_tile<BN, EPI, EW>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi);
+      epilogue_tile<BN, EPI, EW>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi,
+          &map_y, &map_y2);
       // The accumulator buffer may be overwritten once all eight warps are done.
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0)
         mbar_arrive(smem_u32(&bar_acc_empty[buf]));
-      if (p.out_range && (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT))
-        epi_range_commit(p.out_range, lo, hi);
     }
+    // One commit of the running range per warp, and every store of this warp
+    // complete before the CTA may exit.
+    if (active && p.out_range &&
+        (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT))
+      epi_range_commit(p.out_range, lo, hi);
+    if (lane == 0)
+      tma_store_wait_all();
   }
 
   // ---------------- teardown ----------------
@@ -583,7 +609,9 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 template <int EPI, int EW>
 __global__ void __launch_bounds__(tc_threads(EW), 1)
     gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap map_a,
-        const __grid_constant__ CUtensorMap map_b, EpiParams p, uint32_t idesc,
+        const __grid_constant__ CUtensorMap map_b,
+        const __grid_constant__ CUtensorMap map_y,
+        const __grid_constant__ CUtensorMap map_y2, EpiParams p, uint32_t idesc,
         int *status) {
   constexpr int BN = 256;
   constexpr int kABytes = kBM * kBK;
@@ -616,7 +644,6 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
   const int64_t tiles_n = ceil_div(p.N, BN);
   const int64_t num_tiles = tiles_m * tiles_n;
   const int num_kb = (int)ceil_div(p.K, kBK);
-
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -717,6 +744,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
     const uint32_t slab0 = staging_base + (uint32_t)ew * kSlabBytes;
     bool ok = active;
     int64_t it = 0;
+    float lo = INFINITY, hi = -INFINITY; // range of this warp's f32 outputs
     for (int64_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
       const int buf = (int)(it & 1);
       const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
@@ -742,17 +770,20 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         break;
       }
       tcgen05_fence_after();
-      float lo = INFINITY, hi = -INFINITY;
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
-      epilogue_tile<BN, EPI, EW>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi);
+      epilogue_tile<BN, EPI, EW>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi,
+          &map_y, &map_y2);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0)
         mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[buf]), 0));
-      if (p.out_range && (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT))
-        epi_range_commit(p.out_range, lo, hi);
     }
+    if (active && p.out_range &&
+        (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT))
+      epi_range_commit(p.out_range, lo, hi);
+    if (lane == 0)
+      tma_store_wait_all();
   }
 
   // ---------------- teardown ----------------
@@ -773,10 +804,12 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 
 // 2-D tensor map over a row-major [rows, cols] matrix of esize-byte elements
 // (1: u8, 2: bf16, 4: i32) whose row pitch is pitch bytes; box = box_cols x
-// box_rows elements, 128-byte swizzle (box_cols * esize must be 128), zero fill
-// outside the matrix.
+// box_rows elements with box_cols * esize == swizzle_bytes (32, 64 or 128: the
+// swizzle mode of that width); loads fill with zeros outside the matrix, stores
+// clip.
 int make_tma_map_2d(CUtensorMap *map, const void *base, int64_t rows,
-    int64_t cols, int64_t pitch, int box_cols, int box_rows, int esize) {
+    int64_t cols, int64_t pitch, int box_cols, int box_rows, int esize,
+    int swizzle_bytes) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
       void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
       const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -794,6 +827,12 @@ int make_tma_map_2d(CUtensorMap *map, const void *base, int64_t rows,
   }
   if (!fn)
     return fail(OMCUDA_ECUDA, "cuTensorMapEncodeTiled is not available");
+  // A box row must span exactly the swizzle width, so that rows are packed
+  // densely in shared memory in the pattern the kernels assume.
+  if (box_cols * esize != swizzle_bytes ||
+      (swizzle_bytes != 32 && swizzle_bytes != 64 && swizzle_bytes != 128))
+    return fail(OMCUDA_EINVAL, "tensor map: box row of %d bytes with a %d-byte swizzle",
+        box_cols * esize, swizzle_bytes);
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)pitch};
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
@@ -802,7 +841,10 @@ int make_tma_map_2d(CUtensorMap *map, const void *base, int64_t rows,
                                  : esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                               : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
-      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_INTERLEAVE_NONE,
+      swizzle_bytes == 32   ? CU_TENSOR_MAP_SWIZZLE_32B
+      : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                            : CU_TENSOR_MAP_SWIZZLE_128B,
       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(OMCUDA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
@@ -827,7 +869,7 @@ namespace {
 // 2-D map for the GEMM operands: box = 128 bytes x box_rows.
 int make_map(CUtensorMap *map, const void *base, int64_t rows, int64_t cols,
     int64_t pitch, int box_rows, int esize = 1) {
-  return make_tma_map_2d(map, base, rows, cols, pitch, kBK / esize, box_rows, esize);
+  return make_tma_map_2d(map, base, rows, cols, pitch, kBK / esize, box_rows, esize, 128);
 }
 
 // Instruction descriptor of tcgen05.mma kind::i8: s32 accumulator, operand
@@ -840,6 +882,33 @@ uint32_t make_idesc(int a_signed, int b_signed, int n) {
   d |= (uint32_t)(n >> 3) << 17;       // N / 8
   d |= (uint32_t)(kBM >> 4) << 24;     // M / 16
   return d;
+}
+
+// Tensor maps of the output for the epilogue's TMA stores: boxes of 32 rows x
+// one slab row (32 f32 / i32 columns; kHalfCols, at most 128, u8 columns; 32
+// bf16 columns of the hi and of the lo plane).  Only encoded when Y can take
+// them (16-byte aligned base and row pitch); otherwise the kernel stores
+// directly and never reads the maps.
+template <int EPI>
+int make_y_maps(const omcudaGemmArgs &a, int half_cols, bool line_store,
+    CUtensorMap *map_y, CUtensorMap *map_y2) {
+  memset(map_y, 0, sizeof(*map_y));
+  memset(map_y2, 0, sizeof(*map_y2));
+  if (!line_store)
+    return OMCUDA_OK;
+  int rc;
+  if (EPI == OMCUDA_EPI_REQUANT) {
+    const int cols = half_cols < 128 ? half_cols : 128; // 32, 64 or 128
+    rc = make_tma_map_2d(map_y, a.Y, a.M, a.N, a.N, cols, 32, 1, cols);
+  } else if (EPI == OMCUDA_EPI_DEQUANT_SPLIT) {
+    rc = make_tma_map_2d(map_y, a.Y, a.M, a.N, a.N * 2, 32, 32, 2, 64);
+    if (rc == OMCUDA_OK)
+      rc = make_tma_map_2d(map_y2, (const uint8_t *)a.Y + (size_t)a.M * a.N * 2, a.M,
+          a.N, a.N * 2, 32, 32, 2, 64);
+  } else {
+    rc = make_tma_map_2d(map_y, a.Y, a.M, a.N, a.N * 4, 32, 32, 4, 128);
+  }
+  return rc;
 }
 
 template <int BN, int EPI, int EW>
@@ -865,11 +934,15 @@ int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
+  CUtensorMap map_y, map_y2;
+  rc = make_y_maps<EPI>(a, epi_cols_per_warp(BN, EW), p.line_store != 0, &map_y, &map_y2);
+  if (rc != OMCUDA_OK)
+    return rc;
   int64_t tiles = ceil_div(a.M, kBM) * ceil_div(a.N, BN);
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   uint32_t idesc = make_idesc(a.a_signed, a.B.b_signed, BN);
   gemm_i8_tc_kernel<BN, EPI, EW><<<grid, tc_threads(EW), Cfg::kSmemBytes, st>>>(
-      map_a, map_b, p, idesc, status);
+      map_a, map_b, map_y, map_y2, p, idesc, status);
   OMCUDA_CHECK_LAUNCH("gemm_i8_tc_kernel");
   return OMCUDA_OK;
 }
@@ -957,8 +1030,12 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  OMCUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_i8_tc2_kernel<EPI, EW>, map_a, map_b, p,
-      idesc, status));
+  CUtensorMap map_y, map_y2;
+  rc = make_y_maps<EPI>(a, epi_cols_per_warp(256, EW), p.line_store != 0, &map_y, &map_y2);
+  if (rc != OMCUDA_OK)
+    return rc;
+  OMCUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_i8_tc2_kernel<EPI, EW>, map_a, map_b,
+      map_y, map_y2, p, idesc, status));
   count_launch();
   return OMCUDA_OK;
 }

@@ -79,6 +79,30 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 
+// TMA store of a shared-memory box to global memory (bulk async group).
+__device__ __forceinline__ void tma_store_2d(
+    const CUtensorMap *map, uint32_t src, int32_t x, int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+      "r"(src), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Until the stores committed so far have read their shared-memory source.
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// Until the stores committed so far are complete.
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// Makes shared-memory writes of this thread visible to the async (TMA) proxy.
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void tcgen05_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -238,7 +262,8 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
 
 // Host-side helpers shared by the tensor-core kernels (gemm_tc.cu).
 int make_tma_map_2d(CUtensorMap *map, const void *base, int64_t rows,
-    int64_t cols, int64_t pitch, int box_cols, int box_rows, int esize);
+    int64_t cols, int64_t pitch, int box_cols, int box_rows, int esize,
+    int swizzle_bytes);
 int *tc_status_word();
 
 } // namespace omcuda

@@ -77,6 +77,7 @@ struct omcudaEncoder {
   // workspace, sized for the largest (batch*seq) seen
   int64_t tokens = 0;
   DevBuf xq, qkv, ctx, a, h1, f, o, ybuf[2];
+  DevBuf stage_in, stage_out; // HBM staging of host tensors (omcudaEncoderRunInto)
   DevBuf ranges;  // 4 running ranges per layer + 1
   DevBuf params;  // 16 bytes per quantize site
   DevBuf dql_scratch;
@@ -502,6 +503,55 @@ extern "C" OMTensorList *omcudaEncoderRun(omcudaEncoder *e, OMTensorList *inputs
   return res;
 }
 
+extern "C" int omcudaEncoderRunInto(
+    omcudaEncoder *e, OMTensor *y, const OMTensor *x) {
+  if (sticky_error())
+    return omcudaGetLastError();
+  int rc = ensure_init();
+  if (rc != OMCUDA_OK)
+    return rc;
+  if (!e || !x || !y || omTensorGetDataType(x) != ONNX_TYPE_FLOAT ||
+      omTensorGetDataType(y) != ONNX_TYPE_FLOAT || omTensorGetRank(x) != 3 ||
+      omTensorGetRank(y) != 3 || omTensorGetShape(x)[2] != e->cfg.hidden)
+    return fail(OMCUDA_EINVAL, "EncoderRunInto: x and y must be f32 [batch, seq, %lld]",
+        (long long)e->cfg.hidden);
+  for (int i = 0; i < 3; ++i)
+    if (omTensorGetShape(x)[i] != omTensorGetShape(y)[i])
+      return fail(OMCUDA_EINVAL, "EncoderRunInto: y must have the shape of x");
+  const int64_t B = omTensorGetShape(x)[0], S = omTensorGetShape(x)[1];
+  const size_t bytes = (size_t)(B * S * e->cfg.hidden) * 4;
+  cudaStream_t st = current_stream();
+  const bool x_dev = omcudaTensorIsOnDevice(x) != 0;
+  const bool y_dev = omcudaTensorIsOnDevice(y) != 0;
+  const float *dx = (const float *)omTensorGetDataPtr(x);
+  float *dy = (float *)omTensorGetDataPtr(y);
+  if (!x_dev) {
+    e->stage_in.ensure(bytes);
+    if (!e->stage_in.p)
+      return OMCUDA_ENOMEM;
+    OMCUDA_CHECK(cudaMemcpyAsync(e->stage_in.p, omTensorGetDataPtr(x), bytes,
+        cudaMemcpyHostToDevice, st));
+    dx = (const float *)e->stage_in.p;
+  }
+  if (!y_dev) {
+    e->stage_out.ensure(bytes);
+    if (!e->stage_out.p)
+      return OMCUDA_ENOMEM;
+    dy = (float *)e->stage_out.p;
+  }
+  rc = omcudaEncoderRunDev(e, dx, B, S, dy, st);
+  if (rc != OMCUDA_OK)
+    return rc;
+  if (!y_dev) {
+    OMCUDA_CHECK(cudaMemcpyAsync(omTensorGetDataPtr(y), dy, bytes,
+        cudaMemcpyDeviceToHost, st));
+    omcudaSynchronize(); // the host buffer is complete when the call returns
+    if (sticky_error())
+      return omcudaGetLastError();
+  }
+  return OMCUDA_OK;
+}
+
 extern "C" void omcudaEncoderSetProfiling(omcudaEncoder *e, int on) {
   if (!e)
     return;
@@ -541,7 +591,7 @@ extern "C" void omcudaEncoderDestroy(omcudaEncoder *e) {
     for (DevBuf *b : all)
       b->release();
   }
-  DevBuf *ws[] = {&e->xq, &e->qkv, &e->ctx, &e->a, &e->h1, &e->f, &e->o,
+  DevBuf *ws[] = {&e->stage_in, &e->stage_out, &e->xq, &e->qkv, &e->ctx, &e->a, &e->h1, &e->f, &e->o,
       &e->ybuf[0], &e->ybuf[1], &e->ranges, &e->params, &e->dql_scratch};
   for (DevBuf *b : ws)
     b->release();

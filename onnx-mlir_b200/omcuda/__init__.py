@@ -474,6 +474,16 @@ class Encoder:
         L.omTensorDestroy(o)
         return out
 
+    def run_into(self, x, y):
+        """run_main_graph with the caller's output: x, y are Tensors (host or
+        device) of shape [B,S,H]; y is filled in place."""
+        L = lib()
+        L.omcudaEncoderRunInto.argtypes = [ctypes.c_void_p] * 3
+        rc = L.omcudaEncoderRunInto(self.handle, y.handle, x.handle)
+        if rc != 0:
+            check()
+            raise OmcudaError(rc, "omcudaEncoderRunInto failed")
+
     def run_dev(self, x_ptr, batch, seq, y_ptr, stream):
         rc = lib().omcudaEncoderRunDev(self.handle, x_ptr, batch, seq, y_ptr, stream)
         if rc != 0:

@@ -282,3 +282,21 @@ def test_dequant_split_epilogue_equals_split_of_dequant(gpu, M, K, N):
         dg.dev.split_bf16(Y.data_ptr, M, N, N, P2.data_ptr, P2.data_ptr + 2 * M * N,
                           N, 0, dg.stream)
         assert np.array_equal(P2.numpy(), planes)
+
+
+@pytest.mark.parametrize("M,K,N", [(4096, 4096, 4096), (5000, 2048, 4104), (300, 512, 1000)])
+def test_whole_output_checksums(gpu, orc, M, K, N):
+    # Every tile of the output is stored exactly once (the epilogue leaves
+    # through TMA stores that clip ragged edges): sampled rows against the
+    # oracle and column sums of the whole result against exact integer sums.
+    from gpu_util import DevGemm
+    rng = np.random.default_rng(K + N)
+    A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    dg = DevGemm(gpu)
+    rows = np.concatenate([np.arange(0, 40), np.arange(max(M - 300, 40), M, 7)])
+    want = orc.matmul_integer_2d(A[rows], B, np.array([117], np.uint8), None)
+    Y = dg.matmul_integer(A, B, 117, None, 1)
+    assert np.array_equal(Y[rows], want)
+    As = A.astype(np.int64) - 117
+    assert np.array_equal(Y.astype(np.int64).sum(0), As.sum(0) @ B.astype(np.int64))
