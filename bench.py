@@ -452,6 +452,8 @@ def cpu_baseline(workload, wl=None, reps=1):
     """Times the oracle's reference-shaped CPU code on a bounded sample."""
     import oracle_lib
     orc = oracle_lib.Oracle(os.path.join(ROOT, "oracle", "_build", "liboracle.so"))
+    # All host cores this process may run on (torchrun exports OMP_NUM_THREADS=1).
+    orc.L.orc_set_threads(len(os.sched_getaffinity(0)))
     threads = orc.L.orc_max_threads()
     if workload in EncoderWorkload.SHAPES:
         c = EncoderWorkload.SHAPES[workload]

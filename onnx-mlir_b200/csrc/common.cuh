@@ -84,6 +84,33 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// Gelu with the exact (erf) formula of the reference,
+// 0.5 * x * (1 + erf(x / sqrt(2))) (src/Conversion/ONNXToKrnl/Math/Elementwise.cpp:358-388),
+// with erf evaluated without a branch as
+//   erf(t) = 1 - 2^(t * Q(t)),  t = min(|x| / sqrt(2), 4),  sign restored,
+// Q a degree-7 polynomial fitted (weighted least squares on [0, 4], weights
+// following the sensitivity of erf to Q) to log2(erfc(t)) / t.  Absolute
+// error of erf below 2e-7 (polynomial 8.5e-8 plus the 2^x approximation), of
+// Gelu below 4e-7 on [-8, 8]; beyond t = 4 erf is 1 in fp32.  About 15
+// instructions against the 35-40 of the library erff with both of its
+// branches taken in a warp, which matters in the GEMM epilogue.  Every Gelu
+// of the library (fused tail and standalone op) goes through this function.
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float t = fminf(fabsf(__fmul_rn(x, 0.70710678118654752440f)), 4.0f);
+  float q = -4.5358585339272395e-05f;
+  q = __fmaf_rn(q, t, 0.00044550743768922985f);
+  q = __fmaf_rn(q, t, -0.0014894406776875257f);
+  q = __fmaf_rn(q, t, -0.0007746315677650273f);
+  q = __fmaf_rn(q, t, 0.02825368382036686f);
+  q = __fmaf_rn(q, t, -0.14848162233829498f);
+  q = __fmaf_rn(q, t, -0.9184163808822632f);
+  q = __fmaf_rn(q, t, -1.6279085874557495f);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(q, t)));
+  const float r = copysignf(__fsub_rn(1.0f, e), x);
+  return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, r));
+}
+
 // Order-preserving float <-> uint mapping so running min/max can use integer
 // atomics.  NaNs never reach these (callers filter with fminf/fmaxf).
 __device__ __forceinline__ uint32_t f32_to_ordered(float f) {

@@ -26,12 +26,13 @@
 //   thread 0   waits for the K tiles (TMA, 128-byte swizzle), issues
 //              S = Q K^T as 12 MMAs (3 split terms x 4 k-steps) into tensor
 //              memory, commits to an mbarrier, refills the K buffers;
-//   4 warps    each thread owns one query row (its TMEM lane): row maximum,
-//              p = 2^(s*c - m), running sum, p split into bf16 hi/lo and
-//              stored back over the scores in tensor memory;
+//   8 warps    two threads per query row (its TMEM lane), 64 keys each: row
+//              maximum (exchanged through shared memory), p = 2^(s*c - m),
+//              running sum, p split into bf16 hi/lo and stored back over the
+//              scores in tensor memory;
 //   thread 0   issues O_j = P V as 24 MMAs with P read from tensor memory and
 //              V (keys x 64, MN-major) from shared memory; refills V;
-//   4 warps    o = o * 2^(m_old - m_new) + O_j in registers.
+//   8 warps    o = o * 2^(m_old - m_new) + O_j in registers (32 columns each).
 // Every wait on an mbarrier is bounded (tc_ptx.cuh); a timeout raises the
 // CTA's abort flag, the CTA frees its tensor memory, writes the status word
 // and returns.
@@ -54,6 +55,7 @@ constexpr int kTDh = 64;            // head size
 constexpr int kTile = 128 * 128;    // bytes of one 128-row x 64-bf16 tile
 constexpr int kTcAttSmem = 6 * kTile + 1024;
 constexpr uint32_t kTmemColsAtt = 256; // S/P: 0..127, O_j: 128..191
+constexpr int kTcAttThreads = 256;     // two threads per query row
 
 // D = A * B (+ D) with A from shared memory.
 __device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t adesc,
@@ -107,6 +109,25 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float a, float b) {
   return r;
 }
 
+// Barrier between the two warps (64 threads) that share a lane quadrant;
+// named barriers 1..4, constant ids so that only those are reserved.
+__device__ __forceinline__ void pair_barrier(int quad) {
+  switch (quad) {
+  case 0:
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    break;
+  case 1:
+    asm volatile("bar.sync 2, 64;" ::: "memory");
+    break;
+  case 2:
+    asm volatile("bar.sync 3, 64;" ::: "memory");
+    break;
+  default:
+    asm volatile("bar.sync 4, 64;" ::: "memory");
+    break;
+  }
+}
+
 // Instruction descriptor of tcgen05.mma kind::f16 with bf16 operands and an
 // fp32 accumulator, M = 128; b_mn_major selects an MN-major (transposed) B.
 __host__ __device__ constexpr uint32_t att_idesc(int n, int b_mn_major) {
@@ -114,7 +135,7 @@ __host__ __device__ constexpr uint32_t att_idesc(int n, int b_mn_major) {
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(kTcAttThreads, 2)
     attention_tc_kernel(const __grid_constant__ CUtensorMap map_hi,
         const __grid_constant__ CUtensorMap map_lo, int32_t q_col, int32_t k_col,
         int32_t v_col, int64_t S, int64_t heads, float scale_log2e,
@@ -124,8 +145,14 @@ __global__ void __launch_bounds__(128, 2)
   __shared__ uint64_t bar_q, bar_k, bar_v, bar_s, bar_o;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ float xch[2][kTQ]; // row maximum / row sum of each half of the keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Warps w and w + 4 share the 32 query rows (TMEM lanes) of quadrant w & 3:
+  // `half` 0 takes keys 0..63 of every block and output columns 0..31, half 1
+  // the rest.
+  const int quad = warp & 3, half = warp >> 2;
+  const int row = quad * 32 + lane;
   const uint64_t t0 = global_timer();
   const int64_t bh = blockIdx.y;
   const int64_t b = bh / heads, h = bh % heads;
@@ -157,7 +184,8 @@ __global__ void __launch_bounds__(128, 2)
   const uint32_t tmem = tmem_slot;
   const uint32_t t_s = tmem;          // scores, then P, columns 0..127
   const uint32_t t_o = tmem + 128u;   // P V of the current key block
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+  const int kc0 = half * (kTK / 2); // first key column of this thread's share
   volatile int *abortp = &abort_flag;
 
   if (tid == 0) {
@@ -175,9 +203,9 @@ __global__ void __launch_bounds__(128, 2)
   constexpr uint32_t kIdescQK = att_idesc(kTK, 0);
   constexpr uint32_t kIdescPV = att_idesc(kTDh, 1);
 
-  float o[kTDh];
+  float o[kTDh / 2];
 #pragma unroll
-  for (int i = 0; i < kTDh; ++i)
+  for (int i = 0; i < kTDh / 2; ++i)
     o[i] = 0.0f;
   float m_run = -INFINITY; // running maximum of s * scale * log2(e)
   float l_run = 0.0f;      // running sum of p
@@ -215,11 +243,11 @@ __global__ void __launch_bounds__(128, 2)
       break;
     tcgen05_fence_after();
 
-    // ---- online softmax of this thread's row ----
+    // ---- online softmax: this thread's half of its row ----
     __syncwarp(); // tcgen05.ld / st are warp-collective: enter them converged
     float mx = -INFINITY;
 #pragma unroll 1
-    for (int c = 0; c < kTK; c += 32) {
+    for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
       uint32_t v[32];
       tmem_ld32(t_s + lane_base + (uint32_t)c, v);
       tmem_ld_wait();
@@ -227,13 +255,18 @@ __global__ void __launch_bounds__(128, 2)
       for (int i = 0; i < 32; ++i)
         mx = fmaxf(mx, __uint_as_float(v[i]));
     }
+    // Row maximum over both halves (the two threads of a row sit in warps w
+    // and w + 4: a 64-thread named barrier per quadrant).
+    xch[half][row] = mx;
+    pair_barrier(quad);
+    mx = fmaxf(mx, xch[half ^ 1][row]);
     const float m_new = fmaxf(m_run, __fmul_rn(mx, scale_log2e));
     const float resc = ex2_approx(__fsub_rn(m_run, m_new)); // 0 on the first block
     m_run = m_new;
     const float neg_m = -m_new;
     float psum = 0.0f;
 #pragma unroll 1
-    for (int c = 0; c < kTK; c += 32) {
+    for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
       uint32_t v[32];
       tmem_ld32(t_s + lane_base + (uint32_t)c, v);
       tmem_ld_wait();
@@ -292,25 +325,27 @@ __global__ void __launch_bounds__(128, 2)
       break;
     tcgen05_fence_after();
     __syncwarp();
-#pragma unroll
-    for (int c = 0; c < kTDh; c += 32) {
+    {
       uint32_t v[32];
-      tmem_ld32(t_o + lane_base + (uint32_t)c, v);
+      tmem_ld32(t_o + lane_base + (uint32_t)(half * 32), v);
       tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        o[c + i] = __fmaf_rn(o[c + i], resc, __uint_as_float(v[i]));
+        o[i] = __fmaf_rn(o[i], resc, __uint_as_float(v[i]));
     }
     tcgen05_fence_before();
   }
 
   if (ok) {
-    // Normalise, store this thread's row, fold it into the running range.
-    const float inv = __fdiv_rn(1.0f, l_run);
-    float *dst = out + ((int64_t)row_q + tid) * ld_out + h * kTDh;
+    // Row sum over both halves, then normalise and store this thread's 32
+    // output columns and fold them into the running range.
+    xch[half][row] = l_run;
+    pair_barrier(quad);
+    const float inv = __fdiv_rn(1.0f, __fadd_rn(xch[0][row], xch[1][row]));
+    float *dst = out + ((int64_t)row_q + row) * ld_out + h * kTDh + half * 32;
     float lo = INFINITY, hi = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < kTDh; i += 4) {
+    for (int i = 0; i < kTDh / 2; i += 4) {
       float4 v = make_float4(__fmul_rn(o[i], inv), __fmul_rn(o[i + 1], inv),
           __fmul_rn(o[i + 2], inv), __fmul_rn(o[i + 3], inv));
       *reinterpret_cast<float4 *>(dst + i) = v;
@@ -397,7 +432,7 @@ int launch_attention_tc(const void *hi, const void *lo, int64_t ld_planes,
     return fail(OMCUDA_ENOMEM, "Attention: cannot allocate the status word");
   dim3 grid((unsigned)(S / kTQ), (unsigned)(B * heads));
   const float scale_log2e = scale * 1.4426950408889634f;
-  attention_tc_kernel<<<grid, 128, kTcAttSmem, st>>>(map_hi, map_lo, (int32_t)q_col,
+  attention_tc_kernel<<<grid, kTcAttThreads, kTcAttSmem, st>>>(map_hi, map_lo, (int32_t)q_col,
       (int32_t)k_col, (int32_t)v_col, S, heads, scale_log2e, out, ld_out,
       (uint32_t *)out_range, status);
   OMCUDA_CHECK_LAUNCH("attention_tc_kernel");

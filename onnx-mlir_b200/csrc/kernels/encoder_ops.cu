@@ -160,12 +160,6 @@ __global__ void __launch_bounds__(256)
 
 // ---- elementwise -------------------------------------------------------------------
 
-__device__ __forceinline__ float gelu_one(float x) {
-  float h = __fmul_rn(0.5f, x);
-  float e = erff(__fmul_rn(x, 0.70710678118654752440f));
-  return __fmul_rn(h, __fadd_rn(1.0f, e));
-}
-
 __global__ void __launch_bounds__(256)
     gelu_kernel(const float *__restrict__ x, int64_t n, float *__restrict__ y) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -174,17 +168,17 @@ __global__ void __launch_bounds__(256)
     const int64_t n4 = n >> 2;
     for (int64_t i = tid; i < n4; i += stride) {
       float4 v = reinterpret_cast<const float4 *>(x)[i];
-      v.x = gelu_one(v.x);
-      v.y = gelu_one(v.y);
-      v.z = gelu_one(v.z);
-      v.w = gelu_one(v.w);
+      v.x = gelu_erf(v.x);
+      v.y = gelu_erf(v.y);
+      v.z = gelu_erf(v.z);
+      v.w = gelu_erf(v.w);
       reinterpret_cast<float4 *>(y)[i] = v;
     }
     for (int64_t i = (n4 << 2) + tid; i < n; i += stride)
-      y[i] = gelu_one(x[i]);
+      y[i] = gelu_erf(x[i]);
   } else {
     for (int64_t i = tid; i < n; i += stride)
-      y[i] = gelu_one(x[i]);
+      y[i] = gelu_erf(x[i]);
   }
 }
 

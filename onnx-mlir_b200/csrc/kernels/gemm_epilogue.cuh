@@ -113,13 +113,6 @@ __device__ __forceinline__ int32_t epi_int(
   return (int32_t)v;
 }
 
-__device__ __forceinline__ float gelu_erf(float x) {
-  // 0.5*x * (1 + erf(x * (1/sqrt(2)))), Elementwise.cpp:358-388.
-  float h = __fmul_rn(0.5f, x);
-  float e = erff(__fmul_rn(x, 0.70710678118654752440f));
-  return __fmul_rn(h, __fadd_rn(1.0f, e));
-}
-
 __device__ __forceinline__ float epi_dequant(const EpiParams &p,
     const EpiScalars &s, int32_t v, int64_t n) {
   float f = __int2float_rn(v); // arith.sitofp

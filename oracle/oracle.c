@@ -491,6 +491,15 @@ void orc_ref_shaped_matmul_integer(const uint8_t *A, const int8_t *B, int64_t M,
   free(B32);
 }
 
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0)
+    omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int orc_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -155,6 +155,9 @@ void orc_ref_shaped_matmul_integer(const uint8_t *A, const int8_t *B, int64_t M,
     int64_t N, int64_t K, int32_t a_zp, int32_t *Y, int threads);
 
 int orc_max_threads(void);
+/* Number of OpenMP threads later calls use (launchers such as torchrun export
+ * OMP_NUM_THREADS=1; the timed CPU baseline sets the host's core count). */
+void orc_set_threads(int n);
 
 /* Exhaustive check that orc_round_even(x) == rintf(x) for every finite float
  * (signs of zero aside); returns the number of mismatches. */
