@@ -293,6 +293,9 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
     // 64- and 32-byte swizzle), as the store's tensor map expects.
     constexpr uint32_t kSwzMask = (uint32_t)kRowB / 16u - 1u;
     const uint32_t row_off = (uint32_t)lane * kRowB;
+    // The XOR term of this thread's row (pieces of a row stay inside it).
+    const uint32_t swz = ((row_off >> 7) & kSwzMask) << 4;
+    const uint32_t my_row = slab0 + row_off;
     const bool warp_in = m_warp < p.M;
 #pragma unroll 1
     for (int g = 0; g < kSlabsPerHalf; ++g) {
@@ -318,29 +321,24 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
         if (kSplit) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint32_t off = row_off + (uint32_t)j * 16u;
-            const uint32_t so = off ^ (((off >> 7) & kSwzMask) << 4);
-            st_shared_v4(slab0 + so, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-            st_shared_v4(slab0 + 2048u + so, v[16 + 4 * j], v[17 + 4 * j],
-                v[18 + 4 * j], v[19 + 4 * j]);
+            const uint32_t so = my_row + (((uint32_t)j * 16u) ^ swz);
+            st_shared_v4(so, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            st_shared_v4(so + 2048u, v[16 + 4 * j], v[17 + 4 * j], v[18 + 4 * j],
+                v[19 + 4 * j]);
           }
         } else if (kOutBytes == 4) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t off = row_off + (uint32_t)j * 16u;
-            st_shared_v4(slab0 + (off ^ (((off >> 7) & kSwzMask) << 4)), v[4 * j],
-                v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          }
+          for (int j = 0; j < 8; ++j)
+            st_shared_v4(my_row + (((uint32_t)j * 16u) ^ swz), v[4 * j], v[4 * j + 1],
+                v[4 * j + 2], v[4 * j + 3]);
         } else {
           uint32_t w[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             w[j] = v[4 * j] | (v[4 * j + 1] << 8) | (v[4 * j + 2] << 16) |
                    (v[4 * j + 3] << 24);
-          const uint32_t off0 = row_off + (uint32_t)cc;
-          const uint32_t off1 = off0 + 16u;
-          st_shared_v4(slab0 + (off0 ^ (((off0 >> 7) & kSwzMask) << 4)), w[0], w[1], w[2], w[3]);
-          st_shared_v4(slab0 + (off1 ^ (((off1 >> 7) & kSwzMask) << 4)), w[4], w[5], w[6], w[7]);
+          st_shared_v4(my_row + ((uint32_t)cc ^ swz), w[0], w[1], w[2], w[3]);
+          st_shared_v4(my_row + (((uint32_t)cc + 16u) ^ swz), w[4], w[5], w[6], w[7]);
         }
       }
       fence_proxy_async_smem(); // the slab was written through the generic proxy
@@ -507,12 +505,9 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
           const uint32_t sb = sa + Cfg::kABytes;
-#pragma unroll
-          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-            const uint64_t adesc = make_smem_desc(sa + kk * kUmmaK);
-            const uint64_t bdesc = make_smem_desc(sb + kk * kUmmaK);
-            umma_i8(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
-          }
+          static_assert(kBK / kUmmaK == 4, "four K slices per stage");
+          umma_i8_x4(d_tmem, make_smem_desc(sa), make_smem_desc(sb), idesc,
+              kb != 0 ? 1u : 0u);
           umma_commit(smem_u32(&bar_empty[stage]));
           if (++stage == kStages) {
             stage = 0;
@@ -717,12 +712,9 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kABytes;
-#pragma unroll
-          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-            const uint64_t adesc = make_smem_desc(sa + kk * kUmmaK);
-            const uint64_t bdesc = make_smem_desc(sb + kk * kUmmaK);
-            umma_i8_pair(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
-          }
+          static_assert(kBK / kUmmaK == 4, "four K slices per stage");
+          umma_i8_pair_x4(d_tmem, make_smem_desc(sa), make_smem_desc(sb), idesc,
+              kb != 0 ? 1u : 0u);
           umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
           if (++stage == kStages) {
             stage = 0;

@@ -136,6 +136,33 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc,
                : "memory");
 }
 
+// Four MMAs over the four 32-byte K slices of one 128-byte operand row,
+// issued back to back from one asm block: a lone thread's instructions between
+// two tcgen05.mma (descriptor arithmetic, predicate set-up) delay the next
+// issue by tens of cycles each, and the tensor pipe idles meanwhile.  The
+// descriptors of slice k are those of slice 0 plus 2 k (32 bytes >> 4).
+__device__ __forceinline__ void umma_i8_x4(uint32_t d_tmem, uint64_t adesc,
+    uint64_t bdesc, uint32_t idesc, uint32_t accumulate_first) {
+  asm volatile("{\n\t"
+               ".reg .pred p, t;\n\t"
+               ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "setp.eq.b32 t, 0, 0;\n\t"
+               "add.u64 a1, %1, 2;\n\t"
+               "add.u64 a2, %1, 4;\n\t"
+               "add.u64 a3, %1, 6;\n\t"
+               "add.u64 b1, %2, 2;\n\t"
+               "add.u64 b2, %2, 4;\n\t"
+               "add.u64 b3, %2, 6;\n\t"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], a1, b1, %3, t;\n\t"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], a2, b2, %3, t;\n\t"
+               "tcgen05.mma.cta_group::1.kind::i8 [%0], a3, b3, %3, t;\n\t"
+               "}" ::"r"(d_tmem),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
+               : "memory");
+}
+
 // Arrives on the mbarrier once every tcgen05.mma issued so far by this thread
 // has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -244,6 +271,29 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc,
                "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
                "}" ::"r"(d_tmem),
                "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+// The same four-slice issue for the CTA pair.
+__device__ __forceinline__ void umma_i8_pair_x4(uint32_t d_tmem, uint64_t adesc,
+    uint64_t bdesc, uint32_t idesc, uint32_t accumulate_first) {
+  asm volatile("{\n\t"
+               ".reg .pred p, t;\n\t"
+               ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "setp.eq.b32 t, 0, 0;\n\t"
+               "add.u64 a1, %1, 2;\n\t"
+               "add.u64 a2, %1, 4;\n\t"
+               "add.u64 a3, %1, 6;\n\t"
+               "add.u64 b1, %2, 2;\n\t"
+               "add.u64 b2, %2, 4;\n\t"
+               "add.u64 b3, %2, 6;\n\t"
+               "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+               "tcgen05.mma.cta_group::2.kind::i8 [%0], a1, b1, %3, t;\n\t"
+               "tcgen05.mma.cta_group::2.kind::i8 [%0], a2, b2, %3, t;\n\t"
+               "tcgen05.mma.cta_group::2.kind::i8 [%0], a3, b3, %3, t;\n\t"
+               "}" ::"r"(d_tmem),
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
                : "memory");
 }
 
