@@ -40,6 +40,18 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 L2_FLUSH_BYTES = 256 << 20
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the int8 GEMM kernel from ncu
+# captures of this script, bytes per launch (encoders: mean over the four GEMM
+# launches of a layer).  The captures and their commands are summarised in
+# profiles/ (gemm_*.md, bert_large_dram_traffic.md).  Outputs that are still
+# in the 126 MB L2 when a kernel ends are not in these counts.
+NCU_GEMM_DRAM_BYTES = {
+    "bert_large": 1391.2e6,
+    "bert_base": 7.57e6,
+    "mmi_4096": 51.85e6,
+    "qlinear_c2": 37.66e6,
+}
+
 
 def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -304,6 +316,12 @@ class EncoderWorkload:
         self.h2d = T * c["H"] * 4
         self.d2h = T * c["H"] * 4
         self.launches_per_step = None
+        # Algorithmic bytes of the four int8 GEMM launches of a layer (A + B +
+        # output; the QKV projection writes two bf16 planes = 4 bytes per
+        # element, the others f32), averaged per launch.
+        H, F = c["H"], c["F"]
+        shapes = [(3 * H, H), (H, H), (F, H), (H, F)]      # (N, K)
+        self.gemm_bytes = sum(T * K + K * N + 4 * T * N for N, K in shapes) / 4.0
         env.torch.cuda.synchronize()
 
     def step(self, _ev=None):
@@ -399,7 +417,7 @@ def run_gpu(args):
         achieved = gemm_ops_total / (gemm_ms_total * 1e-3) / 1e12
         roof_extra = {"launches_timed": gemm_n, "avg_launch_ms": gemm_ms,
                       "share_of_step": gemm_ms_total / ms}
-        algo_bytes = None
+        algo_bytes = wl.gemm_bytes
     else:
         gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_evs) / args.steps
         achieved = wl.ops / (gemm_ms * 1e-3) / 1e12
@@ -425,7 +443,8 @@ def run_gpu(args):
         "peak_source": "2 x %s TFLOP/s bf16 cuBLAS burst (%s); an int8 figure "
                        "is not in MEASURED_PEAKS.json" % (peaks["bf16_tflops"],
                                                           peaks["source"]),
-        "algorithmic_bytes": algo_bytes, "traffic": None}
+        "algorithmic_bytes": algo_bytes,
+        "traffic": NCU_GEMM_DRAM_BYTES.get(args.workload)}
     roofline.update(roof_extra)
     out = {
         "metric": wl.metric, "value": value, "unit": wl.unit,
