@@ -331,7 +331,9 @@ int omcudaDevAttentionBf16(const void *hi, const void *lo, int64_t ld_planes,
  * DynamicQuantizeLinear that follows does not need its own reduction pass.
  * omcudaDevRangeInit arms `count` ranges; omcudaDevQuantizeFromRange derives
  * scale / zero point from one (exactly as DynamicQuantizeLinear.cpp:43-84
- * does from the reduced min/max), re-arms it and quantizes x. */
+ * does from the reduced min/max), writes them to params / y_scale / y_zp and
+ * quantizes x, in one launch.  The range is left as it is: arm it again
+ * before its producer runs a second time. */
 int omcudaDevRangeInit(void *ranges, int64_t count, void *stream);
 int omcudaDevQuantizeFromRange(const float *x, int64_t n, void *range,
     uint8_t *y, float *params /* 2 floats */, float *y_scale, uint8_t *y_zp,

@@ -145,27 +145,6 @@ __global__ void __launch_bounds__(kDqlThreads)
   }
 }
 
-// Scale / zero point from a running range kept by a producer's epilogue
-// (ordered-uint encoding, see f32_to_ordered); re-arms the range.
-__global__ void dql_params_from_range_kernel(uint32_t *__restrict__ range,
-    float *__restrict__ params, float *__restrict__ y_scale,
-    uint8_t *__restrict__ y_zp) {
-  if (threadIdx.x != 0 || blockIdx.x != 0)
-    return;
-  float lo = ordered_to_f32(range[0]);
-  float hi = ordered_to_f32(range[1]);
-  float s, z;
-  dql_params_from_range(lo, hi, &s, &z);
-  params[0] = s;
-  params[1] = z;
-  if (y_scale)
-    *y_scale = s;
-  if (y_zp)
-    *y_zp = (uint8_t)(unsigned int)z;
-  range[0] = 0xffffffffu; // +inf side: any value lowers it
-  range[1] = 0u;          // -inf side: any value raises it
-}
-
 // One element exactly as the reference computes it
 // (QuantizeLinear.cpp:124-145): IEEE divide, round half even, add the zero
 // point, clip, convert.
@@ -244,16 +223,39 @@ __device__ __forceinline__ uint32_t quantize_four(float4 v, const QuantConsts &c
          (quantize_one<kSigned>(v.w, c) << 24);
 }
 
+// Where the range-driven form of the kernel leaves its scalars.
+struct QuantOutputs {
+  float *params;  // {scale, zero point as float}
+  float *y_scale; // the op's y_scale output, may be null
+  uint8_t *y_zp;  // the op's y_zero_point output, may be null
+};
+
 // params: {scale, zp as float}.  If zp8 is non-NULL the zero point is read
-// from it instead (QuantizeLinear with a given 8-bit zero point).
+// from it instead (QuantizeLinear with a given 8-bit zero point).  If range is
+// non-NULL, scale and zero point are derived from that running {min,max}
+// (ordered-uint encoding, see f32_to_ordered) as DynamicQuantizeLinear does.
 template <bool kSigned>
 __global__ void __launch_bounds__(kDqlThreads)
     quantize_kernel(const float *__restrict__ x, int64_t n,
         uint8_t *__restrict__ y, const float *__restrict__ params,
         const float *__restrict__ scale_ptr, const void *__restrict__ zp8,
-        int has_zp) {
+        int has_zp, const uint32_t *__restrict__ range, QuantOutputs outs) {
   float scale, zp_f;
-  if (params) {
+  if (range) {
+    // Scale and zero point straight from a producer's running range (every
+    // thread derives the same two scalars; block 0 also publishes them for
+    // the ops that follow).
+    dql_params_from_range(ordered_to_f32(__ldg(range)), ordered_to_f32(__ldg(range + 1)),
+        &scale, &zp_f);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      outs.params[0] = scale;
+      outs.params[1] = zp_f;
+      if (outs.y_scale)
+        *outs.y_scale = scale;
+      if (outs.y_zp)
+        *outs.y_zp = (uint8_t)(unsigned int)zp_f; // fptoui; zp_f is in [0,255]
+    }
+  } else if (params) {
     scale = __ldg(params);
     zp_f = __ldg(params + 1);
   } else {
@@ -325,15 +327,8 @@ int launch_quantize_with_params(const float *x, int64_t n, uint8_t *y,
     const float *params, cudaStream_t st) {
   int grid = grid_for(n, kDqlThreads * 16);
   quantize_kernel<false><<<grid, kDqlThreads, 0, st>>>(
-      x, n, y, params, nullptr, nullptr, 1);
+      x, n, y, params, nullptr, nullptr, 1, nullptr, QuantOutputs{});
   OMCUDA_CHECK_LAUNCH("quantize_kernel");
-  return OMCUDA_OK;
-}
-
-int launch_params_from_range(uint32_t *range, float *params, float *y_scale,
-    uint8_t *y_zp, cudaStream_t st) {
-  dql_params_from_range_kernel<<<1, 32, 0, st>>>(range, params, y_scale, y_zp);
-  OMCUDA_CHECK_LAUNCH("dql_params_from_range_kernel");
   return OMCUDA_OK;
 }
 
@@ -364,10 +359,14 @@ extern "C" int omcudaDevQuantizeFromRange(const float *x, int64_t n, void *range
   if (n < 0 || (n > 0 && (!x || !y)) || !range || !params)
     return fail(OMCUDA_EINVAL, "QuantizeFromRange: bad argument");
   cudaStream_t st = (cudaStream_t)stream;
-  int rc = launch_params_from_range((uint32_t *)range, params, y_scale, y_zp, st);
-  if (rc != OMCUDA_OK || n == 0)
-    return rc;
-  return launch_quantize_with_params(x, n, y, params, st);
+  // One launch: every block derives the scalars from the range itself (a
+  // block of its own when there is nothing to quantize).
+  int grid = grid_for(n, kDqlThreads * 16);
+  QuantOutputs outs{params, y_scale, y_zp};
+  quantize_kernel<false><<<grid, kDqlThreads, 0, st>>>(
+      x, n, y, nullptr, nullptr, nullptr, 1, (const uint32_t *)range, outs);
+  OMCUDA_CHECK_LAUNCH("quantize_kernel");
+  return OMCUDA_OK;
 }
 
 extern "C" int omcudaDevQuantizeLinear(const float *x, int64_t n, void *y,
@@ -380,10 +379,10 @@ extern "C" int omcudaDevQuantizeLinear(const float *x, int64_t n, void *y,
   int grid = grid_for(n, kDqlThreads * 16);
   if (y_signed)
     quantize_kernel<true><<<grid, kDqlThreads, 0, st>>>(
-        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr);
+        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr, nullptr, QuantOutputs{});
   else
     quantize_kernel<false><<<grid, kDqlThreads, 0, st>>>(
-        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr);
+        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr, nullptr, QuantOutputs{});
   OMCUDA_CHECK_LAUNCH("quantize_kernel");
   return OMCUDA_OK;
 }

@@ -941,7 +941,16 @@ int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
 
 // A long K loop hides the epilogue behind the MMAs and wants pipeline depth;
 // a short one is bounded by the epilogue and wants more warps on it.
-inline bool want_wide_epilogue(const omcudaGemmArgs &a) { return a.K < 2048; }
+// (OMCUDA_GEMM_EW=8|16 overrides the choice, for experiments.)
+inline bool want_wide_epilogue(const omcudaGemmArgs &a) {
+  static const int forced = [] {
+    const char *s = getenv("OMCUDA_GEMM_EW");
+    return s ? atoi(s) : 0;
+  }();
+  if (forced == 8 || forced == 16)
+    return forced == 16;
+  return a.K < 2048;
+}
 
 template <int BN, int EPI>
 int launch_bn_epi(const omcudaGemmArgs &a, cudaStream_t st) {

@@ -19,8 +19,6 @@ bool pool_owns(const void *p);
 // dql.cu
 int launch_quantize_with_params(const float *x, int64_t n, uint8_t *y,
     const float *params, cudaStream_t st);
-int launch_params_from_range(uint32_t *range, float *params, float *y_scale,
-    uint8_t *y_zp, cudaStream_t st);
 
 // gemm_tc.cu / gemm_simt.cu
 bool gemm_tc_supported(const omcudaGemmArgs &a);
