@@ -16,6 +16,8 @@ shapes and value distributions of the reference configurations):
   bert_large  24 layers, hidden 1024, 16 heads, FFN 4096, seq 512, batch 256;
               metric sequences/s.  With N > 1 the per-rank outputs are joined
               by one NCCL all-gather inside the step.
+  mmi_sweep   the 15-shape MatMulInteger sweep (M x (K,N)), per-shape list in
+              the JSON line; rows of the M >= 4096 members sharded with N > 1.
 
 A step is one pass of the workload's graph over one batch.  `value` is timed
 with inputs resident in HBM; `e2e` runs the same graph through the krnl.call
@@ -156,12 +158,12 @@ class LinearWorkload:
     """DQL -> int8 GEMM -> dequant (mmi_4096) or QLinearMatMul (qlinear_c2)."""
     metric, unit, dtype = "MatMulInteger int8 TOPS", "TOPS", "u8*s8->s32"
 
-    def __init__(self, env, name, seed):
+    def __init__(self, env, name, seed, shape=None):
         self.env, self.name = env, name
         torch, dev = env.torch, env.dev
         rng = np.random.default_rng(seed)
-        if name == "mmi_4096":
-            self.M = self.N = self.K = 4096
+        if name == "mmi_4096" or shape is not None:
+            self.M, self.K, self.N = shape if shape is not None else (4096, 4096, 4096)
             self.kind = "dynquant"
             self.Xh = rng.normal(size=(self.M, self.K)).astype(np.float32)
             self.Wh = rng.integers(-127, 128, (self.K, self.N), dtype=np.int8)
@@ -467,6 +469,113 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+SWEEP_M = (1, 16, 256, 4096, 16384)
+SWEEP_KN = ((4096, 4096), (4096, 14336), (14336, 4096))
+
+
+def run_sweep(args):
+    """The GEMM sweep of the reference configurations: DQL -> MatMulInteger ->
+    dequant at M in {1,16,256,4096,16384} x (K,N) in {(4096,4096),
+    (4096,14336), (14336,4096)}; with N GPUs the rows of the M >= 4096 members
+    are sharded (each rank runs M / N rows), the others run replicated.  One
+    JSON line: aggregate TOPS (sum of ops / sum of times) and a per-shape list.
+    Small M is bound by the read of the K*N int8 weights, so each shape also
+    reports the bytes/s of that read."""
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    env = GpuEnv(local_rank)
+    peaks = load_peaks()
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = env.m.launch_count()
+    rows, tot_ops, tot_ms, tot_e2e_ops, tot_e2e_ms = [], 0.0, 0.0, 0.0, 0.0
+    for K, N in SWEEP_KN:
+        for M in SWEEP_M:
+            m_rank = M // world if (M >= 4096 and world > 1) else M
+            wl = LinearWorkload(env, "mmi_%dx%dx%d" % (M, K, N), 42 + rank,
+                                shape=(m_rank, K, N))
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True),
+                    torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                   for _ in range(args.steps)]
+            for _ in range(args.warmup):
+                env.flush_l2()
+                wl.step()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            for e in evs:
+                env.flush_l2()
+                e[0].record(env.stream)
+                wl.step((e[1], e[2]))
+                e[3].record(env.stream)
+            torch.cuda.synchronize()
+            ms = sum(e[0].elapsed_time(e[3]) for e in evs) / args.steps
+            gemm_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+            e2e_n = 2
+            wl.step_e2e()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(e2e_n):
+                wl.step_e2e()
+            env.m.synchronize()
+            e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_n
+            if world > 1:
+                t = torch.tensor([ms, gemm_ms, e2e_ms], dtype=torch.float64, device=env.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms, gemm_ms, e2e_ms = (float(v) for v in t.tolist())
+            mult = world if m_rank != M else 1     # sharded members: all ranks' rows
+            ops = wl.ops * mult
+            rows.append({"M": M, "K": K, "N": N, "rows_per_gpu": m_rank,
+                         "ms_per_step": ms, "tops": ops / ms / 1e9,
+                         "gemm_ms": gemm_ms, "gemm_tops": ops / gemm_ms / 1e9,
+                         "gemm_frac_of_int8_peak": wl.ops / gemm_ms / 1e9 / int8_peak,
+                         "weight_read_gbs": K * N / gemm_ms / 1e6,
+                         "e2e_ms": e2e_ms, "e2e_tops": ops / e2e_ms / 1e9})
+            tot_ops += ops
+            tot_ms += ms
+            tot_e2e_ops += ops
+            tot_e2e_ms += e2e_ms
+            del wl
+            env.m.lib().omcudaForgetConstants()   # the weights' host buffer is gone
+            torch.cuda.empty_cache()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = env.m.launch_count() - launches0
+    if rank == 0:
+        big = [r for r in rows if r["M"] >= 4096]
+        print(json.dumps({
+            "metric": LinearWorkload.metric, "value": tot_ops / tot_ms / 1e9, "unit": "TOPS",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": tot_ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": LinearWorkload.dtype, "data": "synthetic",
+            "config": {"workload": "mmi_sweep", "shapes": len(rows),
+                       "l2": "flushed between timed iterations (256 MiB write)",
+                       "graph": "DynamicQuantizeLinear->MatMulInteger->Cast/Mul",
+                       "sharding": "rows of the M >= 4096 members split over the GPUs"},
+            "e2e": {"value": tot_e2e_ops / tot_e2e_ms / 1e9, "unit": "TOPS",
+                    "h2d_bytes_per_step": None, "d2h_bytes_per_step": None, "steps": 2},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"kernel": "gemm_i8_tc_kernel", "bound": "tensor",
+                         "achieved": sum(r["gemm_tops"] * r["gemm_ms"] for r in big) /
+                                     sum(r["gemm_ms"] for r in big) / world,
+                         "peak": int8_peak, "unit": "TOP/s",
+                         "frac": sum(r["gemm_tops"] * r["gemm_ms"] for r in big) /
+                                 sum(r["gemm_ms"] for r in big) / world / int8_peak,
+                         "peak_source": "2 x bf16 cuBLAS burst (%s); members with M >= 4096, "
+                                        "per GPU" % peaks["source"],
+                         "traffic": None},
+            "sweep": rows}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def cpu_baseline(workload, wl=None, reps=1):
     """Times the oracle's reference-shaped CPU code on a bounded sample."""
     import oracle_lib
@@ -549,11 +658,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="omcuda", choices=["omcuda", "reference"])
     ap.add_argument("--workload", default="bert_large",
-                    choices=["mmi_4096", "qlinear_c2", "bert_base", "bert_large"])
+                    choices=["mmi_4096", "qlinear_c2", "bert_base", "bert_large",
+                             "mmi_sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "omcuda" else args.warmup
-    if args.impl == "reference":
+    if args.workload == "mmi_sweep":
+        if args.impl == "reference":
+            args.workload = "mmi_4096"   # the CPU arm times the sweep's 4096^3 member
+            run_reference(args)
+        else:
+            run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

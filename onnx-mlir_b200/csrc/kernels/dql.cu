@@ -216,11 +216,42 @@ __device__ __forceinline__ uint32_t quantize_one(float x, const QuantConsts &c) 
   return __float_as_uint(s) & 0xffu;
 }
 
+// Four elements by the exact formula, out of line: the fast path below calls
+// it for the rare float4 that holds a near-tie element, and must not carry the
+// divide's instructions as predicated code.
+template <bool kSigned>
+__device__ __noinline__ uint32_t quantize_four_exact(float4 v, float scale, float zp_f) {
+  return quantize_one_exact<kSigned>(v.x, scale, zp_f) |
+         (quantize_one_exact<kSigned>(v.y, scale, zp_f) << 8) |
+         (quantize_one_exact<kSigned>(v.z, scale, zp_f) << 16) |
+         (quantize_one_exact<kSigned>(v.w, scale, zp_f) << 24);
+}
+
+// quantize_one on the four elements of a float4 with one near-tie test for
+// all of them.
 template <bool kSigned>
 __device__ __forceinline__ uint32_t quantize_four(float4 v, const QuantConsts &c) {
-  return quantize_one<kSigned>(v.x, c) | (quantize_one<kSigned>(v.y, c) << 8) |
-         (quantize_one<kSigned>(v.z, c) << 16) |
-         (quantize_one<kSigned>(v.w, c) << 24);
+  if (!c.fast)
+    return quantize_four_exact<kSigned>(v, c.scale, c.zp_f);
+  const float kMagic = 12582912.0f; // 1.5 * 2^23
+  const float t0 = __fmaf_rn(v.x, c.rcp, kMagic), t1 = __fmaf_rn(v.y, c.rcp, kMagic);
+  const float t2 = __fmaf_rn(v.z, c.rcp, kMagic), t3 = __fmaf_rn(v.w, c.rcp, kMagic);
+  const float d0 = __fmaf_rn(v.x, c.rcp, -__fsub_rn(t0, kMagic));
+  const float d1 = __fmaf_rn(v.y, c.rcp, -__fsub_rn(t1, kMagic));
+  const float d2 = __fmaf_rn(v.z, c.rcp, -__fsub_rn(t2, kMagic));
+  const float d3 = __fmaf_rn(v.w, c.rcp, -__fsub_rn(t3, kMagic));
+  // NaN distances (infinite or NaN inputs) fall through fmaxf and take the
+  // fast path, which saturates them as the exact formula does.
+  const float dmax = fmaxf(fmaxf(fabsf(d0), fabsf(d1)), fmaxf(fabsf(d2), fabsf(d3)));
+  if (dmax > 0.499f) // a near tie, or a value too large for the mantissa trick
+    return quantize_four_exact<kSigned>(v, c.scale, c.zp_f);
+  const float lo = kSigned ? kMagic - 128.0f : kMagic;
+  const float hi = kSigned ? kMagic + 127.0f : kMagic + 255.0f;
+  const uint32_t b0 = __float_as_uint(clipf(__fadd_rn(t0, c.zp_f), lo, hi)) & 0xffu;
+  const uint32_t b1 = __float_as_uint(clipf(__fadd_rn(t1, c.zp_f), lo, hi)) & 0xffu;
+  const uint32_t b2 = __float_as_uint(clipf(__fadd_rn(t2, c.zp_f), lo, hi)) & 0xffu;
+  const uint32_t b3 = __float_as_uint(clipf(__fadd_rn(t3, c.zp_f), lo, hi));
+  return b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
 }
 
 // Where the range-driven form of the kernel leaves its scalars.

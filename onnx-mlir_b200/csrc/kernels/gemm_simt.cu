@@ -347,6 +347,6 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
         "GemmI8: the split-bf16 tail exists on the tensor-core kernel only "
         "(K %% 16 == 0, 16-byte aligned A)");
   bool use_tc = (a.kernel_choice == 1) || a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT ||
-                (a.kernel_choice == 0 && tc_ok && a.M > 16);
+                (a.kernel_choice == 0 && tc_ok && a.M > 4);
   return use_tc ? launch_gemm_tc(a, st) : launch_gemm_simt(a, st);
 }
