@@ -270,6 +270,11 @@ typedef struct {
   void *out_minmax;
   /* 0 = choose; 1 = force the tcgen05 kernel; 2 = force the SIMT kernel. */
   int kernel_choice;
+  /* DEQUANT only: optional f32 [M,N] added last (y = tail(acc) + residual),
+   * the onnx.Add of a residual connection around the linear
+   * (Math/Elementwise.cpp, one more separately rounded fp32 add). May be
+   * NULL. */
+  const float *residual;
 } omcudaGemmArgs;
 
 /* Device status word the GEMM writes on a bounded-wait timeout. */

@@ -11,7 +11,7 @@
 //
 // The three tails:
 //   I32      MatMulInteger result.
-//   DEQUANT  Cast(i32->f32) -> Mul -> [Mul] -> [Add] [-> Gelu]
+//   DEQUANT  Cast(i32->f32) -> Mul -> [Mul] -> [Add] [-> Gelu] [-> Add residual]
 //            (src/Conversion/ONNXToKrnl/Math/Elementwise.cpp:477-486, 358-388);
 //            each fp32 op is rounded on its own (no fma).
 //   DEQUANT_SPLIT  the DEQUANT value x written as two bf16 planes,
@@ -45,6 +45,8 @@ struct EpiParams {
   const float *bias;
   int gelu;
   int32_t y_zp;
+  const float *residual; // f32 [M,N] added after the DEQUANT tail, or nullptr
+  int res_vec_ok;        // residual rows take 16-byte loads
   uint32_t *out_range; // ordered-uint {min,max} or nullptr
   int vec_ok;    // per-column vectors are 16-byte aligned: 128-bit loads allowed
   int line_store; // set by the tensor-core launcher: Y takes 16-byte line stores

@@ -173,6 +173,8 @@ __global__ void __launch_bounds__(256)
       reinterpret_cast<int32_t *>(p.Y)[m * p.N + n] = v;
     } else if (p.kind == OMCUDA_EPI_DEQUANT) {
       float y = epi_dequant(p, sc, v, n);
+      if (p.residual)
+        y = __fadd_rn(y, __ldg(p.residual + m * p.N + n));
       reinterpret_cast<float *>(p.Y)[m * p.N + n] = y;
       lo = fminf(lo, y);
       hi = fmaxf(hi, y);
@@ -207,6 +209,8 @@ EpiParams make_epi_params(const omcudaGemmArgs &a) {
   p.bias = a.bias;
   p.gelu = a.gelu;
   p.y_zp = a.y_zp;
+  p.residual = (a.epilogue == OMCUDA_EPI_DEQUANT) ? a.residual : nullptr;
+  p.res_vec_ok = ((((uintptr_t)a.residual) & 15u) == 0) && (a.N % 4 == 0);
   p.out_range = reinterpret_cast<uint32_t *>(a.out_minmax);
   p.vec_ok = ((((uintptr_t)a.B.colsum | (uintptr_t)a.bias | (uintptr_t)a.sb) & 15u) == 0) &&
              (a.N % 4 == 0);
@@ -330,6 +334,8 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
     return fail(OMCUDA_EINVAL, "GemmI8: b_zp needs the row sums of A");
   if (a.a_zp && a.a_zp_len != 0 && !a.B.colsum)
     return fail(OMCUDA_EINVAL, "GemmI8: a_zp needs the column sums of B");
+  if (a.residual && a.epilogue != OMCUDA_EPI_DEQUANT)
+    return fail(OMCUDA_EINVAL, "GemmI8: a residual goes with the dequant epilogue only");
   if ((a.epilogue == OMCUDA_EPI_DEQUANT || a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT) &&
       (!a.sa || !a.sb))
     return fail(OMCUDA_EINVAL, "GemmI8: dequant epilogue needs both scales");

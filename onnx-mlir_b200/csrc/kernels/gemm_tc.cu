@@ -116,8 +116,8 @@ __device__ __forceinline__ void load_cols32(
 // byte per word).
 template <int EPI>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
-    const EpiScalars &sc, const EpiRow &row, int64_t nc, int valid,
-    uint32_t (&v)[32], float &lo, float &hi) {
+    const EpiScalars &sc, const EpiRow &row, const float *res_row, int64_t nc,
+    int valid, uint32_t (&v)[32], float &lo, float &hi) {
   const bool vec = p.vec_ok != 0;
   if (p.b_zp_len != 0) {
     // - bz[n] * rowsum[m] + K * az * bz[n]  =  bz[n] * (K * az - rowsum[m])
@@ -189,6 +189,13 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
 #pragma unroll
       for (int j = 0; j < 32; ++j)
         f[j] = gelu_erf(f[j]);
+    }
+    if (EPI == OMCUDA_EPI_DEQUANT && res_row) {
+      float r[32];
+      load_cols32(res_row, nc, valid, p.res_vec_ok != 0, r);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        f[j] = __fadd_rn(f[j], r[j]);
     }
     if (p.out_range) {
       if (valid == 32) {
@@ -280,6 +287,7 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
   row.rs = 0;
   if (row_ok)
     row = epi_row(p, m);
+  const float *res_row = (row_ok && p.residual) ? p.residual + m * p.N : nullptr;
   if (use_slab) {
     // Results pass through a shared-memory slab (32 rows per warp, rows of
     // kRowB bytes in the 128-byte-swizzle pattern) and leave with one TMA
@@ -309,7 +317,7 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
         const int64_t nc = ng + cc;
         const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
         if (row_ok && valid > 0)
-          epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
+          epilogue_chunk<EPI>(p, sc, row, res_row, nc, valid, v, lo, hi);
         if (kSplit)
           split_words_bf16(v);
         if (cc == 0) {
@@ -363,7 +371,7 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
       const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
       if (!row_ok || valid <= 0)
         continue;
-      epilogue_chunk<EPI>(p, sc, row, nc, valid, v, lo, hi);
+      epilogue_chunk<EPI>(p, sc, row, res_row, nc, valid, v, lo, hi);
       if (kSplit) {
         split_words_bf16(v);
         uint16_t *dhi = reinterpret_cast<uint16_t *>(p.Y) + m * p.N + nc;
@@ -551,6 +559,13 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         }
         if (src)
           asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
+        // ... and this warp's block of the residual (32 rows x kHalfCols f32)
+        // towards L2: the epilogue reads it one row per thread.
+        if (p.residual && m_warp + lane < p.M) {
+          const float *rr = p.residual + (m_warp + lane) * p.N + n0;
+          for (int c = 0; c < kHalfCols && n0 + c < p.N; c += 32)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(rr + c));
+        }
       }
       if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase, abortp, t0)) {
         ok = false;
@@ -756,6 +771,13 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         }
         if (src)
           asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
+        // ... and this warp's block of the residual (32 rows x kHalfCols f32)
+        // towards L2: the epilogue reads it one row per thread.
+        if (p.residual && m_warp + lane < p.M) {
+          const float *rr = p.residual + (m_warp + lane) * p.N + n0;
+          for (int c = 0; c < kHalfCols && n0 + c < p.N; c += 32)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(rr + c));
+        }
       }
       if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase, abortp, t0)) {
         ok = false;

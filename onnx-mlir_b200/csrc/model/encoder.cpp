@@ -13,11 +13,13 @@
 //                 linears share xq; columns are independent, so the result
 //                 is bit-identical to three launches)
 //     ctx[T,H]  = attention(qkv)              keeps the range of ctx
-//     a[T,H]    = GEMM(quantize(ctx), Wo) dequant + bias
-//     h1        = LayerNorm(x + a)            keeps the range of h1
+//     a[T,H]    = x + GEMM(quantize(ctx), Wo) dequant + bias   (the residual
+//                 add rides in the GEMM's tail for activations beyond L2
+//                 size, inside LayerNorm otherwise)
+//     h1        = LayerNorm(a)                keeps the range of h1
 //     f[T,F]    = GEMM(quantize(h1), W1) dequant + bias + Gelu, keeps range
-//     o[T,H]    = GEMM(quantize(f), W2) dequant + bias
-//     y         = LayerNorm(h1 + o)           keeps the range of y (next x)
+//     o[T,H]    = h1 + GEMM(quantize(f), W2) dequant + bias
+//     y         = LayerNorm(o)                keeps the range of y (next x)
 //
 // DynamicQuantizeLinear needs the min/max of its whole input before it can
 // write a byte.  Instead of a separate reduction pass, each producer folds the
@@ -145,7 +147,8 @@ __global__ void fill_kernel(float *dst, int64_t n, float v) {
 int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
     const float *a_scale, const omcudaPreparedB &B, int64_t M,
     const float *w_scale, int64_t ws_len, const float *bias, int gelu, void *Y,
-    void *out_range, cudaStream_t st, int epilogue = OMCUDA_EPI_DEQUANT) {
+    void *out_range, cudaStream_t st, int epilogue = OMCUDA_EPI_DEQUANT,
+    const float *residual = nullptr) {
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (e->profiling) {
     while (e->ev.size() < e->ev_used + 2) {
@@ -181,6 +184,7 @@ int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
   g.bias = bias;
   g.gelu = gelu;
   g.out_minmax = out_range;
+  g.residual = residual;
   int rc = omcudaDevGemmI8(&g, st);
   if (e1)
     cudaEventRecord(e1, st);
@@ -362,6 +366,7 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
   const bool use_tc_attention =
       omcudaDevAttentionBf16Supported(batch, seq, heads, dh, 3 * H, H) != 0;
   // (the f32 [T,3H] buffer holds the two bf16 [T,3H] planes instead)
+  const bool fuse_residual = (size_t)(T * H) * 4 >= ((size_t)64 << 20);
   void *planes_hi = e->qkv.p;
   void *planes_lo = (uint8_t *)e->qkv.p + (size_t)(T * 3 * H) * 2;
 #define RUN(call)                                                              \
@@ -411,10 +416,15 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
     }
     RUN(omcudaDevQuantizeFromRange((const float *)e->ctx.p, T * H, r_ctx, xq,
         p_ctx, p_ctx + 2, (uint8_t *)(p_ctx + 3), st));
+    // a = [x +] Linear(ctx): the residual add rides in the GEMM's tail when
+    // the activations are too large for L2 (it saves LayerNorm one pass over
+    // HBM); small ones are cheaper to add inside LayerNorm.  Same fp32 add
+    // either way.
     RUN(gemm(e, xq, (const uint8_t *)(p_ctx + 3), p_ctx + 2, L.wo, T,
         (const float *)L.scal.p, 1, (const float *)L.bo.p, 0, (float *)e->a.p,
-        nullptr, st));
-    RUN(omcudaDevLayerNorm(cur, (const float *)e->a.p, T, H,
+        nullptr, st, OMCUDA_EPI_DEQUANT, fuse_residual ? cur : nullptr));
+    RUN(omcudaDevLayerNorm(fuse_residual ? (const float *)e->a.p : cur,
+        fuse_residual ? nullptr : (const float *)e->a.p, T, H,
         (const float *)L.ln1g.p, L.has_ln1b ? (const float *)L.ln1b.p : nullptr,
         eps, (float *)e->h1.p, r_h1, st));
     RUN(omcudaDevQuantizeFromRange((const float *)e->h1.p, T * H, r_h1, xq,
@@ -426,8 +436,10 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
         p_f + 2, (uint8_t *)(p_f + 3), st));
     RUN(gemm(e, xq, (const uint8_t *)(p_f + 3), p_f + 2, L.w2, T,
         (const float *)L.scal.p + 2, 1, (const float *)L.b2.p, 0,
-        (float *)e->o.p, nullptr, st));
-    RUN(omcudaDevLayerNorm((const float *)e->h1.p, (const float *)e->o.p, T, H,
+        (float *)e->o.p, nullptr, st, OMCUDA_EPI_DEQUANT,
+        fuse_residual ? (const float *)e->h1.p : nullptr));
+    RUN(omcudaDevLayerNorm(fuse_residual ? (const float *)e->o.p : (const float *)e->h1.p,
+        fuse_residual ? nullptr : (const float *)e->o.p, T, H,
         (const float *)L.ln2g.p, L.has_ln2b ? (const float *)L.ln2b.p : nullptr,
         eps, nxt, r_y, st));
     cur = nxt;

@@ -36,6 +36,7 @@ class GemmArgs(ctypes.Structure):
         ("y_signed", _i32),
         ("out_minmax", _vp),
         ("kernel_choice", _i32),
+        ("residual", _vp),
     ]
 
 

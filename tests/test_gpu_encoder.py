@@ -73,7 +73,10 @@ def unfused_layer_on_gpu(gpu, x, B, S, H, heads, w):
 
 
 @pytest.mark.parametrize("B,S,H,heads,F,nl", [(2, 40, 128, 2, 256, 2),
-                                              (2, 128, 768, 12, 3072, 2)])
+                                              (2, 128, 768, 12, 3072, 2),
+                                              # 64 MiB of activations: the residual
+                                              # adds move into the GEMM tails
+                                              (256, 512, 128, 2, 256, 1)])
 def test_encoder_equals_unfused_chain_bit_exact(gpu, B, S, H, heads, F, nl):
     layers = make_encoder(12, H, F, nl)
     x = np.random.default_rng(13).normal(size=(B, S, H)).astype(np.float32)

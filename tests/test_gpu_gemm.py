@@ -300,3 +300,36 @@ def test_whole_output_checksums(gpu, orc, M, K, N):
     assert np.array_equal(Y[rows], want)
     As = A.astype(np.int64) - 117
     assert np.array_equal(Y.astype(np.int64).sum(0), As.sum(0) @ B.astype(np.int64))
+
+@pytest.mark.parametrize("M,K,N,choice", [(300, 256, 192, 1), (260, 512, 1000, 1), (3, 100, 70, 2)])
+def test_dequant_tail_with_residual(gpu, M, K, N, choice):
+    # y = tail(acc) + residual, the onnx.Add of a residual connection folded
+    # into the GEMM: one more separately rounded fp32 add, so it must equal
+    # the sum of the plain tail's result and the residual bit for bit.
+    from gpu_util import DevGemm
+    rng = np.random.default_rng(M * N)
+    dg = DevGemm(gpu)
+    A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    res = rng.normal(0, 1, (M, N)).astype(np.float32)
+    pb, keep = dg.prepare(B)
+    dA, dres = dg.dtensor(A), dg.dtensor(res)
+    az = dg.dtensor(np.array([99], np.uint8))
+    sa = dg.dtensor(np.array([0.02], np.float32))
+    sb = dg.dtensor(np.array([0.003], np.float32))
+    bias = dg.dtensor(rng.normal(0, 0.5, N).astype(np.float32))
+    g = dg.dev.GemmArgs()
+    g.M, g.N, g.K = M, N, K
+    g.A, g.a_signed, g.B = dA.data_ptr, 0, pb
+    g.a_zp, g.a_zp_len = az.data_ptr, 1
+    g.sa, g.sb, g.sb_len, g.bias = sa.data_ptr, sb.data_ptr, 1, bias.data_ptr
+    g.kernel_choice, g.epilogue = choice, dg.dev.EPI_DEQUANT
+    Y0 = gpu.Tensor.device_empty((M, N), np.float32)
+    g.Y = Y0.data_ptr
+    dg.dev.gemm_i8(g, dg.stream)
+    Y1 = gpu.Tensor.device_empty((M, N), np.float32)
+    g.Y, g.residual = Y1.data_ptr, dres.data_ptr
+    dg.dev.gemm_i8(g, dg.stream)
+    y0, y1 = Y0.numpy(), Y1.numpy()
+    gpu.synchronize()
+    assert y1.tobytes() == (y0 + res).astype(np.float32).tobytes()
