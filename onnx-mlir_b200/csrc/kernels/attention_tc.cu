@@ -57,27 +57,55 @@ constexpr int kTcAttSmem = 6 * kTile + 1024;
 constexpr uint32_t kTmemColsAtt = 256; // S/P: 0..127, O_j: 128..191
 constexpr int kTcAttThreads = 256;     // two threads per query row
 
-// D = A * B (+ D) with A from shared memory.
-__device__ __forceinline__ void umma_bf16_ss(uint32_t d_tmem, uint64_t adesc,
-    uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// Four MMAs over the four 16-element K slices of a 64-wide K-major operand
+// pair, issued back to back from one asm block (descriptor + 2 per 32-byte
+// slice): instructions between two tcgen05.mma of the lone issuing thread
+// would each delay the next issue.
+__device__ __forceinline__ void umma_bf16_ss_x4(uint32_t d_tmem, uint64_t adesc,
+    uint64_t bdesc, uint32_t idesc, uint32_t accumulate_first) {
   asm volatile("{\n\t"
-               ".reg .pred p;\n\t"
+               ".reg .pred p, t;\n\t"
+               ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
                "setp.ne.b32 p, %4, 0;\n\t"
+               "setp.eq.b32 t, 0, 0;\n\t"
+               "add.u64 a1, %1, 2;\n\t"
+               "add.u64 a2, %1, 4;\n\t"
+               "add.u64 a3, %1, 6;\n\t"
+               "add.u64 b1, %2, 2;\n\t"
+               "add.u64 b2, %2, 4;\n\t"
+               "add.u64 b3, %2, 6;\n\t"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, t;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, t;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, t;\n\t"
                "}" ::"r"(d_tmem),
-               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
                : "memory");
 }
 
-// D = A * B (+ D) with A (128 rows x 16 bf16 = 8 columns) from tensor memory.
-__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem,
-    uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// Four P V MMAs over 64 keys (two 32-key chunks): A (P) from tensor memory at
+// columns a, a + 8, a + 32, a + 40; B (V, MN-major) advances 16 keys = 2048
+// bytes (descriptor + 128) per slice.
+__device__ __forceinline__ void umma_bf16_ts_x4(uint32_t d_tmem, uint32_t a_tmem,
+    uint64_t bdesc, uint32_t idesc, uint32_t accumulate_first) {
   asm volatile("{\n\t"
-               ".reg .pred p;\n\t"
+               ".reg .pred p, t;\n\t"
+               ".reg .b32 a1, a2, a3;\n\t"
+               ".reg .b64 b1, b2, b3;\n\t"
                "setp.ne.b32 p, %4, 0;\n\t"
+               "setp.eq.b32 t, 0, 0;\n\t"
+               "add.u32 a1, %1, 8;\n\t"
+               "add.u32 a2, %1, 32;\n\t"
+               "add.u32 a3, %1, 40;\n\t"
+               "add.u64 b1, %2, 128;\n\t"
+               "add.u64 b2, %2, 256;\n\t"
+               "add.u64 b3, %2, 384;\n\t"
                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, t;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %3, t;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %3, t;\n\t"
                "}" ::"r"(d_tmem),
-               "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+               "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
                : "memory");
 }
 
@@ -223,12 +251,11 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
         // small terms first: Ql Kh, Qh Kl, then Qh Kh
         const uint32_t qa[3] = {s_ql, s_qh, s_qh};
         const uint32_t kb[3] = {s_kh, s_kl, s_kh};
+        static_assert(kTDh == 64, "four K slices per operand row");
 #pragma unroll
         for (int t = 0; t < 3; ++t)
-#pragma unroll
-          for (int kk = 0; kk < kTDh / 16; ++kk)
-            umma_bf16_ss(t_s, make_smem_desc(qa[t] + kk * 32),
-                make_smem_desc(kb[t] + kk * 32), kIdescQK, (t | kk) != 0 ? 1u : 0u);
+          umma_bf16_ss_x4(t_s, make_smem_desc(qa[t]), make_smem_desc(kb[t]), kIdescQK,
+              t != 0 ? 1u : 0u);
         umma_commit(smem_u32(&bar_s));
         ok = mbar_wait(smem_u32(&bar_s), ph, abortp, t0);
         if (ok && j + 1 < nkb) { // the K buffers are free again
@@ -303,14 +330,13 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
         // small terms first: Pl Vh, Ph Vl, then Ph Vh
         const uint32_t pa[3] = {16u, 0u, 0u}; // column offset of lo / hi inside a chunk
         const uint32_t vb[3] = {s_vh, s_vl, s_vh};
+        static_assert(kTK == 128, "two groups of four 16-key slices per block");
 #pragma unroll
-        for (int t = 0; t < 3; ++t)
-#pragma unroll
-          for (int kk = 0; kk < kTK / 16; ++kk) {
-            const uint32_t a_col = (uint32_t)((kk >> 1) * 32 + (kk & 1) * 8) + pa[t];
-            umma_bf16_ts(t_o, t_s + a_col, make_smem_desc(vb[t] + kk * 2048),
-                kIdescPV, (t | kk) != 0 ? 1u : 0u);
-          }
+        for (int t = 0; t < 3; ++t) {
+          const uint64_t dv = make_smem_desc(vb[t]);
+          umma_bf16_ts_x4(t_o, t_s + pa[t], dv, kIdescPV, t != 0 ? 1u : 0u);
+          umma_bf16_ts_x4(t_o, t_s + 64u + pa[t], dv + 512, kIdescPV, 1u);
+        }
         umma_commit(smem_u32(&bar_o));
         ok = mbar_wait(smem_u32(&bar_o), ph, abortp, t0);
         if (ok && j + 1 < nkb) { // the V buffers are free again
