@@ -236,7 +236,17 @@ typedef enum {
    * f32: Y holds hi = bf16(x) as [M,N] bf16, followed by lo = bf16(x - hi) as
    * [M,N] bf16 (2*M*N*2 bytes in all): the operand format of
    * omcudaDevAttentionBf16.  Tensor-core kernel only. */
-  OMCUDA_EPI_DEQUANT_SPLIT = 3
+  OMCUDA_EPI_DEQUANT_SPLIT = 3,
+  /* The two halves of "linear tail -> DynamicQuantizeLinear" without the f32
+   * tensor in between (tensor-core kernel only).  DEQUANT_RANGE computes the
+   * DEQUANT values, folds them into out_minmax and stores nothing (Y may be
+   * NULL).  DEQUANT_QUANT computes the same values again and stores them as
+   * uint8 [M,N], quantized with the scale and zero point that
+   * DynamicQuantizeLinear derives from the range in q_range
+   * (DynamicQuantizeLinear.cpp:43-84, QuantizeLinear.cpp:122-145); it leaves
+   * those scalars where q_params / q_scale / q_zp point. */
+  OMCUDA_EPI_DEQUANT_RANGE = 4,
+  OMCUDA_EPI_DEQUANT_QUANT = 5
 } omcudaEpilogue;
 
 typedef struct {
@@ -275,6 +285,14 @@ typedef struct {
    * (Math/Elementwise.cpp, one more separately rounded fp32 add). May be
    * NULL. */
   const float *residual;
+  /* DEQUANT_QUANT only: q_range = running range (omcudaDevRangeInit layout)
+   * of the values about to be quantized; q_params (2 floats: scale, zero
+   * point as float) is required, q_scale (y_scale) and q_zp (y_zero_point as
+   * uint8) may be NULL.  All device pointers. */
+  const void *q_range;
+  float *q_params;
+  float *q_scale;
+  uint8_t *q_zp;
 } omcudaGemmArgs;
 
 /* Device status word the GEMM writes on a bounded-wait timeout. */

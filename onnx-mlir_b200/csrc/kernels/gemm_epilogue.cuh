@@ -17,6 +17,11 @@
 //   DEQUANT_SPLIT  the DEQUANT value x written as two bf16 planes,
 //            hi = bf16(x) and lo = bf16(x - hi): the operand format of the
 //            tensor-core attention kernel (tensor-core GEMM only).
+//   DEQUANT_RANGE / DEQUANT_QUANT  the DEQUANT value folded into a running
+//            range only, and the same value quantized as DynamicQuantizeLinear
+//            would with the parameters that range gives (tensor-core GEMM
+//            only): together "linear -> DynamicQuantizeLinear" without the f32
+//            tensor ever reaching memory.
 //   REQUANT  QLinearMatMul: f32(acc) * S[n], round half even, fptosi,
 //            + y zero point, truncate to 8 bits
 //            (src/Conversion/ONNXToKrnl/Math/QLinearMatMul.cpp:123-138).
@@ -48,12 +53,22 @@ struct EpiParams {
   const float *residual; // f32 [M,N] added after the DEQUANT tail, or nullptr
   int res_vec_ok;        // residual rows take 16-byte loads
   uint32_t *out_range; // ordered-uint {min,max} or nullptr
+  const uint32_t *q_range; // DEQUANT_QUANT: range the quantize parameters come from
+  float *q_params;         // DEQUANT_QUANT: {scale, zero point as float} out
+  float *q_scale;          // optional y_scale out
+  uint8_t *q_zp;           // optional y_zero_point out
   int vec_ok;    // per-column vectors are 16-byte aligned: 128-bit loads allowed
   int line_store; // set by the tensor-core launcher: Y takes 16-byte line stores
 };
 
 // Host: flattens the public argument block (gemm_simt.cu).
 EpiParams make_epi_params(const omcudaGemmArgs &a);
+
+// The tails that start with the DEQUANT arithmetic.
+__host__ __device__ constexpr bool epi_is_dequant(int kind) {
+  return kind == OMCUDA_EPI_DEQUANT || kind == OMCUDA_EPI_DEQUANT_SPLIT ||
+         kind == OMCUDA_EPI_DEQUANT_RANGE || kind == OMCUDA_EPI_DEQUANT_QUANT;
+}
 
 #ifdef __CUDACC__
 __device__ __forceinline__ int32_t load_zp8(
@@ -91,7 +106,7 @@ __device__ __forceinline__ EpiScalars epi_scalars(const EpiParams &p) {
   EpiScalars s;
   s.sa = 1.0f;
   s.s0 = 1.0f;
-  if (p.kind == OMCUDA_EPI_DEQUANT || p.kind == OMCUDA_EPI_DEQUANT_SPLIT) {
+  if (epi_is_dequant(p.kind)) {
     s.sa = __ldg(p.sa);
     if (p.sb_len == 1)
       s.s0 = __fmul_rn(s.sa, __ldg(p.sb)); // onnx.Mul of the two scalars

@@ -212,6 +212,10 @@ EpiParams make_epi_params(const omcudaGemmArgs &a) {
   p.residual = (a.epilogue == OMCUDA_EPI_DEQUANT) ? a.residual : nullptr;
   p.res_vec_ok = ((((uintptr_t)a.residual) & 15u) == 0) && (a.N % 4 == 0);
   p.out_range = reinterpret_cast<uint32_t *>(a.out_minmax);
+  p.q_range = reinterpret_cast<const uint32_t *>(a.q_range);
+  p.q_params = a.q_params;
+  p.q_scale = a.q_scale;
+  p.q_zp = a.q_zp;
   p.vec_ok = ((((uintptr_t)a.B.colsum | (uintptr_t)a.bias | (uintptr_t)a.sb) & 15u) == 0) &&
              (a.N % 4 == 0);
   p.line_store = 0;
@@ -320,7 +324,8 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
   if (!args)
     return fail(OMCUDA_EINVAL, "GemmI8: null args");
   const omcudaGemmArgs &a = *args;
-  if (a.M < 0 || a.N <= 0 || a.K <= 0 || !a.A || !a.B.bt || !a.Y)
+  if (a.M < 0 || a.N <= 0 || a.K <= 0 || !a.A || !a.B.bt ||
+      (!a.Y && a.epilogue != OMCUDA_EPI_DEQUANT_RANGE))
     return fail(OMCUDA_EINVAL, "GemmI8: bad shape or null operand");
   if (a.M == 0)
     return OMCUDA_OK;
@@ -336,9 +341,14 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
     return fail(OMCUDA_EINVAL, "GemmI8: a_zp needs the column sums of B");
   if (a.residual && a.epilogue != OMCUDA_EPI_DEQUANT)
     return fail(OMCUDA_EINVAL, "GemmI8: a residual goes with the dequant epilogue only");
-  if ((a.epilogue == OMCUDA_EPI_DEQUANT || a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT) &&
-      (!a.sa || !a.sb))
+  if (a.epilogue < OMCUDA_EPI_I32 || a.epilogue > OMCUDA_EPI_DEQUANT_QUANT)
+    return fail(OMCUDA_EINVAL, "GemmI8: unknown epilogue %d", a.epilogue);
+  if (epi_is_dequant(a.epilogue) && (!a.sa || !a.sb))
     return fail(OMCUDA_EINVAL, "GemmI8: dequant epilogue needs both scales");
+  if (a.epilogue == OMCUDA_EPI_DEQUANT_RANGE && !a.out_minmax)
+    return fail(OMCUDA_EINVAL, "GemmI8: the range-only tail needs out_minmax");
+  if (a.epilogue == OMCUDA_EPI_DEQUANT_QUANT && (!a.q_range || !a.q_params))
+    return fail(OMCUDA_EINVAL, "GemmI8: the quantizing tail needs q_range and q_params");
   if (a.epilogue == OMCUDA_EPI_REQUANT && !a.sb)
     return fail(OMCUDA_EINVAL, "GemmI8: requant epilogue needs S");
   if (a.epilogue != OMCUDA_EPI_I32 && a.sb_len != 1 && a.sb_len != a.N)
@@ -348,11 +358,14 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
   if (a.kernel_choice == 1 && !tc_ok)
     return fail(OMCUDA_ENOTSUP,
         "GemmI8: tensor-core kernel needs K %% 16 == 0 and 16-byte aligned A");
-  if (a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT && (!tc_ok || a.kernel_choice == 2))
+  const bool tc_only = a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT ||
+                       a.epilogue == OMCUDA_EPI_DEQUANT_RANGE ||
+                       a.epilogue == OMCUDA_EPI_DEQUANT_QUANT;
+  if (tc_only && (!tc_ok || a.kernel_choice == 2))
     return fail(OMCUDA_ENOTSUP,
-        "GemmI8: the split-bf16 tail exists on the tensor-core kernel only "
-        "(K %% 16 == 0, 16-byte aligned A)");
-  bool use_tc = (a.kernel_choice == 1) || a.epilogue == OMCUDA_EPI_DEQUANT_SPLIT ||
+        "GemmI8: the split-bf16, range-only and quantizing tails exist on the "
+        "tensor-core kernel only (K %% 16 == 0, 16-byte aligned A)");
+  bool use_tc = (a.kernel_choice == 1) || tc_only ||
                 (a.kernel_choice == 0 && tc_ok && a.M > 4);
   return use_tc ? launch_gemm_tc(a, st) : launch_gemm_simt(a, st);
 }

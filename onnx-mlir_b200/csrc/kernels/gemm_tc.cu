@@ -37,6 +37,7 @@
 
 #include "../runtime/internal.h"
 #include "gemm_epilogue.cuh"
+#include "quantize.cuh"
 #include "tc_ptx.cuh"
 
 namespace omcuda {
@@ -112,12 +113,14 @@ __device__ __forceinline__ void load_cols32(
 }
 
 // Turns 32 raw accumulators of one row into 32 output words (EPI_I32: the
-// corrected i32; EPI_DEQUANT and EPI_DEQUANT_SPLIT: f32 bits; EPI_REQUANT: one
-// byte per word).
+// corrected i32; EPI_DEQUANT, EPI_DEQUANT_SPLIT and EPI_DEQUANT_RANGE: f32
+// bits; EPI_REQUANT: one byte per word; EPI_DEQUANT_QUANT: words 0..7 hold
+// the 32 output bytes, four to a word).
 template <int EPI>
 __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
-    const EpiScalars &sc, const EpiRow &row, const float *res_row, int64_t nc,
-    int valid, uint32_t (&v)[32], float &lo, float &hi) {
+    const EpiScalars &sc, const QuantConsts &qc, const EpiRow &row,
+    const float *res_row, int64_t nc, int valid, uint32_t (&v)[32], float &lo,
+    float &hi) {
   const bool vec = p.vec_ok != 0;
   if (p.b_zp_len != 0) {
     // - bz[n] * rowsum[m] + K * az * bz[n]  =  bz[n] * (K * az - rowsum[m])
@@ -154,7 +157,7 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
   }
   if (EPI == OMCUDA_EPI_I32)
     return;
-  if (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT) {
+  if (epi_is_dequant(EPI)) {
     float f[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j)
@@ -213,6 +216,14 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
           }
       }
     }
+    if (EPI == OMCUDA_EPI_DEQUANT_QUANT) {
+      // DynamicQuantizeLinear's quantize step on the values just computed.
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[j] = quantize_four<false>(
+            make_float4(f[4 * j], f[4 * j + 1], f[4 * j + 2], f[4 * j + 3]), qc);
+      return;
+    }
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       v[j] = __float_as_uint(f[j]);
@@ -260,6 +271,28 @@ __device__ __forceinline__ void split_words_bf16(uint32_t (&v)[32]) {
   }
 }
 
+// EPI_DEQUANT_QUANT: scale and zero point as DynamicQuantizeLinear derives
+// them from the range a range-only pass of the same product left behind.
+// Every thread computes the same two scalars; one thread of the grid also
+// publishes them for the operators that follow.
+template <int EPI>
+__device__ __forceinline__ QuantConsts epi_quant_consts(const EpiParams &p, bool publish) {
+  if (EPI != OMCUDA_EPI_DEQUANT_QUANT)
+    return QuantConsts{1.0f, 1.0f, 0.0f, true};
+  float scale, zp_f;
+  dql_params_from_range(ordered_to_f32(__ldg(p.q_range)),
+      ordered_to_f32(__ldg(p.q_range + 1)), &scale, &zp_f);
+  if (publish) {
+    p.q_params[0] = scale;
+    p.q_params[1] = zp_f;
+    if (p.q_scale)
+      *p.q_scale = scale;
+    if (p.q_zp)
+      *p.q_zp = (uint8_t)(unsigned int)zp_f; // fptoui; zp_f is in [0,255]
+  }
+  return make_quant_consts(scale, zp_f);
+}
+
 // Drains one accumulator tile half (this warp's 32 TMEM lanes x kHalfCols
 // columns starting at taddr) through the epilogue into Y.
 //   m_warp   first output row of this warp's 32 rows
@@ -267,13 +300,17 @@ __device__ __forceinline__ void split_words_bf16(uint32_t (&v)[32]) {
 //   slab0    this warp's 4 KiB staging slab in shared memory
 template <int BN, int EPI, int EW>
 __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
-    const EpiScalars &sc, uint32_t taddr, int64_t m_warp, int64_t n0,
-    uint32_t slab0, int lane, bool use_slab, float &lo, float &hi,
+    const EpiScalars &sc, const QuantConsts &qc, uint32_t taddr, int64_t m_warp,
+    int64_t n0, uint32_t slab0, int lane, bool use_slab, float &lo, float &hi,
     const CUtensorMap *map_y, const CUtensorMap *map_y2) {
   // EPI_DEQUANT_SPLIT stages like the 4-byte tails (32 columns per 128-byte
   // slab row: 16 words of bf16 hi pairs, then 16 words of lo pairs).
   constexpr bool kSplit = EPI == OMCUDA_EPI_DEQUANT_SPLIT;
-  constexpr int kOutBytes = (EPI == OMCUDA_EPI_REQUANT) ? 1 : 4;
+  // EPI_DEQUANT_RANGE walks the tile like the f32 tail and stores nothing.
+  constexpr bool kNoStore = EPI == OMCUDA_EPI_DEQUANT_RANGE;
+  constexpr bool kPacked = EPI == OMCUDA_EPI_DEQUANT_QUANT; // bytes arrive four to a word
+  constexpr int kOutBytes =
+      (EPI == OMCUDA_EPI_REQUANT || EPI == OMCUDA_EPI_DEQUANT_QUANT) ? 1 : 4;
   constexpr int kHalfCols = epi_cols_per_warp(BN, EW);
   constexpr int kSlabCols =
       (128 / kOutBytes) < kHalfCols ? (128 / kOutBytes) : kHalfCols;
@@ -317,7 +354,9 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
         const int64_t nc = ng + cc;
         const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
         if (row_ok && valid > 0)
-          epilogue_chunk<EPI>(p, sc, row, res_row, nc, valid, v, lo, hi);
+          epilogue_chunk<EPI>(p, sc, qc, row, res_row, nc, valid, v, lo, hi);
+        if (kNoStore)
+          continue;
         if (kSplit)
           split_words_bf16(v);
         if (cc == 0) {
@@ -343,12 +382,15 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
           uint32_t w[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            w[j] = v[4 * j] | (v[4 * j + 1] << 8) | (v[4 * j + 2] << 16) |
-                   (v[4 * j + 3] << 24);
+            w[j] = kPacked ? v[j]
+                           : (v[4 * j] | (v[4 * j + 1] << 8) | (v[4 * j + 2] << 16) |
+                                 (v[4 * j + 3] << 24));
           st_shared_v4(my_row + ((uint32_t)cc ^ swz), w[0], w[1], w[2], w[3]);
           st_shared_v4(my_row + (((uint32_t)cc + 16u) ^ swz), w[4], w[5], w[6], w[7]);
         }
       }
+      if (kNoStore)
+        continue;
       fence_proxy_async_smem(); // the slab was written through the generic proxy
       __syncwarp();
       if (lane == 0 && warp_in && ng < p.N) {
@@ -371,7 +413,9 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
       const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
       if (!row_ok || valid <= 0)
         continue;
-      epilogue_chunk<EPI>(p, sc, row, res_row, nc, valid, v, lo, hi);
+      epilogue_chunk<EPI>(p, sc, qc, row, res_row, nc, valid, v, lo, hi);
+      if (kNoStore)
+        continue;
       if (kSplit) {
         split_words_bf16(v);
         uint16_t *dhi = reinterpret_cast<uint16_t *>(p.Y) + m * p.N + nc;
@@ -400,7 +444,7 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
 #pragma unroll
         for (int j = 0; j < 32; ++j)
           if (j < valid)
-            dst[j] = (uint8_t)v[j];
+            dst[j] = kPacked ? (uint8_t)(v[j >> 2] >> (8 * (j & 3))) : (uint8_t)v[j];
       }
     }
   }
@@ -533,6 +577,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
     const int c_lo = (ew >> 2) * kHalfCols; // this warp's share of the columns
     const bool active = c_lo < BN;          // narrow tiles leave some warps idle
     const EpiScalars sc = epi_scalars(p);
+    const QuantConsts qc = epi_quant_consts<EPI>(p, warp == 2 && lane == 0 && blockIdx.x == 0);
     const bool use_slab = p.line_store != 0;
     const uint32_t slab0 = staging_base + (uint32_t)ew * Cfg::kSlabBytes;
     bool ok = active;
@@ -574,8 +619,8 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       tcgen05_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
-      epilogue_tile<BN, EPI, EW>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi,
-          &map_y, &map_y2);
+      epilogue_tile<BN, EPI, EW>(p, sc, qc, taddr, m_warp, n0, slab0, lane, use_slab,
+          lo, hi, &map_y, &map_y2);
       // The accumulator buffer may be overwritten once all eight warps are done.
       tcgen05_fence_before();
       __syncwarp();
@@ -584,8 +629,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
     }
     // One commit of the running range per warp, and every store of this warp
     // complete before the CTA may exit.
-    if (active && p.out_range &&
-        (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT))
+    if (active && p.out_range && epi_is_dequant(EPI) && EPI != OMCUDA_EPI_DEQUANT_QUANT)
       epi_range_commit(p.out_range, lo, hi);
     if (lane == 0)
       tma_store_wait_all();
@@ -747,6 +791,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
     const int c_lo = (ew >> 2) * kHalfCols;
     const bool active = c_lo < BN;
     const EpiScalars sc = epi_scalars(p);
+    const QuantConsts qc = epi_quant_consts<EPI>(p, warp == 2 && lane == 0 && blockIdx.x == 0);
     const bool use_slab = p.line_store != 0;
     const uint32_t slab0 = staging_base + (uint32_t)ew * kSlabBytes;
     bool ok = active;
@@ -786,15 +831,14 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       tcgen05_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
-      epilogue_tile<BN, EPI, EW>(p, sc, taddr, m_warp, n0, slab0, lane, use_slab, lo, hi,
-          &map_y, &map_y2);
+      epilogue_tile<BN, EPI, EW>(p, sc, qc, taddr, m_warp, n0, slab0, lane, use_slab,
+          lo, hi, &map_y, &map_y2);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0)
         mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[buf]), 0));
     }
-    if (active && p.out_range &&
-        (EPI == OMCUDA_EPI_DEQUANT || EPI == OMCUDA_EPI_DEQUANT_SPLIT))
+    if (active && p.out_range && epi_is_dequant(EPI) && EPI != OMCUDA_EPI_DEQUANT_QUANT)
       epi_range_commit(p.out_range, lo, hi);
     if (lane == 0)
       tma_store_wait_all();
@@ -903,6 +947,18 @@ uint32_t make_idesc(int a_signed, int b_signed, int n) {
 // bf16 columns of the hi and of the lo plane).  Only encoded when Y can take
 // them (16-byte aligned base and row pitch); otherwise the kernel stores
 // directly and never reads the maps.
+// 16-byte stores of whole lines need an aligned base and row pitch (the
+// range-only tail stores nothing and walks the tile the same way).
+template <int EPI>
+bool y_takes_line_stores(const omcudaGemmArgs &a) {
+  if (EPI == OMCUDA_EPI_DEQUANT_RANGE)
+    return true;
+  const int esize = (EPI == OMCUDA_EPI_REQUANT || EPI == OMCUDA_EPI_DEQUANT_QUANT)
+                        ? 1
+                        : (EPI == OMCUDA_EPI_DEQUANT_SPLIT ? 2 : 4);
+  return (((uintptr_t)a.Y & 15u) == 0) && ((a.N * esize) % 16 == 0);
+}
+
 template <int EPI>
 int make_y_maps(const omcudaGemmArgs &a, int half_cols, bool line_store,
     CUtensorMap *map_y, CUtensorMap *map_y2) {
@@ -911,7 +967,9 @@ int make_y_maps(const omcudaGemmArgs &a, int half_cols, bool line_store,
   if (!line_store)
     return OMCUDA_OK;
   int rc;
-  if (EPI == OMCUDA_EPI_REQUANT) {
+  if (EPI == OMCUDA_EPI_DEQUANT_RANGE)
+    return OMCUDA_OK; // nothing is stored
+  if (EPI == OMCUDA_EPI_REQUANT || EPI == OMCUDA_EPI_DEQUANT_QUANT) {
     const int cols = half_cols < 128 ? half_cols : 128; // 32, 64 or 128
     rc = make_tma_map_2d(map_y, a.Y, a.M, a.N, a.N, cols, 32, 1, cols);
   } else if (EPI == OMCUDA_EPI_DEQUANT_SPLIT) {
@@ -942,9 +1000,7 @@ int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   if (rc != OMCUDA_OK)
     return rc;
   EpiParams p = make_epi_params(a);
-  // 16-byte stores of whole lines need an aligned base and row pitch.
-  const int esize = (EPI == OMCUDA_EPI_REQUANT) ? 1 : (EPI == OMCUDA_EPI_DEQUANT_SPLIT ? 2 : 4);
-  p.line_store = (((uintptr_t)a.Y & 15u) == 0) && ((a.N * esize) % 16 == 0);
+  p.line_store = y_takes_line_stores<EPI>(a);
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
@@ -991,6 +1047,10 @@ int launch_bn(const omcudaGemmArgs &a, cudaStream_t st) {
     return launch_bn_epi<BN, OMCUDA_EPI_REQUANT>(a, st);
   case OMCUDA_EPI_DEQUANT_SPLIT:
     return launch_bn_epi<BN, OMCUDA_EPI_DEQUANT_SPLIT>(a, st);
+  case OMCUDA_EPI_DEQUANT_RANGE:
+    return launch_bn_epi<BN, OMCUDA_EPI_DEQUANT_RANGE>(a, st);
+  case OMCUDA_EPI_DEQUANT_QUANT:
+    return launch_bn_epi<BN, OMCUDA_EPI_DEQUANT_QUANT>(a, st);
   default:
     return fail(OMCUDA_EINVAL, "GemmI8: unknown epilogue %d", a.epilogue);
   }
@@ -1031,8 +1091,7 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   if (rc != OMCUDA_OK)
     return rc;
   EpiParams p = make_epi_params(a);
-  const int esize = (EPI == OMCUDA_EPI_REQUANT) ? 1 : (EPI == OMCUDA_EPI_DEQUANT_SPLIT ? 2 : 4);
-  p.line_store = (((uintptr_t)a.Y & 15u) == 0) && ((a.N * esize) % 16 == 0);
+  p.line_store = y_takes_line_stores<EPI>(a);
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
@@ -1079,6 +1138,10 @@ int launch_pair(const omcudaGemmArgs &a, cudaStream_t st) {
     return launch_pair_epi<OMCUDA_EPI_REQUANT>(a, st);
   case OMCUDA_EPI_DEQUANT_SPLIT:
     return launch_pair_epi<OMCUDA_EPI_DEQUANT_SPLIT>(a, st);
+  case OMCUDA_EPI_DEQUANT_RANGE:
+    return launch_pair_epi<OMCUDA_EPI_DEQUANT_RANGE>(a, st);
+  case OMCUDA_EPI_DEQUANT_QUANT:
+    return launch_pair_epi<OMCUDA_EPI_DEQUANT_QUANT>(a, st);
   default:
     return fail(OMCUDA_EINVAL, "GemmI8: unknown epilogue %d", a.epilogue);
   }

@@ -32,6 +32,7 @@
 
 #include <cerrno>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -148,7 +149,8 @@ int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
     const float *a_scale, const omcudaPreparedB &B, int64_t M,
     const float *w_scale, int64_t ws_len, const float *bias, int gelu, void *Y,
     void *out_range, cudaStream_t st, int epilogue = OMCUDA_EPI_DEQUANT,
-    const float *residual = nullptr) {
+    const float *residual = nullptr, const void *q_range = nullptr,
+    float *q_slot = nullptr) {
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (e->profiling) {
     while (e->ev.size() < e->ev_used + 2) {
@@ -185,10 +187,27 @@ int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
   g.gelu = gelu;
   g.out_minmax = out_range;
   g.residual = residual;
+  if (q_slot) { // a quantize site's slot: scale, zero point, y_scale, y_zero_point
+    g.q_range = q_range;
+    g.q_params = q_slot;
+    g.q_scale = q_slot + 2;
+    g.q_zp = (uint8_t *)(q_slot + 3);
+  }
   int rc = omcudaDevGemmI8(&g, st);
   if (e1)
     cudaEventRecord(e1, st);
   return rc;
+}
+
+// OMCUDA_FFN_TWO_PASS=0|1 overrides the size rule, for experiments.
+bool ffn_two_pass_wanted(size_t f32_bytes) {
+  static const int forced = [] {
+    const char *s = getenv("OMCUDA_FFN_TWO_PASS");
+    return s ? atoi(s) : -1;
+  }();
+  if (forced == 0 || forced == 1)
+    return forced == 1;
+  return f32_bytes >= ((size_t)256 << 20);
 }
 
 int ensure_workspace(omcudaEncoder *e, int64_t T) {
@@ -367,6 +386,13 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
       omcudaDevAttentionBf16Supported(batch, seq, heads, dh, 3 * H, H) != 0;
   // (the f32 [T,3H] buffer holds the two bf16 [T,3H] planes instead)
   const bool fuse_residual = (size_t)(T * H) * 4 >= ((size_t)64 << 20);
+  // Gelu(Linear(h1)) feeds nothing but a DynamicQuantizeLinear.  When that
+  // f32 [T,F] tensor is far larger than L2, writing it and reading it back
+  // costs more than running the product twice: once to learn the range of
+  // the activations, once to quantize them on the way out.  Same values,
+  // same bytes; the f32 tensor never exists.
+  const bool ffn_two_pass = ffn_two_pass_wanted((size_t)(T * F) * 4);
+  uint8_t *fq = (uint8_t *)e->f.p; // uint8 [T,F] in the two-pass form
   void *planes_hi = e->qkv.p;
   void *planes_lo = (uint8_t *)e->qkv.p + (size_t)(T * 3 * H) * 2;
 #define RUN(call)                                                              \
@@ -429,12 +455,21 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
         eps, (float *)e->h1.p, r_h1, st));
     RUN(omcudaDevQuantizeFromRange((const float *)e->h1.p, T * H, r_h1, xq,
         p_h1, p_h1 + 2, (uint8_t *)(p_h1 + 3), st));
-    RUN(gemm(e, xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
-        (const float *)L.scal.p + 1, 1, (const float *)L.b1.p, 1,
-        (float *)e->f.p, r_f, st));
-    RUN(omcudaDevQuantizeFromRange((const float *)e->f.p, T * F, r_f, xq, p_f,
-        p_f + 2, (uint8_t *)(p_f + 3), st));
-    RUN(gemm(e, xq, (const uint8_t *)(p_f + 3), p_f + 2, L.w2, T,
+    if (ffn_two_pass) {
+      RUN(gemm(e, xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
+          (const float *)L.scal.p + 1, 1, (const float *)L.b1.p, 1, nullptr, r_f,
+          st, OMCUDA_EPI_DEQUANT_RANGE));
+      RUN(gemm(e, xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
+          (const float *)L.scal.p + 1, 1, (const float *)L.b1.p, 1, fq, nullptr,
+          st, OMCUDA_EPI_DEQUANT_QUANT, nullptr, r_f, p_f));
+    } else {
+      RUN(gemm(e, xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
+          (const float *)L.scal.p + 1, 1, (const float *)L.b1.p, 1,
+          (float *)e->f.p, r_f, st));
+      RUN(omcudaDevQuantizeFromRange((const float *)e->f.p, T * F, r_f, xq, p_f,
+          p_f + 2, (uint8_t *)(p_f + 3), st));
+    }
+    RUN(gemm(e, ffn_two_pass ? fq : xq, (const uint8_t *)(p_f + 3), p_f + 2, L.w2, T,
         (const float *)L.scal.p + 2, 1, (const float *)L.b2.p, 0,
         (float *)e->o.p, nullptr, st, OMCUDA_EPI_DEQUANT,
         fuse_residual ? (const float *)e->h1.p : nullptr));

@@ -8,6 +8,7 @@ import ctypes
 from . import OmcudaError, check, lib
 
 EPI_I32, EPI_DEQUANT, EPI_REQUANT, EPI_DEQUANT_SPLIT = 0, 1, 2, 3
+EPI_DEQUANT_RANGE, EPI_DEQUANT_QUANT = 4, 5
 KERNEL_AUTO, KERNEL_TENSOR_CORE, KERNEL_SIMT = 0, 1, 2
 
 _vp, _i64, _i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
@@ -37,6 +38,7 @@ class GemmArgs(ctypes.Structure):
         ("out_minmax", _vp),
         ("kernel_choice", _i32),
         ("residual", _vp),
+        ("q_range", _vp), ("q_params", _vp), ("q_scale", _vp), ("q_zp", _vp),
     ]
 
 
@@ -108,6 +110,18 @@ def prepare_b(B, b_signed, K, N, bt, colsum, stream):
 
 def gemm_i8(args, stream):
     _ok(_bind().omcudaDevGemmI8(ctypes.byref(args), stream))
+
+
+def range_init(ranges, count, stream):
+    L = _bind()
+    L.omcudaDevRangeInit.argtypes = [_vp, _i64, _vp]
+    _ok(L.omcudaDevRangeInit(ranges, count, stream))
+
+
+def quantize_from_range(x, n, rng, y, params, y_scale, y_zp, stream):
+    L = _bind()
+    L.omcudaDevQuantizeFromRange.argtypes = [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp]
+    _ok(L.omcudaDevQuantizeFromRange(x, n, rng, y, params, y_scale, y_zp, stream))
 
 
 def requant_scale(a_scale, b_scale, n, y_scale, S, stream):

@@ -284,6 +284,62 @@ def test_dequant_split_epilogue_equals_split_of_dequant(gpu, M, K, N):
         assert np.array_equal(P2.numpy(), planes)
 
 
+@pytest.mark.parametrize("M,K,N,gelu", [(300, 256, 192, 1), (1024, 1024, 4096, 1),
+                                        (33, 64, 72, 0), (515, 512, 1000, 1)])
+def test_range_then_quantizing_tails_equal_dequant_then_quantize(gpu, M, K, N, gelu):
+    # "linear -> DynamicQuantizeLinear" run as two passes over the product
+    # (range only, then quantize while storing uint8) must give the bytes,
+    # scale and zero point of the f32 tail followed by the quantize kernel.
+    from gpu_util import DevGemm
+    rng = np.random.default_rng(M * 7 + N)
+    dg = DevGemm(gpu)
+    A = rng.integers(0, 256, (M, K), dtype=np.uint8)
+    B = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    pb, keep = dg.prepare(B)
+    dA = dg.dtensor(A)
+    az = dg.dtensor(np.array([128], np.uint8))
+    sa = dg.dtensor(np.array([0.011], np.float32))
+    sb = dg.dtensor(np.array([0.0004], np.float32))
+    bias = dg.dtensor(rng.normal(0, 0.5, N).astype(np.float32))
+    g = dg.dev.GemmArgs()
+    g.M, g.N, g.K = M, N, K
+    g.A, g.a_signed, g.B = dA.data_ptr, 0, pb
+    g.a_zp, g.a_zp_len = az.data_ptr, 1
+    g.sa, g.sb, g.sb_len, g.bias, g.gelu = sa.data_ptr, sb.data_ptr, 1, bias.data_ptr, gelu
+    g.kernel_choice = dg.dev.KERNEL_TENSOR_CORE
+    ranges = gpu.Tensor.device_empty((4,), np.int32)
+    dg.dev.range_init(ranges.data_ptr, 2, dg.stream)
+    # reference chain: f32 tail with running range, then the quantize kernel
+    Y = gpu.Tensor.device_empty((M, N), np.float32)
+    g.epilogue, g.Y, g.out_minmax = dg.dev.EPI_DEQUANT, Y.data_ptr, ranges.data_ptr
+    dg.dev.gemm_i8(g, dg.stream)
+    q_ref = gpu.Tensor.device_empty((M, N), np.uint8)
+    par_ref = gpu.Tensor.device_empty((4,), np.float32)
+    dg.dev.quantize_from_range(Y.data_ptr, M * N, ranges.data_ptr, q_ref.data_ptr,
+                               par_ref.data_ptr, par_ref.data_ptr + 8,
+                               par_ref.data_ptr + 12, dg.stream)
+    # two passes over the product, no f32 tensor
+    g.epilogue, g.Y, g.out_minmax = dg.dev.EPI_DEQUANT_RANGE, None, ranges.data_ptr + 8
+    dg.dev.gemm_i8(g, dg.stream)
+    q = gpu.Tensor.device_empty((M, N), np.uint8)
+    par = gpu.Tensor.device_empty((4,), np.float32)
+    g.epilogue, g.Y, g.out_minmax = dg.dev.EPI_DEQUANT_QUANT, q.data_ptr, None
+    g.q_range, g.q_params = ranges.data_ptr + 8, par.data_ptr
+    g.q_scale, g.q_zp = par.data_ptr + 8, par.data_ptr + 12
+    dg.dev.gemm_i8(g, dg.stream)
+    r = ranges.numpy()
+    gpu.synchronize()
+    assert r[0] == r[2] and r[1] == r[3]
+    # slots: scale, zero point as float, y_scale, first byte = y_zero_point
+    pw, pw_ref = par.numpy().view(np.uint32), par_ref.numpy().view(np.uint32)
+    assert np.array_equal(pw[:3], pw_ref[:3]) and (pw[3] & 0xff) == (pw_ref[3] & 0xff)
+    assert np.array_equal(q.numpy(), q_ref.numpy())
+    # and the bytes are DynamicQuantizeLinear of the f32 tensor (numpy restatement)
+    y = Y.numpy()
+    scale = np.float32(np.float32(max(y.max(), 0) - min(y.min(), 0)) / np.float32(255))
+    assert par.numpy()[0] == scale
+
+
 @pytest.mark.parametrize("M,K,N", [(4096, 4096, 4096), (5000, 2048, 4104), (300, 512, 1000)])
 def test_whole_output_checksums(gpu, orc, M, K, N):
     # Every tile of the output is stored exactly once (the epilogue leaves
