@@ -22,7 +22,9 @@ shapes and value distributions of the reference configurations):
 A step is one pass of the workload's graph over one batch.  `value` is timed
 with inputs resident in HBM; `e2e` runs the same graph through the krnl.call
 entry points with pinned host buffers, host<->device copies inside the timed
-region.  With N > 1 every rank runs the workload on its own batch (weights
+region (the encoder workloads use the pipelined Submit / Wait form of the
+host-tensor call: every step still copies its input in and its output out,
+and those copies overlap the runs of the neighbouring steps).  With N > 1 every rank runs the workload on its own batch (weights
 replicated, no data-path collective): weak scaling.
 """
 import argparse
@@ -313,6 +315,11 @@ class EncoderWorkload:
         self.oX = env.m.Tensor.from_numpy(self.hX.numpy())
         self.hY = torch.empty(shape, dtype=torch.float32).pin_memory()
         self.oY = env.m.Tensor.from_numpy(self.hY.numpy())
+        # a second pair of pinned host tensors for the pipelined e2e loop
+        self.hX2 = self.hX.clone().pin_memory()
+        self.oX2 = env.m.Tensor.from_numpy(self.hX2.numpy())
+        self.hY2 = torch.empty(shape, dtype=torch.float32).pin_memory()
+        self.oY2 = env.m.Tensor.from_numpy(self.hY2.numpy())
         self.units = float(c["B"])
         T = c["B"] * c["S"]
         self.h2d = T * c["H"] * 4
@@ -341,6 +348,22 @@ class EncoderWorkload:
         if self.world > 1:
             from omcuda.sharding import gather_rows
             gather_rows(self.Y, self.world * self.c["B"], out=self.Yall)
+
+    def run_e2e(self, steps, before_each=None):
+        """`steps` calls of the pipelined host-tensor API back to back: every
+        call copies its input from pinned host memory and its output back,
+        and the copies of one call overlap the run of its neighbours.  All
+        outputs are in host memory when this returns."""
+        for i in range(steps):
+            if before_each is not None:
+                before_each()
+            x, y = (self.oX, self.oY) if i % 2 == 0 else (self.oX2, self.oY2)
+            self.enc.submit(x, y)
+            if self.world > 1:
+                from omcuda.sharding import gather_rows
+                gather_rows(self.Y, self.world * self.c["B"], out=self.Yall)
+        self.enc.wait()
+        self.last = float(self.hY[0, 0, 0]) + float(self.hY2[0, 0, 0])
 
     def config(self):
         c = self.c
@@ -428,7 +451,24 @@ def run_gpu(args):
     env.m.synchronize()
 
     e2e_steps = max(1, min(args.steps, 5 if is_encoder else 10))
-    e2e_ms = timed(wl.step_e2e, e2e_steps, 1)
+    if is_encoder:
+        # The host-tensor API as a pipeline (Submit / Wait): one timed block
+        # over all steps, bracketed by events on the launching stream; the
+        # closing event is recorded after the host has seen every output.
+        wl.run_e2e(2, env.flush_l2)
+        barrier()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record(env.stream)
+        wl.run_e2e(e2e_steps, env.flush_l2)
+        b1.record(env.stream)
+        barrier()
+        e2e_ms = b0.elapsed_time(b1)
+        if world > 1:
+            t = torch.tensor([e2e_ms], dtype=torch.float64, device=env.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+    else:
+        e2e_ms = timed(wl.step_e2e, e2e_steps, 1)
 
     if rank != 0:
         if world > 1:
@@ -456,7 +496,10 @@ def run_gpu(args):
         "data": "synthetic", "config": wl.config(),
         "e2e": {"value": e2e_value, "unit": wl.unit,
                 "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                "steps": e2e_steps},
+                "steps": e2e_steps,
+                "api": ("omcudaEncoderSubmit / omcudaEncoderWait, all steps in "
+                        "one timed block" if is_encoder else
+                        "one krnl.call-style entry per step")},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": roofline,

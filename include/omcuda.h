@@ -405,6 +405,17 @@ OMTensorList *omcudaEncoderRun(omcudaEncoder *enc, OMTensorList *inputs);
  * memory (omcudaHostAlloc) for full-speed copies.  Returns when y is complete
  * (host y) or with the work queued on the calling thread's stream (device y). */
 int omcudaEncoderRunInto(omcudaEncoder *enc, OMTensor *y, const OMTensor *x);
+/* The same for host tensors as a pipeline: Submit queues "copy x in, run, copy
+ * y out" and returns; the copy-in of a call overlaps the run of the call
+ * before it and its copy-out the run of the call after it (separate copy
+ * streams, two sets of staging buffers).  At most two calls are in flight: a
+ * third Submit first waits for the oldest.  x must stay unchanged and y is
+ * complete only after omcudaEncoderWait, which waits for every submitted
+ * call and reports any error.  Give pinned host memory (omcudaHostAlloc);
+ * pageable memory makes the copies synchronous.  Every call computes exactly
+ * what omcudaEncoderRunInto computes. */
+int omcudaEncoderSubmit(omcudaEncoder *enc, OMTensor *y, const OMTensor *x);
+int omcudaEncoderWait(omcudaEncoder *enc);
 /* Device-pointer form: x, y are device f32 [batch*seq, hidden]. */
 int omcudaEncoderRunDev(omcudaEncoder *enc, const float *x, int64_t batch,
     int64_t seq, float *y, void *stream);

@@ -81,6 +81,15 @@ struct omcudaEncoder {
   int64_t tokens = 0;
   DevBuf xq, qkv, ctx, a, h1, f, o, ybuf[2];
   DevBuf stage_in, stage_out; // HBM staging of host tensors (omcudaEncoderRunInto)
+  // Pipelined host-tensor runs (omcudaEncoderSubmit): two slots, so that the
+  // copies of one call overlap the encoder run of its neighbours.
+  struct Slot {
+    DevBuf in, out;
+    cudaEvent_t in_done = nullptr, run_done = nullptr, out_done = nullptr;
+    bool used = false;
+  } slot[2];
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;
+  uint64_t submitted = 0;
   DevBuf ranges;  // 4 running ranges per layer + 1
   DevBuf params;  // 16 bytes per quantize site
   DevBuf dql_scratch;
@@ -199,15 +208,15 @@ int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
   return rc;
 }
 
-// OMCUDA_FFN_TWO_PASS=0|1 overrides the size rule, for experiments.
-bool ffn_two_pass_wanted(size_t f32_bytes) {
-  static const int forced = [] {
+// Off unless OMCUDA_FFN_TWO_PASS=1: on B200 the two passes over the product
+// measured slower than one pass that writes f32 plus the quantize pass (the
+// Gelu tail is bound by instruction issue, not by the f32 traffic it saves).
+bool ffn_two_pass_wanted() {
+  static const bool on = [] {
     const char *s = getenv("OMCUDA_FFN_TWO_PASS");
-    return s ? atoi(s) : -1;
+    return s && atoi(s) == 1;
   }();
-  if (forced == 0 || forced == 1)
-    return forced == 1;
-  return f32_bytes >= ((size_t)256 << 20);
+  return on;
 }
 
 int ensure_workspace(omcudaEncoder *e, int64_t T) {
@@ -386,12 +395,11 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
       omcudaDevAttentionBf16Supported(batch, seq, heads, dh, 3 * H, H) != 0;
   // (the f32 [T,3H] buffer holds the two bf16 [T,3H] planes instead)
   const bool fuse_residual = (size_t)(T * H) * 4 >= ((size_t)64 << 20);
-  // Gelu(Linear(h1)) feeds nothing but a DynamicQuantizeLinear.  When that
-  // f32 [T,F] tensor is far larger than L2, writing it and reading it back
-  // costs more than running the product twice: once to learn the range of
-  // the activations, once to quantize them on the way out.  Same values,
-  // same bytes; the f32 tensor never exists.
-  const bool ffn_two_pass = ffn_two_pass_wanted((size_t)(T * F) * 4);
+  // Gelu(Linear(h1)) feeds nothing but a DynamicQuantizeLinear, so the f32
+  // [T,F] tensor can be avoided by running the product twice: once to learn
+  // the range of the activations, once to quantize them on the way out.
+  // Same values, same bytes (an experiment switch, see ffn_two_pass_wanted).
+  const bool ffn_two_pass = ffn_two_pass_wanted();
   uint8_t *fq = (uint8_t *)e->f.p; // uint8 [T,F] in the two-pass form
   void *planes_hi = e->qkv.p;
   void *planes_lo = (uint8_t *)e->qkv.p + (size_t)(T * 3 * H) * 2;
@@ -599,6 +607,83 @@ extern "C" int omcudaEncoderRunInto(
   return OMCUDA_OK;
 }
 
+// One call of the pipeline: H2D on the encoder's inbound copy stream, the run
+// on the calling thread's stream, D2H on the outbound copy stream, chained by
+// events.  Slot k & 1 is reused by call k + 2: its input buffer once run k is
+// done (a stream wait), its output buffer once copy-out k is done (a host
+// wait, which also bounds the queue to two calls).
+extern "C" int omcudaEncoderSubmit(
+    omcudaEncoder *e, OMTensor *y, const OMTensor *x) {
+  if (sticky_error())
+    return omcudaGetLastError();
+  int rc = ensure_init();
+  if (rc != OMCUDA_OK)
+    return rc;
+  if (!e || !x || !y || omTensorGetDataType(x) != ONNX_TYPE_FLOAT ||
+      omTensorGetDataType(y) != ONNX_TYPE_FLOAT || omTensorGetRank(x) != 3 ||
+      omTensorGetRank(y) != 3 || omTensorGetShape(x)[2] != e->cfg.hidden)
+    return fail(OMCUDA_EINVAL, "EncoderSubmit: x and y must be f32 [batch, seq, %lld]",
+        (long long)e->cfg.hidden);
+  for (int i = 0; i < 3; ++i)
+    if (omTensorGetShape(x)[i] != omTensorGetShape(y)[i])
+      return fail(OMCUDA_EINVAL, "EncoderSubmit: y must have the shape of x");
+  if (omcudaTensorIsOnDevice(x) || omcudaTensorIsOnDevice(y))
+    return fail(OMCUDA_EINVAL,
+        "EncoderSubmit: host tensors only (device tensors: omcudaEncoderRunInto)");
+  const int64_t B = omTensorGetShape(x)[0], S = omTensorGetShape(x)[1];
+  const size_t bytes = (size_t)(B * S * e->cfg.hidden) * 4;
+  cudaStream_t st = current_stream();
+  if (!e->copy_in) {
+    OMCUDA_CHECK(cudaStreamCreateWithFlags(&e->copy_in, cudaStreamNonBlocking));
+    OMCUDA_CHECK(cudaStreamCreateWithFlags(&e->copy_out, cudaStreamNonBlocking));
+  }
+  omcudaEncoder::Slot &sl = e->slot[e->submitted & 1];
+  if (!sl.in_done) {
+    OMCUDA_CHECK(cudaEventCreateWithFlags(&sl.in_done, cudaEventDisableTiming));
+    OMCUDA_CHECK(cudaEventCreateWithFlags(&sl.run_done, cudaEventDisableTiming));
+    OMCUDA_CHECK(cudaEventCreateWithFlags(&sl.out_done, cudaEventDisableTiming));
+  }
+  if (sl.used) {
+    OMCUDA_CHECK(cudaEventSynchronize(sl.out_done));
+    OMCUDA_CHECK(cudaStreamWaitEvent(e->copy_in, sl.run_done, 0));
+  }
+  if (bytes > sl.in.bytes || bytes > sl.out.bytes) {
+    // growing a buffer frees the old one: nothing may still be using it
+    OMCUDA_CHECK(cudaStreamSynchronize(st));
+    sl.in.ensure(bytes);
+    sl.out.ensure(bytes);
+    if (!sl.in.p || !sl.out.p)
+      return OMCUDA_ENOMEM;
+  }
+  OMCUDA_CHECK(cudaMemcpyAsync(sl.in.p, omTensorGetDataPtr(x), bytes,
+      cudaMemcpyHostToDevice, e->copy_in));
+  OMCUDA_CHECK(cudaEventRecord(sl.in_done, e->copy_in));
+  OMCUDA_CHECK(cudaStreamWaitEvent(st, sl.in_done, 0));
+  rc = omcudaEncoderRunDev(e, (const float *)sl.in.p, B, S, (float *)sl.out.p, st);
+  if (rc != OMCUDA_OK)
+    return rc;
+  OMCUDA_CHECK(cudaEventRecord(sl.run_done, st));
+  OMCUDA_CHECK(cudaStreamWaitEvent(e->copy_out, sl.run_done, 0));
+  OMCUDA_CHECK(cudaMemcpyAsync(omTensorGetDataPtr(y), sl.out.p, bytes,
+      cudaMemcpyDeviceToHost, e->copy_out));
+  OMCUDA_CHECK(cudaEventRecord(sl.out_done, e->copy_out));
+  sl.used = true;
+  ++e->submitted;
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaEncoderWait(omcudaEncoder *e) {
+  if (!e)
+    return fail(OMCUDA_EINVAL, "EncoderWait: null encoder");
+  if (e->copy_out) {
+    for (auto &sl : e->slot)
+      if (sl.used)
+        OMCUDA_CHECK(cudaEventSynchronize(sl.out_done));
+  }
+  omcudaSynchronize(); // surfaces a bounded-wait timeout of the kernels
+  return sticky_error() ? omcudaGetLastError() : OMCUDA_OK;
+}
+
 extern "C" void omcudaEncoderSetProfiling(omcudaEncoder *e, int on) {
   if (!e)
     return;
@@ -631,6 +716,19 @@ extern "C" void omcudaEncoderDestroy(omcudaEncoder *e) {
     cudaStreamSynchronize(current_stream());
   for (cudaEvent_t ev : e->ev)
     cudaEventDestroy(ev);
+  for (auto &sl : e->slot) {
+    if (sl.out_done)
+      cudaEventSynchronize(sl.out_done);
+    for (cudaEvent_t ev : {sl.in_done, sl.run_done, sl.out_done})
+      if (ev)
+        cudaEventDestroy(ev);
+    sl.in.release();
+    sl.out.release();
+  }
+  if (e->copy_in)
+    cudaStreamDestroy(e->copy_in);
+  if (e->copy_out)
+    cudaStreamDestroy(e->copy_out);
   for (auto &L : e->layers) {
     DevBuf *all[] = {&L.wqkv_bt, &L.wqkv_cs, &L.wo_bt, &L.wo_cs, &L.w1_bt,
         &L.w1_cs, &L.w2_bt, &L.w2_cs, &L.qkv_scale, &L.scal, &L.bqkv, &L.bo,

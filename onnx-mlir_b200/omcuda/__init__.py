@@ -484,6 +484,24 @@ class Encoder:
             check()
             raise OmcudaError(rc, "omcudaEncoderRunInto failed")
 
+    def submit(self, x, y):
+        """Pipelined run_into for host Tensors: queues copy-in, run, copy-out
+        and returns; y is complete after wait()."""
+        L = lib()
+        L.omcudaEncoderSubmit.argtypes = [ctypes.c_void_p] * 3
+        rc = L.omcudaEncoderSubmit(self.handle, y.handle, x.handle)
+        if rc != 0:
+            check()
+            raise OmcudaError(rc, "omcudaEncoderSubmit failed")
+
+    def wait(self):
+        L = lib()
+        L.omcudaEncoderWait.argtypes = [ctypes.c_void_p]
+        rc = L.omcudaEncoderWait(self.handle)
+        if rc != 0:
+            check()
+            raise OmcudaError(rc, "omcudaEncoderWait failed")
+
     def run_dev(self, x_ptr, batch, seq, y_ptr, stream):
         rc = lib().omcudaEncoderRunDev(self.handle, x_ptr, batch, seq, y_ptr, stream)
         if rc != 0:

@@ -102,6 +102,43 @@ def test_encoder_first_linear_is_bit_exact(gpu, orc):
         assert got.tobytes() == want.tobytes()
 
 
+def test_pipelined_submit_equals_run_into(gpu):
+    # Five different batches through the pipelined host-tensor calls (copies
+    # of one call overlap the run of its neighbours, two staging slots) give,
+    # bit for bit, what the synchronous call gives for each of them; nothing
+    # is complete before wait(), everything after it.
+    B, S, H, heads, F = 4, 128, 128, 2, 256
+    layers = make_encoder(13, H, F, 2)
+    enc = gpu.Encoder(H, heads, F, layers)
+    rng = np.random.default_rng(14)
+    xs = [rng.normal(size=(B, S, H)).astype(np.float32) * (1 + i) for i in range(5)]
+    want = []
+    for x in xs:
+        y = np.zeros((B, S, H), np.float32)
+        enc.run_into(gpu.Tensor.from_numpy(x), gpu.Tensor.from_numpy(y))
+        want.append(y)
+    ys = [np.zeros((B, S, H), np.float32) for _ in xs]
+    keep = []
+    for x, y in zip(xs, ys):
+        tx, ty = gpu.Tensor.from_numpy(x), gpu.Tensor.from_numpy(y)
+        keep.append((tx, ty))
+        enc.submit(tx, ty)
+    enc.wait()
+    for y, w in zip(ys, want):
+        assert np.array_equal(y, w)
+    # a larger batch afterwards grows the staging buffers
+    x = rng.normal(size=(2 * B, S, H)).astype(np.float32)
+    y, w = np.zeros_like(x), np.zeros_like(x)
+    enc.run_into(gpu.Tensor.from_numpy(x), gpu.Tensor.from_numpy(w))
+    tx, ty = gpu.Tensor.from_numpy(x), gpu.Tensor.from_numpy(y)
+    enc.submit(tx, ty)
+    enc.wait()
+    assert np.array_equal(y, w)
+    with pytest.raises(gpu.OmcudaError):
+        enc.submit(gpu.Tensor.from_numpy(x).to_device(), gpu.Tensor.from_numpy(y))
+    enc.close()
+
+
 def test_encoder_rejects_wrong_input(gpu):
     layers = make_encoder(11, 128, 256, 1)
     enc = gpu.Encoder(128, 2, 256, layers)
