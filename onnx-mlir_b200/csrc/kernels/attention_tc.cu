@@ -20,9 +20,11 @@
 // head h of Q / K / V owns columns [col + 64 h, col + 64 h + 64) of its rows.
 // out is [T, ld_out] fp32.
 //
-// One CTA = 128 query rows of one (batch, head); two CTAs share an SM so that
-// one's softmax (CUDA cores) overlaps the other's matrix products (tensor
-// pipe).  Per block of 128 keys:
+// A work item = 128 query rows of one (batch, head).  Two persistent CTAs
+// share an SM, so that one's softmax (CUDA cores) overlaps the other's matrix
+// products (tensor pipe); each walks its share of the items and requests the
+// Q and first K tiles of its next item while the current one is in its last
+// key block.  Per block of 128 keys:
 //   thread 0   waits for the K tiles (TMA, 128-byte swizzle), issues
 //              S = Q K^T as 12 MMAs (3 split terms x 4 k-steps) into tensor
 //              memory, commits to an mbarrier, refills the K buffers;
@@ -33,6 +35,8 @@
 //   thread 0   issues O_j = P V as 24 MMAs with P read from tensor memory and
 //              V (keys x 64, MN-major) from shared memory; refills V;
 //   8 warps    o = o * 2^(m_old - m_new) + O_j in registers (32 columns each).
+// The normalised 128 x 64 result of an item is staged in the (then free) V
+// buffers and leaves with two TMA stores of whole 128-byte lines.
 // Every wait on an mbarrier is bounded (tc_ptx.cuh); a timeout raises the
 // CTA's abort flag, the CTA frees its tensor memory, writes the status word
 // and returns.
@@ -163,12 +167,31 @@ __host__ __device__ constexpr uint32_t att_idesc(int n, int b_mn_major) {
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// Coordinates of one work item: 128 query rows of one (batch, head).
+struct AttItem {
+  int32_t row_q, row_kv, cq, ck, cv, col_out;
+};
+
+__device__ __forceinline__ AttItem att_item(int64_t item, int nq, int64_t S,
+    int64_t heads, int32_t q_col, int32_t k_col, int32_t v_col) {
+  const int64_t bh = item / nq, qt = item % nq;
+  const int64_t b = bh / heads, h = bh % heads;
+  AttItem it;
+  it.row_kv = (int32_t)(b * S);
+  it.row_q = it.row_kv + (int32_t)qt * kTQ;
+  it.col_out = (int32_t)h * kTDh;
+  it.cq = q_col + it.col_out;
+  it.ck = k_col + it.col_out;
+  it.cv = v_col + it.col_out;
+  return it;
+}
+
 __global__ void __launch_bounds__(kTcAttThreads, 2)
     attention_tc_kernel(const __grid_constant__ CUtensorMap map_hi,
-        const __grid_constant__ CUtensorMap map_lo, int32_t q_col, int32_t k_col,
-        int32_t v_col, int64_t S, int64_t heads, float scale_log2e,
-        float *__restrict__ out, int64_t ld_out, uint32_t *__restrict__ out_range,
-        int *status) {
+        const __grid_constant__ CUtensorMap map_lo,
+        const __grid_constant__ CUtensorMap map_out, int32_t q_col, int32_t k_col,
+        int32_t v_col, int64_t S, int64_t heads, int64_t n_items, float scale_log2e,
+        uint32_t *__restrict__ out_range, int *status) {
   extern __shared__ uint8_t att_tc_smem[];
   __shared__ uint64_t bar_q, bar_k, bar_v, bar_s, bar_o;
   __shared__ uint32_t tmem_slot;
@@ -182,13 +205,8 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
   const int quad = warp & 3, half = warp >> 2;
   const int row = quad * 32 + lane;
   const uint64_t t0 = global_timer();
-  const int64_t bh = blockIdx.y;
-  const int64_t b = bh / heads, h = bh % heads;
-  const int32_t row_q = (int32_t)(b * S + (int64_t)blockIdx.x * kTQ);
-  const int32_t row_kv = (int32_t)(b * S);
-  const int32_t cq = q_col + (int32_t)h * kTDh, ck = k_col + (int32_t)h * kTDh,
-                cv = v_col + (int32_t)h * kTDh;
   const int nkb = (int)(S / kTK);
+  const int nq = (int)(S / kTQ);
 
   const uint32_t smem0 = (smem_u32(att_tc_smem) + 1023u) & ~1023u;
   const uint32_t s_qh = smem0, s_ql = smem0 + kTile, s_kh = smem0 + 2 * kTile,
@@ -216,171 +234,218 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
   const int kc0 = half * (kTK / 2); // first key column of this thread's share
   volatile int *abortp = &abort_flag;
 
-  if (tid == 0) {
+  // The CTA walks the items blockIdx.x, blockIdx.x + gridDim.x, ...; the
+  // operands of an item's first key block are requested while the item
+  // before it is still in its last block, as soon as their buffers are free.
+  if (tid == 0 && (int64_t)blockIdx.x < n_items) {
+    const AttItem it = att_item(blockIdx.x, nq, S, heads, q_col, k_col, v_col);
     mbar_expect_tx(smem_u32(&bar_q), 2 * kTile);
-    tma_load_2d(s_qh, &map_hi, cq, row_q, smem_u32(&bar_q));
-    tma_load_2d(s_ql, &map_lo, cq, row_q, smem_u32(&bar_q));
+    tma_load_2d(s_qh, &map_hi, it.cq, it.row_q, smem_u32(&bar_q));
+    tma_load_2d(s_ql, &map_lo, it.cq, it.row_q, smem_u32(&bar_q));
     mbar_expect_tx(smem_u32(&bar_k), 2 * kTile);
-    tma_load_2d(s_kh, &map_hi, ck, row_kv, smem_u32(&bar_k));
-    tma_load_2d(s_kl, &map_lo, ck, row_kv, smem_u32(&bar_k));
+    tma_load_2d(s_kh, &map_hi, it.ck, it.row_kv, smem_u32(&bar_k));
+    tma_load_2d(s_kl, &map_lo, it.ck, it.row_kv, smem_u32(&bar_k));
     mbar_expect_tx(smem_u32(&bar_v), 2 * kTile);
-    tma_load_2d(s_vh, &map_hi, cv, row_kv, smem_u32(&bar_v));
-    tma_load_2d(s_vl, &map_lo, cv, row_kv, smem_u32(&bar_v));
+    tma_load_2d(s_vh, &map_hi, it.cv, it.row_kv, smem_u32(&bar_v));
+    tma_load_2d(s_vl, &map_lo, it.cv, it.row_kv, smem_u32(&bar_v));
   }
 
   constexpr uint32_t kIdescQK = att_idesc(kTK, 0);
   constexpr uint32_t kIdescPV = att_idesc(kTDh, 1);
 
-  float o[kTDh / 2];
-#pragma unroll
-  for (int i = 0; i < kTDh / 2; ++i)
-    o[i] = 0.0f;
-  float m_run = -INFINITY; // running maximum of s * scale * log2(e)
-  float l_run = 0.0f;      // running sum of p
   bool ok = true;
+  uint32_t nblk = 0;  // key blocks done by this CTA: parity of bar_k / s / v / o
+  uint32_t nitem = 0; // items done by this CTA: parity of bar_q
+  float lo_run = INFINITY, hi_run = -INFINITY; // range of this thread's outputs
 
-  for (int j = 0; j < nkb; ++j) {
-    const uint32_t ph = (uint32_t)(j & 1);
-    // ---- S = Q K_j^T ----
-    if (tid == 0) {
-      if (j == 0)
-        ok = mbar_wait(smem_u32(&bar_q), 0, abortp, t0);
-      ok = ok && mbar_wait(smem_u32(&bar_k), ph, abortp, t0);
-      if (ok) {
-        tcgen05_fence_after();
-        // small terms first: Ql Kh, Qh Kl, then Qh Kh
-        const uint32_t qa[3] = {s_ql, s_qh, s_qh};
-        const uint32_t kb[3] = {s_kh, s_kl, s_kh};
-        static_assert(kTDh == 64, "four K slices per operand row");
+  for (int64_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++nitem) {
+    const AttItem it = att_item(item, nq, S, heads, q_col, k_col, v_col);
+    const bool has_next = item + gridDim.x < n_items;
+    AttItem nx = it;
+    if (tid == 0 && has_next)
+      nx = att_item(item + gridDim.x, nq, S, heads, q_col, k_col, v_col);
+
+    float o[kTDh / 2];
 #pragma unroll
-        for (int t = 0; t < 3; ++t)
-          umma_bf16_ss_x4(t_s, make_smem_desc(qa[t]), make_smem_desc(kb[t]), kIdescQK,
-              t != 0 ? 1u : 0u);
-        umma_commit(smem_u32(&bar_s));
-        ok = mbar_wait(smem_u32(&bar_s), ph, abortp, t0);
-        if (ok && j + 1 < nkb) { // the K buffers are free again
-          mbar_expect_tx(smem_u32(&bar_k), 2 * kTile);
-          tma_load_2d(s_kh, &map_hi, ck, row_kv + (j + 1) * kTK, smem_u32(&bar_k));
-          tma_load_2d(s_kl, &map_lo, ck, row_kv + (j + 1) * kTK, smem_u32(&bar_k));
+    for (int i = 0; i < kTDh / 2; ++i)
+      o[i] = 0.0f;
+    float m_run = -INFINITY; // running maximum of s * scale * log2(e)
+    float l_run = 0.0f;      // running sum of p
+
+    for (int j = 0; j < nkb; ++j, ++nblk) {
+      const uint32_t ph = nblk & 1u;
+      // ---- S = Q K_j^T ----
+      if (tid == 0) {
+        if (j == 0)
+          ok = mbar_wait(smem_u32(&bar_q), nitem & 1u, abortp, t0);
+        ok = ok && mbar_wait(smem_u32(&bar_k), ph, abortp, t0);
+        if (ok) {
+          tcgen05_fence_after();
+          // small terms first: Ql Kh, Qh Kl, then Qh Kh
+          const uint32_t qa[3] = {s_ql, s_qh, s_qh};
+          const uint32_t kb[3] = {s_kh, s_kl, s_kh};
+          static_assert(kTDh == 64, "four K slices per operand row");
+#pragma unroll
+          for (int t = 0; t < 3; ++t)
+            umma_bf16_ss_x4(t_s, make_smem_desc(qa[t]), make_smem_desc(kb[t]),
+                kIdescQK, t != 0 ? 1u : 0u);
+          umma_commit(smem_u32(&bar_s));
+          if (j == 0 && nitem != 0) {
+            // The V buffers held the previous item's output for its TMA
+            // store: refill them once the store has read them.
+            tma_store_wait_read();
+            mbar_expect_tx(smem_u32(&bar_v), 2 * kTile);
+            tma_load_2d(s_vh, &map_hi, it.cv, it.row_kv, smem_u32(&bar_v));
+            tma_load_2d(s_vl, &map_lo, it.cv, it.row_kv, smem_u32(&bar_v));
+          }
+          ok = mbar_wait(smem_u32(&bar_s), ph, abortp, t0);
+          if (ok && j + 1 < nkb) { // the K buffers are free again
+            mbar_expect_tx(smem_u32(&bar_k), 2 * kTile);
+            tma_load_2d(s_kh, &map_hi, it.ck, it.row_kv + (j + 1) * kTK, smem_u32(&bar_k));
+            tma_load_2d(s_kl, &map_lo, it.ck, it.row_kv + (j + 1) * kTK, smem_u32(&bar_k));
+          } else if (ok && has_next) { // so are the Q buffers: next item
+            mbar_expect_tx(smem_u32(&bar_q), 2 * kTile);
+            tma_load_2d(s_qh, &map_hi, nx.cq, nx.row_q, smem_u32(&bar_q));
+            tma_load_2d(s_ql, &map_lo, nx.cq, nx.row_q, smem_u32(&bar_q));
+            mbar_expect_tx(smem_u32(&bar_k), 2 * kTile);
+            tma_load_2d(s_kh, &map_hi, nx.ck, nx.row_kv, smem_u32(&bar_k));
+            tma_load_2d(s_kl, &map_lo, nx.ck, nx.row_kv, smem_u32(&bar_k));
+          }
         }
       }
-    }
-    ok = __syncthreads_and(ok) != 0;
-    if (!ok)
-      break;
-    tcgen05_fence_after();
-
-    // ---- online softmax: this thread's half of its row ----
-    __syncwarp(); // tcgen05.ld / st are warp-collective: enter them converged
-    float mx = -INFINITY;
-#pragma unroll 1
-    for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
-      uint32_t v[32];
-      tmem_ld32(t_s + lane_base + (uint32_t)c, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        mx = fmaxf(mx, __uint_as_float(v[i]));
-    }
-    // Row maximum over both halves (the two threads of a row sit in warps w
-    // and w + 4: a 64-thread named barrier per quadrant).
-    xch[half][row] = mx;
-    pair_barrier(quad);
-    mx = fmaxf(mx, xch[half ^ 1][row]);
-    const float m_new = fmaxf(m_run, __fmul_rn(mx, scale_log2e));
-    const float resc = ex2_approx(__fsub_rn(m_run, m_new)); // 0 on the first block
-    m_run = m_new;
-    const float neg_m = -m_new;
-    float psum = 0.0f;
-#pragma unroll 1
-    for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
-      uint32_t v[32];
-      tmem_ld32(t_s + lane_base + (uint32_t)c, v);
-      tmem_ld_wait();
-      uint32_t whi[16], wlo[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 =
-            ex2_approx(__fmaf_rn(__uint_as_float(v[2 * i]), scale_log2e, neg_m));
-        const float p1 = ex2_approx(
-            __fmaf_rn(__uint_as_float(v[2 * i + 1]), scale_log2e, neg_m));
-        psum = __fadd_rn(psum, __fadd_rn(p0, p1));
-        const uint32_t hi = cvt_bf16x2(p0, p1);
-        const float r0 = __fsub_rn(p0, __uint_as_float(hi << 16));
-        const float r1 = __fsub_rn(p1, __uint_as_float(hi & 0xffff0000u));
-        whi[i] = hi;
-        wlo[i] = cvt_bf16x2(r0, r1);
-      }
-      // P of keys c..c+31: hi in columns c..c+15, lo in c+16..c+31 (the
-      // scores of those columns are already consumed).
-      tmem_st16(t_s + lane_base + (uint32_t)c, whi);
-      tmem_st16(t_s + lane_base + (uint32_t)c + 16u, wlo);
-    }
-    l_run = __fadd_rn(__fmul_rn(l_run, resc), psum);
-    tmem_st_wait();
-    tcgen05_fence_before();
-    __syncthreads(); // every row of P is in tensor memory
-
-    // ---- O_j = P V_j ----
-    if (tid == 0) {
+      ok = __syncthreads_and(ok) != 0;
+      if (!ok)
+        break;
       tcgen05_fence_after();
-      ok = mbar_wait(smem_u32(&bar_v), ph, abortp, t0);
-      if (ok) {
-        tcgen05_fence_after();
-        // small terms first: Pl Vh, Ph Vl, then Ph Vh
-        const uint32_t pa[3] = {16u, 0u, 0u}; // column offset of lo / hi inside a chunk
-        const uint32_t vb[3] = {s_vh, s_vl, s_vh};
-        static_assert(kTK == 128, "two groups of four 16-key slices per block");
+
+      // ---- online softmax: this thread's half of its row ----
+      __syncwarp(); // tcgen05.ld / st are warp-collective: enter them converged
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(t_s + lane_base + (uint32_t)c, v);
+        tmem_ld_wait();
 #pragma unroll
-        for (int t = 0; t < 3; ++t) {
-          const uint64_t dv = make_smem_desc(vb[t]);
-          umma_bf16_ts_x4(t_o, t_s + pa[t], dv, kIdescPV, t != 0 ? 1u : 0u);
-          umma_bf16_ts_x4(t_o, t_s + 64u + pa[t], dv + 512, kIdescPV, 1u);
+        for (int i = 0; i < 32; ++i)
+          mx = fmaxf(mx, __uint_as_float(v[i]));
+      }
+      // Row maximum over both halves (the two threads of a row sit in warps w
+      // and w + 4: a 64-thread named barrier per quadrant).
+      xch[half][row] = mx;
+      pair_barrier(quad);
+      mx = fmaxf(mx, xch[half ^ 1][row]);
+      const float m_new = fmaxf(m_run, __fmul_rn(mx, scale_log2e));
+      const float resc = ex2_approx(__fsub_rn(m_run, m_new)); // 0 on the first block
+      m_run = m_new;
+      const float neg_m = -m_new;
+      float psum = 0.0f;
+#pragma unroll 1
+      for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
+        uint32_t v[32];
+        tmem_ld32(t_s + lane_base + (uint32_t)c, v);
+        tmem_ld_wait();
+        uint32_t whi[16], wlo[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 =
+              ex2_approx(__fmaf_rn(__uint_as_float(v[2 * i]), scale_log2e, neg_m));
+          const float p1 = ex2_approx(
+              __fmaf_rn(__uint_as_float(v[2 * i + 1]), scale_log2e, neg_m));
+          psum = __fadd_rn(psum, __fadd_rn(p0, p1));
+          const uint32_t hi = cvt_bf16x2(p0, p1);
+          const float r0 = __fsub_rn(p0, __uint_as_float(hi << 16));
+          const float r1 = __fsub_rn(p1, __uint_as_float(hi & 0xffff0000u));
+          whi[i] = hi;
+          wlo[i] = cvt_bf16x2(r0, r1);
         }
-        umma_commit(smem_u32(&bar_o));
-        ok = mbar_wait(smem_u32(&bar_o), ph, abortp, t0);
-        if (ok && j + 1 < nkb) { // the V buffers are free again
-          mbar_expect_tx(smem_u32(&bar_v), 2 * kTile);
-          tma_load_2d(s_vh, &map_hi, cv, row_kv + (j + 1) * kTK, smem_u32(&bar_v));
-          tma_load_2d(s_vl, &map_lo, cv, row_kv + (j + 1) * kTK, smem_u32(&bar_v));
+        // P of keys c..c+31: hi in columns c..c+15, lo in c+16..c+31 (the
+        // scores of those columns are already consumed).
+        tmem_st16(t_s + lane_base + (uint32_t)c, whi);
+        tmem_st16(t_s + lane_base + (uint32_t)c + 16u, wlo);
+      }
+      l_run = __fadd_rn(__fmul_rn(l_run, resc), psum);
+      tmem_st_wait();
+      tcgen05_fence_before();
+      __syncthreads(); // every row of P is in tensor memory
+
+      // ---- O_j = P V_j ----
+      if (tid == 0) {
+        tcgen05_fence_after();
+        ok = mbar_wait(smem_u32(&bar_v), ph, abortp, t0);
+        if (ok) {
+          tcgen05_fence_after();
+          // small terms first: Pl Vh, Ph Vl, then Ph Vh
+          const uint32_t pa[3] = {16u, 0u, 0u}; // column offset of lo / hi inside a chunk
+          const uint32_t vb[3] = {s_vh, s_vl, s_vh};
+          static_assert(kTK == 128, "two groups of four 16-key slices per block");
+#pragma unroll
+          for (int t = 0; t < 3; ++t) {
+            const uint64_t dv = make_smem_desc(vb[t]);
+            umma_bf16_ts_x4(t_o, t_s + pa[t], dv, kIdescPV, t != 0 ? 1u : 0u);
+            umma_bf16_ts_x4(t_o, t_s + 64u + pa[t], dv + 512, kIdescPV, 1u);
+          }
+          umma_commit(smem_u32(&bar_o));
+          ok = mbar_wait(smem_u32(&bar_o), ph, abortp, t0);
+          if (ok && j + 1 < nkb) { // the V buffers are free again
+            mbar_expect_tx(smem_u32(&bar_v), 2 * kTile);
+            tma_load_2d(s_vh, &map_hi, it.cv, it.row_kv + (j + 1) * kTK, smem_u32(&bar_v));
+            tma_load_2d(s_vl, &map_lo, it.cv, it.row_kv + (j + 1) * kTK, smem_u32(&bar_v));
+          }
         }
       }
+      ok = __syncthreads_and(ok) != 0;
+      if (!ok)
+        break;
+      tcgen05_fence_after();
+      __syncwarp();
+      {
+        uint32_t v[32];
+        tmem_ld32(t_o + lane_base + (uint32_t)(half * 32), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          o[i] = __fmaf_rn(o[i], resc, __uint_as_float(v[i]));
+      }
+      tcgen05_fence_before();
     }
-    ok = __syncthreads_and(ok) != 0;
     if (!ok)
       break;
-    tcgen05_fence_after();
-    __syncwarp();
-    {
-      uint32_t v[32];
-      tmem_ld32(t_o + lane_base + (uint32_t)(half * 32), v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        o[i] = __fmaf_rn(o[i], resc, __uint_as_float(v[i]));
-    }
-    tcgen05_fence_before();
-  }
 
-  if (ok) {
-    // Row sum over both halves, then normalise and store this thread's 32
-    // output columns and fold them into the running range.
+    // Row sum over both halves, then normalise.  The 128 x 64 result leaves
+    // through the V buffers (free after the last P V): half 0's 32 columns in
+    // the first 16 KiB tile, half 1's in the second, rows of 128 bytes in the
+    // 128-byte swizzle pattern, one TMA store per tile, which writes whole
+    // lines.  The next item's V load waits for the store to have read them.
     xch[half][row] = l_run;
     pair_barrier(quad);
     const float inv = __fdiv_rn(1.0f, __fadd_rn(xch[0][row], xch[1][row]));
-    float *dst = out + ((int64_t)row_q + row) * ld_out + h * kTDh + half * 32;
-    float lo = INFINITY, hi = -INFINITY;
+    const uint32_t my_row = (half ? s_vl : s_vh) + (uint32_t)row * 128u;
+    const uint32_t swz = ((uint32_t)row & 7u) << 4;
 #pragma unroll
     for (int i = 0; i < kTDh / 2; i += 4) {
-      float4 v = make_float4(__fmul_rn(o[i], inv), __fmul_rn(o[i + 1], inv),
+      const float4 v = make_float4(__fmul_rn(o[i], inv), __fmul_rn(o[i + 1], inv),
           __fmul_rn(o[i + 2], inv), __fmul_rn(o[i + 3], inv));
-      *reinterpret_cast<float4 *>(dst + i) = v;
-      lo = fminf(lo, fminf(fminf(v.x, v.y), fminf(v.z, v.w)));
-      hi = fmaxf(hi, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(
+                       my_row + (((uint32_t)i * 4u) ^ swz)),
+                   "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                   : "memory");
+      lo_run = fminf(lo_run, fminf(fminf(v.x, v.y), fminf(v.z, v.w)));
+      hi_run = fmaxf(hi_run, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
     }
-    if (out_range)
-      range_commit_warp(out_range, lo, hi);
+    fence_proxy_async_smem(); // the tiles were written through the generic proxy
+    __syncthreads();
+    if (tid == 0) {
+      tma_store_2d(&map_out, s_vh, it.col_out, it.row_q);
+      tma_store_2d(&map_out, s_vl, it.col_out + 32, it.row_q);
+      tma_store_commit();
+    }
   }
+
+  if (ok && out_range && (int64_t)blockIdx.x < n_items)
+    range_commit_warp(out_range, lo_run, hi_run);
+  if (tid == 0)
+    tma_store_wait_all();
 
   // ---- teardown ----
   tcgen05_fence_before();
@@ -428,7 +493,7 @@ bool attention_tc_supported(int64_t B, int64_t S, int64_t heads, int64_t dh,
   }();
   if (disabled)
     return false;
-  return dh == kTDh && S > 0 && S % kTK == 0 && B * heads <= 65535 &&
+  return dh == kTDh && S > 0 && S % kTK == 0 && B * heads > 0 &&
          B * S < (int64_t(1) << 31) && ld_planes % 8 == 0 && ld_out % 4 == 0 &&
          ((((uintptr_t)hi | (uintptr_t)lo | (uintptr_t)out) & 15u) == 0);
 }
@@ -446,20 +511,28 @@ int launch_attention_tc(const void *hi, const void *lo, int64_t ld_planes,
     attr_set = true;
   }
   const int64_t T = B * S;
-  CUtensorMap map_hi, map_lo;
+  CUtensorMap map_hi, map_lo, map_out;
   int rc = make_tma_map_2d(&map_hi, hi, T, ld_planes, ld_planes * 2, kTDh, kTK, 2, 128);
   if (rc != OMCUDA_OK)
     return rc;
   rc = make_tma_map_2d(&map_lo, lo, T, ld_planes, ld_planes * 2, kTDh, kTK, 2, 128);
   if (rc != OMCUDA_OK)
     return rc;
+  // output: boxes of 128 rows x 32 fp32 columns (128-byte rows)
+  rc = make_tma_map_2d(&map_out, out, T, heads * kTDh, ld_out * 4, 32, kTQ, 4, 128);
+  if (rc != OMCUDA_OK)
+    return rc;
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "Attention: cannot allocate the status word");
-  dim3 grid((unsigned)(S / kTQ), (unsigned)(B * heads));
+  // Persistent CTAs, two per SM, each walking its share of the
+  // (batch, head, 128-query-row) items.
+  const int64_t n_items = (S / kTQ) * B * heads;
+  const int64_t resident = (int64_t)sm_count() * 2;
+  const unsigned grid = (unsigned)(n_items < resident ? n_items : resident);
   const float scale_log2e = scale * 1.4426950408889634f;
-  attention_tc_kernel<<<grid, kTcAttThreads, kTcAttSmem, st>>>(map_hi, map_lo, (int32_t)q_col,
-      (int32_t)k_col, (int32_t)v_col, S, heads, scale_log2e, out, ld_out,
+  attention_tc_kernel<<<grid, kTcAttThreads, kTcAttSmem, st>>>(map_hi, map_lo, map_out,
+      (int32_t)q_col, (int32_t)k_col, (int32_t)v_col, S, heads, n_items, scale_log2e,
       (uint32_t *)out_range, status);
   OMCUDA_CHECK_LAUNCH("attention_tc_kernel");
   return OMCUDA_OK;
