@@ -660,13 +660,42 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 //   empty[s]      (each)    tcgen05.commit to both CTAs when the MMAs are done
 //   acc_full[b]   (each)    tcgen05.commit to both CTAs after the last K step
 //   acc_empty[b]  (leader)  16 arrives: the 8 epilogue warps of both CTAs
+//
+// Work units.  Whole 256 x 256 tiles are dealt round-robin to the clusters.
+// When the tiles left over after the last complete round would keep at most
+// half of the clusters busy, each of them is cut into two 256 x 128 units
+// (tcgen05.mma with N = 128, 64 B columns per CTA), so that the last round
+// takes about half as long: units [0, full_units) are whole tiles, the rest
+// alternate between the two halves of the remaining tiles.
+struct PairUnit {
+  int64_t tile;
+  int narrow; // 1: a 128-column half tile
+  int half;   // which half
+};
+
+__device__ __forceinline__ PairUnit pair_unit(int64_t u, int64_t full_units) {
+  PairUnit r;
+  if (u < full_units) {
+    r.tile = u;
+    r.narrow = 0;
+    r.half = 0;
+  } else {
+    const int64_t k = u - full_units;
+    r.tile = full_units + (k >> 1);
+    r.narrow = 1;
+    r.half = (int)(k & 1);
+  }
+  return r;
+}
+
 template <int EPI, int EW>
 __global__ void __launch_bounds__(tc_threads(EW), 1)
     gemm_i8_tc2_kernel(const __grid_constant__ CUtensorMap map_a,
         const __grid_constant__ CUtensorMap map_b,
+        const __grid_constant__ CUtensorMap map_b_half,
         const __grid_constant__ CUtensorMap map_y,
         const __grid_constant__ CUtensorMap map_y2, EpiParams p, uint32_t idesc,
-        int *status) {
+        uint32_t idesc_half, int64_t full_units, int64_t num_units, int *status) {
   constexpr int BN = 256;
   constexpr int kABytes = kBM * kBK;
   constexpr int kBHalfBytes = (BN / 2) * kBK;
@@ -694,9 +723,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t staging_base = smem_base + kStages * kStageBytes;
 
-  const int64_t tiles_m = ceil_div(p.M, 2 * kBM);
   const int64_t tiles_n = ceil_div(p.N, BN);
-  const int64_t num_tiles = tiles_m * tiles_n;
   const int num_kb = (int)ceil_div(p.K, kBK);
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -725,9 +752,15 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+      for (int64_t u = cluster_id; u < num_units && ok; u += num_clusters) {
+        const PairUnit un = pair_unit(u, full_units);
+        const int64_t t = un.tile;
         const int32_t m0 = (int32_t)((t / tiles_n) * (2 * kBM) + rank * kBM);
-        const int32_t n0 = (int32_t)((t % tiles_n) * BN + rank * (BN / 2));
+        // this CTA's share of the B columns: 128 of 256, or 64 of 128
+        const int32_t n0 = un.narrow
+                               ? (int32_t)((t % tiles_n) * BN + un.half * (BN / 2) + rank * (BN / 4))
+                               : (int32_t)((t % tiles_n) * BN + rank * (BN / 2));
+        const uint32_t stage_tx = un.narrow ? kABytes + kBHalfBytes / 2 : kStageBytes;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, t0)) {
             ok = false;
@@ -737,9 +770,9 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kABytes;
           if (rank == 0)
-            mbar_expect_tx(smem_u32(&bar_full[stage]), 2 * kStageBytes);
+            mbar_expect_tx(smem_u32(&bar_full[stage]), 2 * stage_tx);
           tma_load_2d_pair(sa, &map_a, kb * kBK, m0, full_leader);
-          tma_load_2d_pair(sb, &map_b, kb * kBK, n0, full_leader);
+          tma_load_2d_pair(sb, un.narrow ? &map_b_half : &map_b, kb * kBK, n0, full_leader);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -754,7 +787,8 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       uint32_t phase = 0;
       bool ok = true;
       int64_t it = 0;
-      for (int64_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+      for (int64_t u = cluster_id; u < num_units && ok; u += num_clusters, ++it) {
+        const uint32_t unit_idesc = u < full_units ? idesc : idesc_half;
         const int buf = (int)(it & 1);
         const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
         if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp, t0)) {
@@ -772,7 +806,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kABytes;
           static_assert(kBK / kUmmaK == 4, "four K slices per stage");
-          umma_i8_pair_x4(d_tmem, make_smem_desc(sa), make_smem_desc(sb), idesc,
+          umma_i8_pair_x4(d_tmem, make_smem_desc(sa), make_smem_desc(sb), unit_idesc,
               kb != 0 ? 1u : 0u);
           umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
           if (++stage == kStages) {
@@ -797,12 +831,16 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
     bool ok = active;
     int64_t it = 0;
     float lo = INFINITY, hi = -INFINITY; // range of this warp's f32 outputs
-    for (int64_t t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+    for (int64_t u = cluster_id; u < num_units && ok; u += num_clusters, ++it) {
+      const PairUnit un = pair_unit(u, full_units);
+      const int64_t t = un.tile;
       const int buf = (int)(it & 1);
       const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
       const int64_t m_warp = (t / tiles_n) * (2 * kBM) + rank * kBM + quad * 32;
-      const int64_t n0 = (t % tiles_n) * BN + c_lo;
-      {
+      const int64_t n0 = (t % tiles_n) * BN + un.half * (BN / 2) + c_lo;
+      // a half tile keeps only the warps of accumulator columns 0..127 busy
+      const bool mine = !un.narrow || c_lo < BN / 2;
+      if (mine) {
         const int line = lane & 7, which = lane >> 3;
         const int64_t nl = n0 + 32 * line;
         const void *src = nullptr;
@@ -831,8 +869,9 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       tcgen05_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
-      epilogue_tile<BN, EPI, EW>(p, sc, qc, taddr, m_warp, n0, slab0, lane, use_slab,
-          lo, hi, &map_y, &map_y2);
+      if (mine)
+        epilogue_tile<BN, EPI, EW>(p, sc, qc, taddr, m_warp, n0, slab0, lane, use_slab,
+            lo, hi, &map_y, &map_y2);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0)
@@ -942,11 +981,6 @@ uint32_t make_idesc(int a_signed, int b_signed, int n) {
   return d;
 }
 
-// Tensor maps of the output for the epilogue's TMA stores: boxes of 32 rows x
-// one slab row (32 f32 / i32 columns; kHalfCols, at most 128, u8 columns; 32
-// bf16 columns of the hi and of the lo plane).  Only encoded when Y can take
-// them (16-byte aligned base and row pitch); otherwise the kernel stores
-// directly and never reads the maps.
 // 16-byte stores of whole lines need an aligned base and row pitch (the
 // range-only tail stores nothing and walks the tile the same way).
 template <int EPI>
@@ -959,6 +993,11 @@ bool y_takes_line_stores(const omcudaGemmArgs &a) {
   return (((uintptr_t)a.Y & 15u) == 0) && ((a.N * esize) % 16 == 0);
 }
 
+// Tensor maps of the output for the epilogue's TMA stores: boxes of 32 rows x
+// one slab row (32 f32 / i32 columns; kHalfCols, at most 128, u8 columns; 32
+// bf16 columns of the hi and of the lo plane).  Only encoded when Y can take
+// them (16-byte aligned base and row pitch); otherwise the kernel stores
+// directly and never reads the maps.
 template <int EPI>
 int make_y_maps(const omcudaGemmArgs &a, int half_cols, bool line_store,
     CUtensorMap *map_y, CUtensorMap *map_y2) {
@@ -1057,6 +1096,15 @@ int launch_bn(const omcudaGemmArgs &a, cudaStream_t st) {
 }
 
 
+// OMCUDA_GEMM_HALF_TILES=0 keeps every unit a whole tile, for experiments.
+inline bool pair_half_tiles_wanted() {
+  static const bool on = [] {
+    const char *s = getenv("OMCUDA_GEMM_HALF_TILES");
+    return !(s && atoi(s) == 0);
+  }();
+  return on;
+}
+
 // The 2-CTA kernel: 256 x 256 tiles on clusters of two CTAs.
 template <int EPI, int EW>
 int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
@@ -1090,16 +1138,29 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   rc = make_map(&map_b, a.B.bt, a.N, a.B.kp, a.B.kp, 128);
   if (rc != OMCUDA_OK)
     return rc;
+  CUtensorMap map_b_half; // 64 B columns per CTA: the 256 x 128 units
+  rc = make_map(&map_b_half, a.B.bt, a.N, a.B.kp, a.B.kp, 64);
+  if (rc != OMCUDA_OK)
+    return rc;
   EpiParams p = make_epi_params(a);
   p.line_store = y_takes_line_stores<EPI>(a);
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
   int64_t tiles = ceil_div(a.M, 2 * kBM) * ceil_div(a.N, 256);
-  int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
-  // M = 256 across the pair (field holds M / 16), N = 256.
+  // Units: whole tiles for the complete rounds; a last round that would keep
+  // at most half of the clusters busy runs as twice as many half tiles.
+  const int64_t rounds_full = (tiles / max_clusters) * max_clusters;
+  const int64_t rest = tiles - rounds_full;
+  const bool split_rest = rest > 0 && 2 * rest <= max_clusters && pair_half_tiles_wanted();
+  const int64_t full_units = split_rest ? rounds_full : tiles;
+  const int64_t num_units = split_rest ? rounds_full + 2 * rest : tiles;
+  int clusters = (int)(num_units < max_clusters ? num_units : max_clusters);
+  // M = 256 across the pair (field holds M / 16), N = 256 or 128.
   uint32_t idesc = make_idesc(a.a_signed, a.B.b_signed, 256);
   idesc = (idesc & ~(0x1fu << 24)) | ((uint32_t)(256 >> 4) << 24);
+  uint32_t idesc_half = make_idesc(a.a_signed, a.B.b_signed, 128);
+  idesc_half = (idesc_half & ~(0x1fu << 24)) | ((uint32_t)(256 >> 4) << 24);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -1117,7 +1178,7 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   if (rc != OMCUDA_OK)
     return rc;
   OMCUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_i8_tc2_kernel<EPI, EW>, map_a, map_b,
-      map_y, map_y2, p, idesc, status));
+      map_b_half, map_y, map_y2, p, idesc, idesc_half, full_units, num_units, status));
   count_launch();
   return OMCUDA_OK;
 }

@@ -285,7 +285,8 @@ def test_dequant_split_epilogue_equals_split_of_dequant(gpu, M, K, N):
 
 
 @pytest.mark.parametrize("M,K,N,gelu", [(300, 256, 192, 1), (1024, 1024, 4096, 1),
-                                        (33, 64, 72, 0), (515, 512, 1000, 1)])
+                                        (33, 64, 72, 0), (515, 512, 1000, 1),
+                                        (2600, 512, 1800, 1)])
 def test_range_then_quantizing_tails_equal_dequant_then_quantize(gpu, M, K, N, gelu):
     # "linear -> DynamicQuantizeLinear" run as two passes over the product
     # (range only, then quantize while storing uint8) must give the bytes,
@@ -340,11 +341,14 @@ def test_range_then_quantizing_tails_equal_dequant_then_quantize(gpu, M, K, N, g
     assert par.numpy()[0] == scale
 
 
-@pytest.mark.parametrize("M,K,N", [(4096, 4096, 4096), (5000, 2048, 4104), (300, 512, 1000)])
+@pytest.mark.parametrize("M,K,N", [(4096, 4096, 4096), (5000, 2048, 4104), (300, 512, 1000),
+                                   (2600, 512, 1800), (9300, 256, 2048)])
 def test_whole_output_checksums(gpu, orc, M, K, N):
     # Every tile of the output is stored exactly once (the epilogue leaves
     # through TMA stores that clip ragged edges): sampled rows against the
     # oracle and column sums of the whole result against exact integer sums.
+    # 4096^3, 2600 x 1800 and 9300 x 2048 end in a round of 256 x 128 half
+    # tiles on the 2-CTA kernel (the last two with ragged edges).
     from gpu_util import DevGemm
     rng = np.random.default_rng(K + N)
     A = rng.integers(0, 256, (M, K), dtype=np.uint8)
