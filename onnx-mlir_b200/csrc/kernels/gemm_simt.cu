@@ -216,7 +216,9 @@ EpiParams make_epi_params(const omcudaGemmArgs &a) {
   p.q_params = a.q_params;
   p.q_scale = a.q_scale;
   p.q_zp = a.q_zp;
-  p.vec_ok = ((((uintptr_t)a.B.colsum | (uintptr_t)a.bias | (uintptr_t)a.sb) & 15u) == 0) &&
+  // (a scalar scale is read with a scalar load wherever it lies)
+  const uintptr_t sb_vec = a.sb_len > 1 ? (uintptr_t)a.sb : 0;
+  p.vec_ok = ((((uintptr_t)a.B.colsum | (uintptr_t)a.bias | sb_vec) & 15u) == 0) &&
              (a.N % 4 == 0);
   p.line_store = 0;
   return p;
