@@ -111,6 +111,77 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, r));
 }
 
+// Three-input fp32 min / max of sm_100 (same result as two fminf / fmaxf:
+// NaN operands are dropped).
+__device__ __forceinline__ float min3f(float a, float b, float c) {
+  float r;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Two Gelus at once on the packed-fp32 instructions of sm_100
+// (mul / add / fma .f32x2: two independent, individually rounded fp32
+// operations per instruction, so each lane gets exactly the bits gelu_erf
+// gives it).  Halves the FMA-pipe instructions of the polynomial, which
+// matters where the GEMM tail is bound by instruction issue.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+__device__ __forceinline__ void gelu_erf_x2(float &x0, float &x1) {
+  const uint64_t x = pack_f32x2(x0, x1);
+  float t0, t1;
+  unpack_f32x2(mul_f32x2(x, pack_f32x2(0.70710678118654752440f, 0.70710678118654752440f)),
+      t0, t1);
+  const uint64_t t = pack_f32x2(fminf(fabsf(t0), 4.0f), fminf(fabsf(t1), 4.0f));
+#define OMCUDA_C2(c) pack_f32x2(c, c)
+  uint64_t q = OMCUDA_C2(-4.5358585339272395e-05f);
+  q = fma_f32x2(q, t, OMCUDA_C2(0.00044550743768922985f));
+  q = fma_f32x2(q, t, OMCUDA_C2(-0.0014894406776875257f));
+  q = fma_f32x2(q, t, OMCUDA_C2(-0.0007746315677650273f));
+  q = fma_f32x2(q, t, OMCUDA_C2(0.02825368382036686f));
+  q = fma_f32x2(q, t, OMCUDA_C2(-0.14848162233829498f));
+  q = fma_f32x2(q, t, OMCUDA_C2(-0.9184163808822632f));
+  q = fma_f32x2(q, t, OMCUDA_C2(-1.6279085874557495f));
+  float a0, a1;
+  unpack_f32x2(mul_f32x2(q, t), a0, a1);
+  float e0, e1;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(a0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(a1));
+  // 1 - e, sign of x restored, then 0.5 x (1 + r)
+  const float r0 = copysignf(__fsub_rn(1.0f, e0), x0);
+  const float r1 = copysignf(__fsub_rn(1.0f, e1), x1);
+  const uint64_t h = mul_f32x2(OMCUDA_C2(0.5f), x);
+  const uint64_t s = add_f32x2(OMCUDA_C2(1.0f), pack_f32x2(r0, r1));
+#undef OMCUDA_C2
+  unpack_f32x2(mul_f32x2(h, s), x0, x1);
+}
+
 // Order-preserving float <-> uint mapping so running min/max can use integer
 // atomics.  NaNs never reach these (callers filter with fminf/fmaxf).
 __device__ __forceinline__ uint32_t f32_to_ordered(float f) {

@@ -164,9 +164,11 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
       f[j] = __int2float_rn((int32_t)v[j]);
     if (p.sb_len == 1) {
       if (p.form == 0) {
+        // (packed fp32: two exactly rounded products per instruction)
+        const uint64_t s2 = pack_f32x2(sc.s0, sc.s0);
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          f[j] = __fmul_rn(f[j], sc.s0);
+        for (int j = 0; j < 32; j += 2)
+          unpack_f32x2(mul_f32x2(pack_f32x2(f[j], f[j + 1]), s2), f[j], f[j + 1]);
       } else {
         const float sb = __ldg(p.sb);
 #pragma unroll
@@ -185,13 +187,14 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
       float b[32];
       load_cols32(p.bias, nc, valid, vec, b);
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        f[j] = __fadd_rn(f[j], b[j]);
+      for (int j = 0; j < 32; j += 2)
+        unpack_f32x2(add_f32x2(pack_f32x2(f[j], f[j + 1]), pack_f32x2(b[j], b[j + 1])),
+            f[j], f[j + 1]);
     }
     if (p.gelu) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        f[j] = gelu_erf(f[j]);
+      for (int j = 0; j < 32; j += 2)
+        gelu_erf_x2(f[j], f[j + 1]);
     }
     if (EPI == OMCUDA_EPI_DEQUANT && res_row) {
       float r[32];
@@ -202,10 +205,11 @@ __device__ __forceinline__ void epilogue_chunk(const EpiParams &p,
     }
     if (p.out_range) {
       if (valid == 32) {
+        // three-input min / max: one instruction per two values
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          lo = fminf(lo, f[j]);
-          hi = fmaxf(hi, f[j]);
+        for (int j = 0; j < 32; j += 2) {
+          lo = min3f(lo, f[j], f[j + 1]);
+          hi = max3f(hi, f[j], f[j + 1]);
         }
       } else {
 #pragma unroll
