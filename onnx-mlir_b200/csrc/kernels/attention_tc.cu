@@ -327,8 +327,8 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
         tmem_ld32(t_s + lane_base + (uint32_t)c, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          mx = fmaxf(mx, __uint_as_float(v[i]));
+        for (int i = 0; i < 32; i += 2)
+          mx = max3f(mx, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
       }
       // Row maximum over both halves (the two threads of a row sit in warps w
       // and w + 4: a 64-thread named barrier per quadrant).
@@ -338,8 +338,11 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
       const float m_new = fmaxf(m_run, __fmul_rn(mx, scale_log2e));
       const float resc = ex2_approx(__fsub_rn(m_run, m_new)); // 0 on the first block
       m_run = m_new;
-      const float neg_m = -m_new;
-      float psum = 0.0f;
+      // (packed fp32 below: two individually rounded operations per instruction)
+      const uint64_t scale2 = pack_f32x2(scale_log2e, scale_log2e);
+      const uint64_t neg_m2 = pack_f32x2(-m_new, -m_new);
+      const uint64_t minus1 = pack_f32x2(-1.0f, -1.0f);
+      uint64_t psum2 = pack_f32x2(0.0f, 0.0f);
 #pragma unroll 1
       for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
         uint32_t v[32];
@@ -348,14 +351,21 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
         uint32_t whi[16], wlo[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 =
-              ex2_approx(__fmaf_rn(__uint_as_float(v[2 * i]), scale_log2e, neg_m));
-          const float p1 = ex2_approx(
-              __fmaf_rn(__uint_as_float(v[2 * i + 1]), scale_log2e, neg_m));
-          psum = __fadd_rn(psum, __fadd_rn(p0, p1));
+          float a0, a1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(v[2 * i]),
+                                     __uint_as_float(v[2 * i + 1])),
+                           scale2, neg_m2),
+              a0, a1);
+          const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
+          const uint64_t p2 = pack_f32x2(p0, p1);
+          psum2 = add_f32x2(psum2, p2);
           const uint32_t hi = cvt_bf16x2(p0, p1);
-          const float r0 = __fsub_rn(p0, __uint_as_float(hi << 16));
-          const float r1 = __fsub_rn(p1, __uint_as_float(hi & 0xffff0000u));
+          // p - hi: one rounding, as the subtraction has
+          float r0, r1;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(hi << 16),
+                                     __uint_as_float(hi & 0xffff0000u)),
+                           minus1, p2),
+              r0, r1);
           whi[i] = hi;
           wlo[i] = cvt_bf16x2(r0, r1);
         }
@@ -364,7 +374,9 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
         tmem_st16(t_s + lane_base + (uint32_t)c, whi);
         tmem_st16(t_s + lane_base + (uint32_t)c + 16u, wlo);
       }
-      l_run = __fadd_rn(__fmul_rn(l_run, resc), psum);
+      float ps0, ps1;
+      unpack_f32x2(psum2, ps0, ps1);
+      l_run = __fadd_rn(__fmul_rn(l_run, resc), __fadd_rn(ps0, ps1));
       tmem_st_wait();
       tcgen05_fence_before();
       __syncthreads(); // every row of P is in tensor memory
@@ -404,8 +416,12 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
         tmem_ld32(t_o + lane_base + (uint32_t)(half * 32), v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          o[i] = __fmaf_rn(o[i], resc, __uint_as_float(v[i]));
+        const uint64_t resc2 = pack_f32x2(resc, resc);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          unpack_f32x2(fma_f32x2(pack_f32x2(o[i], o[i + 1]), resc2,
+                           pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]))),
+              o[i], o[i + 1]);
       }
       tcgen05_fence_before();
     }
