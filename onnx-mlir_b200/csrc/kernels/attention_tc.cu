@@ -58,7 +58,7 @@ constexpr int kTK = 128;            // keys per block
 constexpr int kTDh = 64;            // head size
 constexpr int kTile = 128 * 128;    // bytes of one 128-row x 64-bf16 tile
 constexpr int kTcAttSmem = 6 * kTile + 1024;
-constexpr uint32_t kTmemColsAtt = 256; // S/P: 0..127, O_j: 128..191
+constexpr uint32_t kTmemColsAtt = 256; // S/P: 0..127, O_j: 128..255
 constexpr int kTcAttThreads = 256;     // two threads per query row
 
 // Four MMAs over the four 16-element K slices of a 64-wide K-major operand
@@ -252,6 +252,12 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
 
   constexpr uint32_t kIdescQK = att_idesc(kTK, 0);
   constexpr uint32_t kIdescPV = att_idesc(kTDh, 1);
+  // P_hi against V_hi and V_lo in one MMA of N = 128: the B descriptor's
+  // leading-dimension offset (stride between 64-element groups along N) is
+  // the distance from the V_hi tile to the V_lo tile, so output columns
+  // 0..63 hold P_hi V_hi and 64..127 hold P_hi V_lo.
+  constexpr uint32_t kIdescPV2 = att_idesc(2 * kTDh, 1);
+  constexpr uint64_t kLboField = (uint64_t)0x3fff << 16;
 
   bool ok = true;
   uint32_t nblk = 0;  // key blocks done by this CTA: parity of bar_k / s / v / o
@@ -387,16 +393,15 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
         ok = mbar_wait(smem_u32(&bar_v), ph, abortp, t0);
         if (ok) {
           tcgen05_fence_after();
-          // small terms first: Pl Vh, Ph Vl, then Ph Vh
-          const uint32_t pa[3] = {16u, 0u, 0u}; // column offset of lo / hi inside a chunk
-          const uint32_t vb[3] = {s_vh, s_vl, s_vh};
           static_assert(kTK == 128, "two groups of four 16-key slices per block");
-#pragma unroll
-          for (int t = 0; t < 3; ++t) {
-            const uint64_t dv = make_smem_desc(vb[t]);
-            umma_bf16_ts_x4(t_o, t_s + pa[t], dv, kIdescPV, t != 0 ? 1u : 0u);
-            umma_bf16_ts_x4(t_o, t_s + 64u + pa[t], dv + 512, kIdescPV, 1u);
-          }
+          const uint64_t dvh = make_smem_desc(s_vh);
+          const uint64_t dv2 = (dvh & ~kLboField) | ((uint64_t)((s_vl - s_vh) >> 4) << 16);
+          // P_hi [V_hi | V_lo] into columns 0..127 of O_j, then P_lo V_hi on
+          // top of columns 0..63 (hi parts at column offset 0, lo at 16)
+          umma_bf16_ts_x4(t_o, t_s, dv2, kIdescPV2, 0u);
+          umma_bf16_ts_x4(t_o, t_s + 64u, dv2 + 512, kIdescPV2, 1u);
+          umma_bf16_ts_x4(t_o, t_s + 16u, dvh, kIdescPV, 1u);
+          umma_bf16_ts_x4(t_o, t_s + 64u + 16u, dvh + 512, kIdescPV, 1u);
           umma_commit(smem_u32(&bar_o));
           ok = mbar_wait(smem_u32(&bar_o), ph, abortp, t0);
           if (ok && j + 1 < nkb) { // the V buffers are free again
@@ -420,6 +425,14 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
 #pragma unroll
         for (int i = 0; i < 32; i += 2)
           unpack_f32x2(fma_f32x2(pack_f32x2(o[i], o[i + 1]), resc2,
+                           pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]))),
+              o[i], o[i + 1]);
+        // ... and the P_hi V_lo part from the upper 64 columns
+        tmem_ld32(t_o + 64u + lane_base + (uint32_t)(half * 32), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2)
+          unpack_f32x2(add_f32x2(pack_f32x2(o[i], o[i + 1]),
                            pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]))),
               o[i], o[i + 1]);
       }
@@ -541,12 +554,12 @@ int launch_attention_tc(const void *hi, const void *lo, int64_t ld_planes,
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "Attention: cannot allocate the status word");
+  const int64_t n_items = (S / kTQ) * B * heads;
+  const float scale_log2e = scale * 1.4426950408889634f;
   // Persistent CTAs, two per SM, each walking its share of the
   // (batch, head, 128-query-row) items.
-  const int64_t n_items = (S / kTQ) * B * heads;
   const int64_t resident = (int64_t)sm_count() * 2;
   const unsigned grid = (unsigned)(n_items < resident ? n_items : resident);
-  const float scale_log2e = scale * 1.4426950408889634f;
   attention_tc_kernel<<<grid, kTcAttThreads, kTcAttSmem, st>>>(map_hi, map_lo, map_out,
       (int32_t)q_col, (int32_t)k_col, (int32_t)v_col, S, heads, n_items, scale_log2e,
       (uint32_t *)out_range, status);
