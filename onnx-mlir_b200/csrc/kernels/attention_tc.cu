@@ -32,9 +32,13 @@
 //              maximum (exchanged through shared memory), p = 2^(s*c - m),
 //              running sum, p split into bf16 hi/lo and stored back over the
 //              scores in tensor memory;
-//   thread 0   issues O_j = P V as 24 MMAs with P read from tensor memory and
-//              V (keys x 64, MN-major) from shared memory; refills V;
-//   8 warps    o = o * 2^(m_old - m_new) + O_j in registers (32 columns each).
+//   thread 0   issues O_j = P V as 16 MMAs with P read from tensor memory and
+//              V (keys x 64, MN-major) from shared memory: P_hi against
+//              [V_hi | V_lo] as one N = 128 product per 16-key slice (into
+//              128 columns of tensor memory), P_lo V_hi on top of the first
+//              64 columns; refills V;
+//   8 warps    o = o * 2^(m_old - m_new) + O_j in registers (32 columns each;
+//              O_j = the sum of the two 64-column halves).
 // The normalised 128 x 64 result of an item is staged in the (then free) V
 // buffers and leaves with two TMA stores of whole 128-byte lines.
 // Every wait on an mbarrier is bounded (tc_ptx.cuh); a timeout raises the
