@@ -544,6 +544,10 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       uint32_t phase = 0;
       bool ok = true;
       int64_t it = 0;
+      // The issuing thread is a chain of dependent round trips (barrier poll,
+      // MMA issue, commit); whether a stage has landed is therefore asked one
+      // stage ahead, before the MMAs of the current stage are issued.
+      bool landed = false;
       for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int buf = (int)(it & 1);
         const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
@@ -554,10 +558,13 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, t0)) {
+          if (!landed && !mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, t0)) {
             ok = false;
             break;
           }
+          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
+          const uint32_t nphase = nstage == 0 ? phase ^ 1u : phase;
+          landed = mbar_test_wait(smem_u32(&bar_full[nstage]), nphase);
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
           const uint32_t sb = sa + Cfg::kABytes;
@@ -565,10 +572,8 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           umma_i8_x4(d_tmem, make_smem_desc(sa), make_smem_desc(sb), idesc,
               kb != 0 ? 1u : 0u);
           umma_commit(smem_u32(&bar_empty[stage]));
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          stage = nstage;
+          phase = nphase;
         }
         if (ok)
           umma_commit(smem_u32(&bar_acc_full[buf]));
@@ -791,6 +796,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       uint32_t phase = 0;
       bool ok = true;
       int64_t it = 0;
+      bool landed = false; // asked one stage ahead, see the single-CTA kernel
       for (int64_t u = cluster_id; u < num_units && ok; u += num_clusters, ++it) {
         const uint32_t unit_idesc = u < full_units ? idesc : idesc_half;
         const int buf = (int)(it & 1);
@@ -802,10 +808,13 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, t0)) {
+          if (!landed && !mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, t0)) {
             ok = false;
             break;
           }
+          const int nstage = stage + 1 == kStages ? 0 : stage + 1;
+          const uint32_t nphase = nstage == 0 ? phase ^ 1u : phase;
+          landed = mbar_test_wait(smem_u32(&bar_full[nstage]), nphase);
           tcgen05_fence_after();
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kABytes;
@@ -813,10 +822,8 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           umma_i8_pair_x4(d_tmem, make_smem_desc(sa), make_smem_desc(sb), unit_idesc,
               kb != 0 ? 1u : 0u);
           umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
-          }
+          stage = nstage;
+          phase = nphase;
         }
         if (ok)
           umma_commit_pair(smem_u32(&bar_acc_full[buf]), 3);

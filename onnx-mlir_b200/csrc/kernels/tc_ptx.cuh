@@ -53,6 +53,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking look at a barrier phase (mbarrier.test_wait never suspends the
+// thread): used to start the poll of the next pipeline stage before the
+// current stage's MMAs are issued, so that its latency is hidden behind them.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t"
+               ".reg .pred p;\n\t"
+               "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t"
+               "}"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Returns false when the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(
     uint32_t bar, uint32_t parity, volatile int *abort_flag, uint64_t t0) {
