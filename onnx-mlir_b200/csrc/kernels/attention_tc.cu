@@ -217,6 +217,11 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
                  s_kl = smem0 + 3 * kTile, s_vh = smem0 + 4 * kTile,
                  s_vl = smem0 + 5 * kTile;
 
+  if (tid == 32) {
+    prefetch_tensormap(&map_hi);
+    prefetch_tensormap(&map_lo);
+    prefetch_tensormap(&map_out);
+  }
   if (tid == 0) {
     abort_flag = 0;
     mbar_init(smem_u32(&bar_q), 1);

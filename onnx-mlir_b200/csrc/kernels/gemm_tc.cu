@@ -490,6 +490,15 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
   const int64_t num_tiles = tiles_m * tiles_n;
   const int num_kb = (int)ceil_div(p.K, kBK);
 
+  if (threadIdx.x == 32) { // (a thread that has nothing else to set up)
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    if (p.line_store) {
+      prefetch_tensormap(&map_y);
+      if (EPI == OMCUDA_EPI_DEQUANT_SPLIT)
+        prefetch_tensormap(&map_y2);
+    }
+  }
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
@@ -734,6 +743,15 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 
   const int64_t tiles_n = ceil_div(p.N, BN);
   const int num_kb = (int)ceil_div(p.K, kBK);
+  if (threadIdx.x == 32) { // (a thread that has nothing else to set up)
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+    if (p.line_store) {
+      prefetch_tensormap(&map_y);
+      if (EPI == OMCUDA_EPI_DEQUANT_SPLIT)
+        prefetch_tensormap(&map_y2);
+    }
+  }
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {

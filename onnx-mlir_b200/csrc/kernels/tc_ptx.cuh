@@ -86,6 +86,12 @@ __device__ __forceinline__ bool mbar_wait(
   return true;
 }
 
+// Starts the fetch of a tensor map (a kernel parameter) so that the first
+// TMA operation on it does not wait for the descriptor.
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map,
     int32_t x, int32_t y, uint32_t bar) {
   asm volatile(
