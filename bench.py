@@ -507,7 +507,7 @@ def run_gpu(args):
     # CPU baseline on a bounded sample of the same workload (rank 0, N=1 only).
     if world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(args.workload, wl)
-    print(json.dumps(out))
+    emit(out)
     if world > 1:
         dist.destroy_process_group()
 
@@ -593,7 +593,7 @@ def run_sweep(args):
     launches = env.m.launch_count() - launches0
     if rank == 0:
         big = [r for r in rows if r["M"] >= 4096]
-        print(json.dumps({
+        emit({
             "metric": LinearWorkload.metric, "value": tot_ops / tot_ms / 1e9, "unit": "TOPS",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": tot_ms, "higher_is_better": True, "scaling": "strong",
@@ -614,7 +614,7 @@ def run_sweep(args):
                          "peak_source": "2 x bf16 cuBLAS burst (%s); members with M >= 4096, "
                                         "per GPU" % peaks["source"],
                          "traffic": None},
-            "sweep": rows}))
+            "sweep": rows})
     if world > 1:
         dist.destroy_process_group()
 
@@ -683,7 +683,7 @@ def run_reference(args):
         config = {"workload": args.workload, "M": M, "N": N, "K": K}
         metric, dtype = LinearWorkload.metric, LinearWorkload.dtype
     dt = cb.pop("seconds_per_rep")
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": metric, "value": cb["value"],
         "unit": cb["unit"], "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
@@ -691,10 +691,28 @@ def run_reference(args):
         "dtype": dtype, "data": "synthetic", "config": config,
         "cpu_baseline": cb,
         "e2e": {"value": cb["value"], "unit": cb["unit"], "h2d_bytes_per_step": 0,
-                "d2h_bytes_per_step": 0}}))
+                "d2h_bytes_per_step": 0}})
+
+
+_JSON_OUT = None
+
+
+def _claim_stdout():
+    """Keeps stdout for the one JSON line: everything else a library prints
+    there (NCCL's version banner, for one) goes to stderr instead."""
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+
+
+def emit(obj):
+    _JSON_OUT.write(json.dumps(obj) + "\n")
+    _JSON_OUT.flush()
 
 
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
