@@ -506,7 +506,7 @@ def run_gpu(args):
     }
     # CPU baseline on a bounded sample of the same workload (rank 0, N=1 only).
     if world == 1 and not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_baseline(args.workload, wl)
+        out["cpu_baseline"] = cpu_baseline(args.workload, wl, long_sample=True)
     emit(out)
     if world > 1:
         dist.destroy_process_group()
@@ -619,8 +619,10 @@ def run_sweep(args):
         dist.destroy_process_group()
 
 
-def cpu_baseline(workload, wl=None, reps=1):
-    """Times the oracle's reference-shaped CPU code on a bounded sample."""
+def cpu_baseline(workload, wl=None, reps=1, long_sample=False):
+    """Times the oracle's reference-shaped CPU code on a bounded sample: about
+    a second of CPU work per repetition for the reference arm's steps, ten to
+    twenty seconds in all for the baseline of the default run (long_sample)."""
     import oracle_lib
     orc = oracle_lib.Oracle(os.path.join(ROOT, "oracle", "_build", "liboracle.so"))
     # All host cores this process may run on (torchrun exports OMP_NUM_THREADS=1).
@@ -634,6 +636,8 @@ def cpu_baseline(workload, wl=None, reps=1):
             from omcuda.synthetic import make_encoder
             layer = make_encoder(42, c["H"], c["F"], 1)[0]
         bs = 2 if workload == "bert_large" else 8
+        if long_sample:
+            bs, reps = (24, 1) if workload == "bert_large" else (c["B"], 6)
         x = np.random.default_rng(0).normal(size=(bs * c["S"], c["H"])).astype(np.float32)
         t0 = time.perf_counter()
         for _ in range(reps):
@@ -641,13 +645,15 @@ def cpu_baseline(workload, wl=None, reps=1):
         dt = (time.perf_counter() - t0) / reps
         return {"value": bs / (dt * c["layers"]), "unit": "seq/s", "cores": threads,
                 "kind": "port", "seconds_per_rep": dt,
-                "sample": "one of %d layers on %d of %d sequences (%.1f s), scaled "
-                          "by the layer count; oracle ops with OpenMP"
-                          % (c["layers"], bs, c["B"], dt)}
+                "sample": "one of %d layers on %d of %d sequences (%d x %.1f s), "
+                          "scaled by the layer count; oracle ops with OpenMP"
+                          % (c["layers"], bs, c["B"], reps, dt)}
     shapes = {"mmi_4096": (4096, 4096, 4096), "qlinear_c2": (16384, 4096, 1024)}
     M, N, K = shapes[workload]
     rng = np.random.default_rng(0)
     rows = 256
+    if long_sample:
+        rows, reps = M, (2 if workload == "mmi_4096" else 3)
     A = rng.integers(0, 256, (rows, K), dtype=np.uint8)
     W = wl.Wh if wl is not None else rng.integers(-127, 128, (K, N), dtype=np.int8)
     t0 = time.perf_counter()
@@ -658,7 +664,7 @@ def cpu_baseline(workload, wl=None, reps=1):
             "cores": threads, "kind": "port", "seconds_per_rep": dt,
             "sample": "%d of %d rows of the same [K=%d,N=%d] GEMM, reference-shaped "
                       "lowering (operands widened to i32, 4x8x8 register tile, "
-                      "OpenMP over rows), %.2f s" % (rows, M, K, N, dt)}
+                      "OpenMP over rows), %d x %.2f s" % (rows, M, K, N, reps, dt)}
 
 
 def run_reference(args):
