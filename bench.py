@@ -637,7 +637,7 @@ def cpu_baseline(workload, wl=None, reps=1, long_sample=False):
             layer = make_encoder(42, c["H"], c["F"], 1)[0]
         bs = 2 if workload == "bert_large" else 8
         if long_sample:
-            bs, reps = (24, 1) if workload == "bert_large" else (c["B"], 6)
+            bs, reps = (32, 1) if workload == "bert_large" else (c["B"], 6)
         x = np.random.default_rng(0).normal(size=(bs * c["S"], c["H"])).astype(np.float32)
         t0 = time.perf_counter()
         for _ in range(reps):
