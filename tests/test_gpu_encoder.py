@@ -146,3 +146,23 @@ def test_encoder_rejects_wrong_input(gpu):
         enc.run(np.zeros((2, 8, 64), np.float32))
     assert ei.value.code == gpu.EINVAL
     enc.close()
+
+
+def test_bert_large_size_batch_permutation(gpu):
+    # Size-independent property at the full BERT-large-shaped configuration
+    # (24 layers, hidden 1024, 16 heads, FFN 4096, batch 256 x 512 tokens):
+    # the per-tensor ranges are order independent and every other op works on
+    # one token or one sequence, so reversing the batch must reverse the
+    # output bit for bit -- whatever CTA, tile or wave a sequence lands in.
+    B, S, H, heads, F, nl = 256, 512, 1024, 16, 4096, 24
+    layers = make_encoder(21, H, F, nl)
+    enc = gpu.Encoder(H, heads, F, layers)
+    rng = np.random.default_rng(22)
+    x = rng.standard_normal((B, S, H), dtype=np.float32)
+    y = enc.run(x)
+    assert np.isfinite(y).all()
+    y_rev = enc.run(np.ascontiguousarray(x[::-1]))
+    assert np.array_equal(y_rev[::-1], y)
+    # and the run is repeatable
+    assert np.array_equal(enc.run(x), y)
+    enc.close()
