@@ -302,11 +302,16 @@ __device__ __forceinline__ QuantConsts epi_quant_consts(const EpiParams &p, bool
 //   m_warp   first output row of this warp's 32 rows
 //   n0       first output column of this warp's column range
 //   slab0    this warp's 4 KiB staging slab in shared memory
-template <int BN, int EPI, int EW>
+//   release  called once, right after the last tensor-memory load of the
+//            tile: the accumulator buffer is handed back to the MMA issuer
+//            before the arithmetic and the stores of the last chunk, which
+//            keeps those off the path that decides when the next tile's MMAs
+//            may start
+template <int BN, int EPI, int EW, typename Release>
 __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
     const EpiScalars &sc, const QuantConsts &qc, uint32_t taddr, int64_t m_warp,
     int64_t n0, uint32_t slab0, int lane, bool use_slab, float &lo, float &hi,
-    const CUtensorMap *map_y, const CUtensorMap *map_y2) {
+    const CUtensorMap *map_y, const CUtensorMap *map_y2, Release &&release) {
   // EPI_DEQUANT_SPLIT stages like the 4-byte tails (32 columns per 128-byte
   // slab row: 16 words of bf16 hi pairs, then 16 words of lo pairs).
   constexpr bool kSplit = EPI == OMCUDA_EPI_DEQUANT_SPLIT;
@@ -355,6 +360,8 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
         __syncwarp(); // tcgen05.ld is warp-collective: enter it converged
         tmem_ld32(taddr + (uint32_t)(g * kSlabCols + cc), v);
         tmem_ld_wait();
+        if (g == kSlabsPerHalf - 1 && cc + 32 >= kSlabCols)
+          release();
         const int64_t nc = ng + cc;
         const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
         if (row_ok && valid > 0)
@@ -413,6 +420,8 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
       __syncwarp();
       tmem_ld32(taddr + (uint32_t)c, v);
       tmem_ld_wait();
+      if (c + 32 >= kHalfCols)
+        release();
       const int64_t nc = n0 + c;
       const int valid = (int)((p.N - nc) < 32 ? (p.N - nc) : 32);
       if (!row_ok || valid <= 0)
@@ -637,13 +646,15 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       tcgen05_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
+      // The accumulator buffer may be overwritten once every warp has read
+      // its share of it.
       epilogue_tile<BN, EPI, EW>(p, sc, qc, taddr, m_warp, n0, slab0, lane, use_slab,
-          lo, hi, &map_y, &map_y2);
-      // The accumulator buffer may be overwritten once all eight warps are done.
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+          lo, hi, &map_y, &map_y2, [&] {
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0)
+              mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+          });
     }
     // One commit of the running range per warp, and every store of this warp
     // complete before the CTA may exit.
@@ -898,13 +909,17 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       tcgen05_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c_lo);
+      auto release = [&] {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0)
+          mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[buf]), 0));
+      };
       if (mine)
         epilogue_tile<BN, EPI, EW>(p, sc, qc, taddr, m_warp, n0, slab0, lane, use_slab,
-            lo, hi, &map_y, &map_y2);
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0)
-        mbar_arrive_cluster(mapa_shared(smem_u32(&bar_acc_empty[buf]), 0));
+            lo, hi, &map_y, &map_y2, release);
+      else
+        release();
     }
     if (active && p.out_range && epi_is_dequant(EPI) && EPI != OMCUDA_EPI_DEQUANT_QUANT)
       epi_range_commit(p.out_range, lo, hi);
