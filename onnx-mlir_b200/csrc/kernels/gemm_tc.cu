@@ -261,8 +261,13 @@ __device__ __forceinline__ void split_words_bf16(uint32_t (&v)[32]) {
     const float a = __uint_as_float(v[2 * i]), b = __uint_as_float(v[2 * i + 1]);
     uint32_t hw;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(hw) : "f"(b), "f"(a));
-    const float ra = __fsub_rn(a, __uint_as_float(hw << 16));
-    const float rb = __fsub_rn(b, __uint_as_float(hw & 0xffff0000u));
+    // x - hi for both values in one packed instruction (hi * -1 + x: one
+    // rounding, the subtraction's)
+    float ra, rb;
+    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(hw << 16),
+                               __uint_as_float(hw & 0xffff0000u)),
+                     pack_f32x2(-1.0f, -1.0f), pack_f32x2(a, b)),
+        ra, rb);
     uint32_t lw;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(lw) : "f"(rb), "f"(ra));
     h[i] = hw;
