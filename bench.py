@@ -479,7 +479,7 @@ def run_gpu(args):
     e2e_value = wl.units * world * e2e_steps / (e2e_ms * 1e-3) / scale
     int8_peak = 2.0 * peaks["bf16_tflops"]
     roofline = {
-        "kernel": "gemm_i8_tc_kernel", "bound": "tensor",
+        "kernel": "gemm_i8_tc2_kernel (gemm_i8_tc_kernel where a shape has too few 256x256 tiles)", "bound": "tensor",
         "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
         "frac": achieved / int8_peak,
         "peak_source": "2 x %s TFLOP/s bf16 cuBLAS burst (%s); an int8 figure "
@@ -605,7 +605,7 @@ def run_sweep(args):
             "e2e": {"value": tot_e2e_ops / tot_e2e_ms / 1e9, "unit": "TOPS",
                     "h2d_bytes_per_step": None, "d2h_bytes_per_step": None, "steps": 2},
             "gpu_launches": int(launches), "clocks": clocks,
-            "roofline": {"kernel": "gemm_i8_tc_kernel", "bound": "tensor",
+            "roofline": {"kernel": "gemm_i8_tc2_kernel (gemm_i8_tc_kernel where a shape has too few 256x256 tiles)", "bound": "tensor",
                          "achieved": sum(r["gemm_tops"] * r["gemm_ms"] for r in big) /
                                      sum(r["gemm_ms"] for r in big) / world,
                          "peak": int8_peak, "unit": "TOP/s",
