@@ -393,3 +393,26 @@ def test_dequant_tail_with_residual(gpu, M, K, N, choice):
     y0, y1 = Y0.numpy(), Y1.numpy()
     gpu.synchronize()
     assert y1.tobytes() == (y0 + res).astype(np.float32).tobytes()
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_shapes_against_exact_products(gpu, seed):
+    # Ragged shapes drawn at random around the tile sizes of the tensor-core
+    # kernels (128 / 256 rows, 64..256 columns, whole and half tiles in the
+    # last round, K not a multiple of the 128-byte K step): every output
+    # element against the exact integer product (float64 holds it exactly).
+    from gpu_util import DevGemm
+    rng = np.random.default_rng(1000 + seed)
+    M = int(rng.integers(130, 5200))
+    N = int(rng.integers(70, 3100))
+    K = 16 * int(rng.integers(1, 80))
+    a_signed, b_signed = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+    A = rng.integers(-128 if a_signed else 0, 128 if a_signed else 256, (M, K)).astype(
+        np.int8 if a_signed else np.uint8)
+    B = rng.integers(-128 if b_signed else 0, 128 if b_signed else 256, (K, N)).astype(
+        np.int8 if b_signed else np.uint8)
+    za = int(rng.integers(-128 if a_signed else 0, 128 if a_signed else 256))
+    dg = DevGemm(gpu)
+    Y = dg.matmul_integer(A, B, za, None, 1)
+    want = (A.astype(np.float64) - za) @ B.astype(np.float64)
+    assert np.array_equal(Y.astype(np.float64), want), (M, N, K, a_signed, b_signed, za)
