@@ -21,11 +21,14 @@ def shard_rows(total_rows, world, rank):
     return first, rows
 
 
-def gather_rows(local, total_rows, group=None, out=None):
+def gather_rows(local, total_rows, group=None, out=None, async_op=False):
     """All-gathers row shards made by shard_rows back into [total_rows, ...].
     `local` is this rank's [rows, ...] tensor (CPU with gloo, CUDA with nccl).
     Ragged shards are padded to the largest shard for the collective.  `out`
-    (optional, [total_rows, ...]) is filled in place when the shards are even."""
+    (optional, [total_rows, ...]) is filled in place when the shards are even.
+    With async_op (even CUDA shards only) the collective is only queued:
+    returns (out, work), and `out` is complete once work.wait() has been
+    called and the current stream has reached that point."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     first, rows = shard_rows(total_rows, world, rank)
@@ -42,8 +45,12 @@ def gather_rows(local, total_rows, group=None, out=None):
         if out is None:
             out = torch.empty((total_rows,) + tail, dtype=local.dtype,
                               device=local.device)
+        if async_op:
+            return out, dist.all_gather_into_tensor(out, padded, group=group, async_op=True)
         dist.all_gather_into_tensor(out, padded, group=group)
         return out
+    if async_op:
+        raise ValueError("async_op needs even shards on CUDA")
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
     pieces = [parts[r][:shard_rows(total_rows, world, r)[1]] for r in range(world)]
