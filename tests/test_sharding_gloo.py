@@ -31,7 +31,14 @@ def _worker(rank, world, port, total_rows, q):
         first, rows = shard_rows(total_rows, world, rank)
         local = full[first:first + rows] * 2.0     # the rank's "forward pass"
         out = gather_rows(local, total_rows)
-        q.put((rank, bool(torch.equal(out, full * 2.0)), tuple(out.shape)))
+        ok = bool(torch.equal(out, full * 2.0))
+        # the queued form exists for even CUDA shards only and must say so
+        try:
+            gather_rows(local, total_rows, async_op=True)
+            ok = False
+        except ValueError:
+            pass
+        q.put((rank, ok, tuple(out.shape)))
     finally:
         dist.destroy_process_group()
 
