@@ -13,8 +13,9 @@
 // epilogue or by split_bf16_kernel below), and each product is evaluated as
 // lo*hi + hi*lo + hi*hi, which leaves a relative error of about 2^-16 per
 // product, far inside the 1e-3 tolerance of the fp32 ops; accumulation is
-// fp32.  The softmax runs online over key blocks (running maximum and sum),
-// the same function as the reference's three-loop form up to fp32 rounding.
+// fp32.  The softmax runs online over key blocks (an exponent offset that
+// tracks the running maximum, and the running sum), the same function as the
+// reference's three-loop form up to fp32 rounding.
 //
 // Layout in HBM: the planes are [T, ld] bf16 row-major (T = batch*seq tokens);
 // head h of Q / K / V owns columns [col + 64 h, col + 64 h + 64) of its rows.
@@ -37,8 +38,13 @@
 //              [V_hi | V_lo] as one N = 128 product per 16-key slice (into
 //              128 columns of tensor memory), P_lo V_hi on top of the first
 //              64 columns; refills V;
-//   8 warps    o = o * 2^(m_old - m_new) + O_j in registers (32 columns each;
-//              O_j = the sum of the two 64-column halves).
+// O accumulates in tensor memory over the key blocks of an item (the P V MMAs
+// add to it); the exponent offset of a row follows its running maximum lazily,
+// moving only when a block's maximum exceeds it by more than 2^8, and only
+// then are O and the row sum rescaled (a tensor-memory load / multiply /
+// store pass): on typical data one pass or none per item instead of one
+// register fold per block.  At the end of the item the 8 warps read O (the sum
+// of its two 64-column halves), normalise and store.
 // The normalised 128 x 64 result of an item is staged in the (then free) V
 // buffers and leaves with two TMA stores of whole 128-byte lines.
 // Every wait on an mbarrier is bounded (tc_ptx.cuh); a timeout raises the
@@ -280,11 +286,13 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
     if (tid == 0 && has_next)
       nx = att_item(item + gridDim.x, nq, S, heads, q_col, k_col, v_col);
 
-    float o[kTDh / 2];
-#pragma unroll
-    for (int i = 0; i < kTDh / 2; ++i)
-      o[i] = 0.0f;
-    float m_run = -INFINITY; // running maximum of s * scale * log2(e)
+    // O accumulates in tensor memory over the key blocks of the item.  The
+    // exponent offset m_ref of a row follows its running maximum lazily: it
+    // moves (and O and the row sum are rescaled) only when a block's maximum
+    // exceeds it by more than 2^8, so p never exceeds 256 and most blocks
+    // need no pass over O at all.  Any offset gives the same softmax once
+    // the sum over the same p normalises the result.
+    float m_ref = -INFINITY; // exponent offset, in units of s * scale * log2(e)
     float l_run = 0.0f;      // running sum of p
 
     for (int j = 0; j < nkb; ++j, ++nblk) {
@@ -350,12 +358,42 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
       xch[half][row] = mx;
       pair_barrier(quad);
       mx = fmaxf(mx, xch[half ^ 1][row]);
-      const float m_new = fmaxf(m_run, __fmul_rn(mx, scale_log2e));
-      const float resc = ex2_approx(__fsub_rn(m_run, m_new)); // 0 on the first block
-      m_run = m_new;
+      const float m_blk = __fmul_rn(mx, scale_log2e);
+      // (true for every row on the first block: m_ref is -inf)
+      const bool move = m_blk > __fadd_rn(m_ref, 8.0f);
+      // Both threads of a row and both warps of a quadrant see the same rows
+      // and maxima, so they take this branch together.
+      if (j > 0 && __any_sync(0xffffffffu, move)) {
+        const float f = move ? ex2_approx(__fsub_rn(m_ref, m_blk)) : 1.0f;
+        l_run = __fmul_rn(l_run, f);
+        const uint64_t f2 = pack_f32x2(f, f);
+#pragma unroll 1
+        for (uint32_t part = 0; part < 2; ++part) { // P_hi V_hi + P_lo V_hi | P_hi V_lo
+          const uint32_t ta = t_o + part * 64u + lane_base + (uint32_t)(half * 32);
+          uint32_t v[32];
+          tmem_ld32(ta, v);
+          tmem_ld_wait();
+          uint32_t w0[16], w1[16];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            float a, b;
+            unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), f2), a, b);
+            w0[i] = __float_as_uint(a);
+            w0[i + 1] = __float_as_uint(b);
+            unpack_f32x2(mul_f32x2(pack_f32x2(__uint_as_float(v[16 + i]), __uint_as_float(v[17 + i])), f2), a, b);
+            w1[i] = __float_as_uint(a);
+            w1[i + 1] = __float_as_uint(b);
+          }
+          tmem_st16(ta, w0);
+          tmem_st16(ta + 16u, w1);
+        }
+        tmem_st_wait();
+      }
+      if (move)
+        m_ref = m_blk;
       // (packed fp32 below: two individually rounded operations per instruction)
       const uint64_t scale2 = pack_f32x2(scale_log2e, scale_log2e);
-      const uint64_t neg_m2 = pack_f32x2(-m_new, -m_new);
+      const uint64_t neg_m2 = pack_f32x2(-m_ref, -m_ref);
       const uint64_t minus1 = pack_f32x2(-1.0f, -1.0f);
       uint64_t psum2 = pack_f32x2(0.0f, 0.0f);
 #pragma unroll 1
@@ -391,7 +429,7 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
       }
       float ps0, ps1;
       unpack_f32x2(psum2, ps0, ps1);
-      l_run = __fadd_rn(__fmul_rn(l_run, resc), __fadd_rn(ps0, ps1));
+      l_run = __fadd_rn(l_run, __fadd_rn(ps0, ps1));
       tmem_st_wait();
       tcgen05_fence_before();
       __syncthreads(); // every row of P is in tensor memory
@@ -407,7 +445,7 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
           const uint64_t dv2 = (dvh & ~kLboField) | ((uint64_t)((s_vl - s_vh) >> 4) << 16);
           // P_hi [V_hi | V_lo] into columns 0..127 of O_j, then P_lo V_hi on
           // top of columns 0..63 (hi parts at column offset 0, lo at 16)
-          umma_bf16_ts_x4(t_o, t_s, dv2, kIdescPV2, 0u);
+          umma_bf16_ts_x4(t_o, t_s, dv2, kIdescPV2, j != 0 ? 1u : 0u);
           umma_bf16_ts_x4(t_o, t_s + 64u, dv2 + 512, kIdescPV2, 1u);
           umma_bf16_ts_x4(t_o, t_s + 16u, dvh, kIdescPV, 1u);
           umma_bf16_ts_x4(t_o, t_s + 64u + 16u, dvh + 512, kIdescPV, 1u);
@@ -420,35 +458,32 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
           }
         }
       }
-      ok = __syncthreads_and(ok) != 0;
-      if (!ok)
-        break;
-      tcgen05_fence_after();
-      __syncwarp();
-      {
-        uint32_t v[32];
-        tmem_ld32(t_o + lane_base + (uint32_t)(half * 32), v);
-        tmem_ld_wait();
-#pragma unroll
-        const uint64_t resc2 = pack_f32x2(resc, resc);
-#pragma unroll
-        for (int i = 0; i < 32; i += 2)
-          unpack_f32x2(fma_f32x2(pack_f32x2(o[i], o[i + 1]), resc2,
-                           pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]))),
-              o[i], o[i + 1]);
-        // ... and the P_hi V_lo part from the upper 64 columns
-        tmem_ld32(t_o + 64u + lane_base + (uint32_t)(half * 32), v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2)
-          unpack_f32x2(add_f32x2(pack_f32x2(o[i], o[i + 1]),
-                           pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]))),
-              o[i], o[i + 1]);
-      }
-      tcgen05_fence_before();
+      // No CTA barrier here: the other threads go on to wait for the next
+      // block's scores, which thread 0 requests only once this P V is done.
     }
+    ok = __syncthreads_and(ok) != 0; // the item's last P V is complete
     if (!ok)
       break;
+    tcgen05_fence_after();
+    __syncwarp();
+    float o[kTDh / 2];
+    {
+      uint32_t v[32];
+      tmem_ld32(t_o + lane_base + (uint32_t)(half * 32), v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        o[i] = __uint_as_float(v[i]);
+      // ... plus the P_hi V_lo part from the upper 64 columns
+      tmem_ld32(t_o + 64u + lane_base + (uint32_t)(half * 32), v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i += 2)
+        unpack_f32x2(add_f32x2(pack_f32x2(o[i], o[i + 1]),
+                         pack_f32x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]))),
+            o[i], o[i + 1]);
+    }
+    tcgen05_fence_before();
 
     // Row sum over both halves, then normalise.  The 128 x 64 result leaves
     // through the V buffers (free after the last P V): half 0's 32 columns in
