@@ -55,6 +55,26 @@ def test_attention(gpu, orc, B, S, heads, dh):
     close(gpu.attention(q, k, v, heads, scale), orc.attention(q, k, v, heads, scale), 1e-3, 1e-5)
 
 
+@pytest.mark.parametrize("scales", [(0.1, 4.0, 0.1, 12.0), (6.0, 0.2, 0.2, 0.2),
+                                    (0.5, 1.0, 2.0, 4.0)])
+def test_attention_growing_and_shrinking_key_blocks(gpu, orc, scales):
+    # The tcgen05 kernel keeps O in tensor memory and moves a row's exponent
+    # offset only when a key block's maximum outgrows it by more than 2^8:
+    # key blocks of very different magnitude make some rows move once, twice
+    # or never, and make later blocks vanish against an early maximum.
+    rng = np.random.default_rng(17)
+    B, S, heads, dh = 2, 512, 2, 64
+    q = rng.normal(0, 1.0, size=(B, S, heads * dh)).astype(np.float32)
+    k = rng.normal(0, 1.0, size=(B, S, heads * dh)).astype(np.float32)
+    v = rng.normal(0, 1.0, size=(B, S, heads * dh)).astype(np.float32)
+    for j, f in enumerate(scales):
+        k[:, 128 * j:128 * (j + 1)] *= np.float32(f)
+    q[:, ::3] *= np.float32(0.05)        # rows whose scores stay small throughout
+    scale = 1.0 / np.sqrt(dh)
+    close(gpu.attention(q, k, v, heads, scale), orc.attention(q, k, v, heads, scale),
+          1e-3, 1e-3)
+
+
 def test_attention_peaked_scores(gpu, orc):
     # Head size 64 with a sequence that is a multiple of 128 runs on the
     # tcgen05 kernel; peaked scores (large logits) exercise the online
