@@ -343,16 +343,19 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
 
       // ---- online softmax: this thread's half of its row ----
       __syncwarp(); // tcgen05.ld / st are warp-collective: enter them converged
+      // The thread's 64 scores are read from tensor memory once and stay in
+      // registers for both passes (maximum, then exponentials).
+      static_assert(kTK / 2 == 64, "two 32-column loads per thread");
+      uint32_t sv[2][32];
+      tmem_ld32(t_s + lane_base + (uint32_t)kc0, sv[0]);
+      tmem_ld32(t_s + lane_base + (uint32_t)kc0 + 32u, sv[1]);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(t_s + lane_base + (uint32_t)c, v);
-        tmem_ld_wait();
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2)
 #pragma unroll
         for (int i = 0; i < 32; i += 2)
-          mx = max3f(mx, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-      }
+          mx = max3f(mx, __uint_as_float(sv[h2][i]), __uint_as_float(sv[h2][i + 1]));
       // Row maximum over both halves (the two threads of a row sit in warps w
       // and w + 4: a 64-thread named barrier per quadrant).
       xch[half][row] = mx;
@@ -396,11 +399,10 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
       const uint64_t neg_m2 = pack_f32x2(-m_ref, -m_ref);
       const uint64_t minus1 = pack_f32x2(-1.0f, -1.0f);
       uint64_t psum2 = pack_f32x2(0.0f, 0.0f);
-#pragma unroll 1
-      for (int c = kc0; c < kc0 + kTK / 2; c += 32) {
-        uint32_t v[32];
-        tmem_ld32(t_s + lane_base + (uint32_t)c, v);
-        tmem_ld_wait();
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int c = kc0 + 32 * h2;
+        const uint32_t(&v)[32] = sv[h2];
         uint32_t whi[16], wlo[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
