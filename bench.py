@@ -24,8 +24,15 @@ with inputs resident in HBM; `e2e` runs the same graph through the krnl.call
 entry points with pinned host buffers, host<->device copies inside the timed
 region (the encoder workloads use the pipelined Submit / Wait form of the
 host-tensor call: every step still copies its input in and its output out,
-and those copies overlap the runs of the neighbouring steps).  With N > 1 every rank runs the workload on its own batch (weights
-replicated, no data-path collective): weak scaling.
+and those copies overlap the runs of the neighbouring steps).  With N > 1
+every rank runs the workload on its own batch (weights replicated, no
+data-path collective): weak scaling, the default.  `--scaling strong` keeps the
+configured batch fixed and splits it over the ranks instead; every N > 1 run of
+an encoder workload also appends that measurement as a "strong" object (and,
+for the default workload, the M >= 4096 members of the GEMM sweep sharded by
+rows as "sweep_strong").  A default N = 1 run adds an "extra" object with the
+other headline kernels: the 4096^3 and QLinearMatMul GEMMs (TOP/s) and
+DynamicQuantizeLinear alone (GB/s).
 """
 import argparse
 import ctypes
@@ -44,17 +51,27 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 L2_FLUSH_BYTES = 256 << 20
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the int8 GEMM kernel from ncu
-# captures of this script, bytes per launch (encoders: mean over the four GEMM
-# launches of a layer).  The captures and their commands are summarised in
-# profiles/ (gemm_*.md, bert_large_dram_traffic.md).  Outputs that are still
-# in the 126 MB L2 when a kernel ends are not in these counts.
+# dram__bytes_read.sum + dram__bytes_write.sum of the int8 GEMM kernel, bytes per
+# launch, from ncu captures of this script (encoders: mean over the four GEMM
+# launches of a layer).  A capture describes the kernel as it was when it was
+# taken: each entry names the tile shape it was taken with, and the figure is
+# reported only while the library still launches that shape.  Outputs that are
+# still in the 126 MB L2 when a kernel ends are not in these counts.
 NCU_GEMM_DRAM_BYTES = {
-    "bert_large": 1391.2e6,
-    "bert_base": 7.57e6,
-    "mmi_4096": 51.85e6,
-    "qlinear_c2": 37.66e6,
+    "bert_large": (1391.2e6, "256x256 tiles, cta_group::2, f32 / bf16-plane outputs"),
+    "bert_base": (7.57e6, "256x256 tiles, cta_group::2"),
+    "mmi_4096": (51.85e6, "256x256 tiles, cta_group::2"),
+    "qlinear_c2": (37.66e6, "256x256 tiles, cta_group::2"),
 }
+GEMM_TILE_IN_USE = "256x256 tiles, cta_group::2"
+
+
+def ncu_traffic(workload):
+    ent = NCU_GEMM_DRAM_BYTES.get(workload)
+    if ent is None or not ent[1].startswith(GEMM_TILE_IN_USE):
+        return None, "no ncu capture of the kernel in its present form"
+    return ent[0], ("ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the "
+                    "int8 GEMM, captured with: " + ent[1])
 
 
 def load_peaks():
@@ -160,7 +177,7 @@ class LinearWorkload:
     """DQL -> int8 GEMM -> dequant (mmi_4096) or QLinearMatMul (qlinear_c2)."""
     metric, unit, dtype = "MatMulInteger int8 TOPS", "TOPS", "u8*s8->s32"
 
-    def __init__(self, env, name, seed, shape=None):
+    def __init__(self, env, name, seed, shape=None, e2e=True):
         self.env, self.name = env, name
         torch, dev = env.torch, env.dev
         rng = np.random.default_rng(seed)
@@ -233,6 +250,8 @@ class LinearWorkload:
         self.g = g
         self.launches_per_step = 3
         env.torch.cuda.synchronize()
+        if not e2e:
+            return
         # e2e: pinned host tensors wrapped as OMTensors
         m = env.m
         if self.kind == "dynquant":
@@ -409,6 +428,8 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     env = GpuEnv(local_rank)
     is_encoder = args.workload in EncoderWorkload.SHAPES
+    if is_encoder and args.scaling == "strong" and world > 1:
+        return run_strong_only(args, env, world, rank, dist)
     if is_encoder:
         wl = EncoderWorkload(env, args.workload, 42 + rank, world, dist)
     else:
@@ -499,6 +520,16 @@ def run_gpu(args):
     else:
         e2e_ms = timed(wl.step_e2e, e2e_steps, 1)
 
+    # Fixed-batch (strong-scaling) measurement of the same graph, and of the
+    # large members of the GEMM sweep, whenever there is more than one rank.
+    strong = sweep_strong = None
+    if world > 1 and is_encoder:
+        strong = strong_scaling_leg(env, wl, world, rank, dist, barrier)
+        if args.workload == "bert_large":
+            sweep_strong = sweep_strong_leg(env, world, rank, dist, barrier)
+    extra = None
+    if world == 1 and args.workload == "bert_large" and not args.no_extra:
+        extra = extra_kernels(env, peaks)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -507,15 +538,26 @@ def run_gpu(args):
     value = wl.units * world * args.steps / (ms * 1e-3) / scale
     e2e_value = wl.units * world * e2e_steps / (e2e_ms * 1e-3) / scale
     int8_peak = 2.0 * peaks["bf16_tflops"]
+    int8_sustained = 2.0 * (peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"])
+    traffic, traffic_source = ncu_traffic(args.workload)
     roofline = {
         "kernel": "gemm_i8_tc2_kernel (gemm_i8_tc_kernel where a shape has too few 256x256 tiles)", "bound": "tensor",
         "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
         "frac": achieved / int8_peak,
-        "peak_source": "2 x %s TFLOP/s bf16 cuBLAS burst (%s); an int8 figure "
-                       "is not in MEASURED_PEAKS.json" % (peaks["bf16_tflops"],
-                                                          peaks["source"]),
+        # the same launches against the other two denominators a reader may
+        # want, and against the HBM roof
+        "frac_sustained": achieved / int8_sustained,
+        "frac_nominal": achieved / 4500.0,
+        "hbm_frac": algo_bytes / (gemm_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+        "peak_source": "frac: 2 x %s TFLOP/s bf16 cuBLAS burst (%s; an int8 figure is not "
+                       "in MEASURED_PEAKS.json); frac_sustained: 2 x %s (the seconds-long "
+                       "loop under the power cap, the fitting one for launches timed inside "
+                       "a long step); frac_nominal: 4500 TOP/s dense int8; hbm_frac: "
+                       "algorithmic bytes / launch time / %s GB/s"
+                       % (peaks["bf16_tflops"], peaks["source"],
+                          peaks["bf16_tflops_sustained"], peaks["hbm_gbs"]),
         "algorithmic_bytes": algo_bytes,
-        "traffic": NCU_GEMM_DRAM_BYTES.get(args.workload)}
+        "traffic": traffic, "traffic_source": traffic_source}
     roofline.update(roof_extra)
     out = {
         "metric": wl.metric, "value": value, "unit": wl.unit,
@@ -533,12 +575,220 @@ def run_gpu(args):
         "clocks": clocks,
         "roofline": roofline,
     }
+    if strong is not None:
+        out["strong"] = strong
+    if sweep_strong is not None:
+        out["sweep_strong"] = sweep_strong
+    if extra is not None:
+        out["extra"] = extra
     # CPU baseline on a bounded sample of the same workload (rank 0, N=1 only).
     if world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(args.workload, wl, long_sample=True)
     emit(out)
     if world > 1:
         dist.destroy_process_group()
+
+
+
+def _max_over_ranks(env, dist, world, vals):
+    if world == 1:
+        return [float(v) for v in vals]
+    t = env.torch.tensor(list(vals), dtype=env.torch.float64, device=env.device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def strong_scaling_leg(env, wl, world, rank, dist, barrier, steps=5, warmup=2):
+    """The encoder at its configured batch split over the ranks (shard_rows),
+    one all-gather of the output rows inside every step: the fixed-batch form
+    of the multi-GPU configuration.  Also times the same batch on one GPU
+    without a gather (every rank runs it at once; max over ranks), so that the
+    speed-up is measured inside one run."""
+    import torch
+    from omcuda.sharding import gather_rows, shard_rows
+    c = wl.c
+    B = c["B"]
+    first, b_local = shard_rows(B, world, rank)
+    x = wl.X[:b_local]
+    y_local = torch.empty((b_local, c["S"], c["H"]), dtype=torch.float32, device=env.device)
+    y_all = wl.Y  # [B, S, H]: the gathered output
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    l0 = env.m.launch_count()
+    rows = []
+    for i in range(warmup + steps):
+        env.flush_l2()
+        e = (ev(), ev(), ev())
+        e[0].record(env.stream)
+        wl.enc.run_dev(x.data_ptr(), b_local, c["S"], y_local.data_ptr(), env.sptr())
+        e[1].record(env.stream)
+        gather_rows(y_local, B, out=y_all)
+        e[2].record(env.stream)
+        if i >= warmup:
+            rows.append(e)
+        if i == warmup - 1:
+            barrier()
+    barrier()
+    launches = (env.m.launch_count() - l0) // (warmup + steps)
+    step_ms = sum(a.elapsed_time(c_) for a, _, c_ in rows) / steps
+    run_ms = sum(a.elapsed_time(b) for a, b, _ in rows) / steps
+    gather_ms = sum(b.elapsed_time(c_) for _, b, c_ in rows) / steps
+    # the whole batch on one GPU, no gather
+    one = []
+    for i in range(1 + 3):
+        env.flush_l2()
+        a, b = ev(), ev()
+        a.record(env.stream)
+        wl.enc.run_dev(wl.X.data_ptr(), B, c["S"], wl.Y.data_ptr(), env.sptr())
+        b.record(env.stream)
+        if i >= 1:
+            one.append((a, b))
+    barrier()
+    one_ms = sum(a.elapsed_time(b) for a, b in one) / len(one)
+    step_ms, run_ms, gather_ms, one_ms = _max_over_ranks(
+        env, dist, world, [step_ms, run_ms, gather_ms, one_ms])
+    return {"scaling": "strong", "global_batch": B, "batch_per_gpu": b_local,
+            "steps": steps, "warmup": warmup,
+            "value": B / (step_ms * 1e-3), "unit": "seq/s", "ms_per_step": step_ms,
+            "encoder_ms": run_ms, "all_gather_ms": gather_ms,
+            "all_gather_bytes_received_per_gpu": (B - b_local) * c["S"] * c["H"] * 4,
+            "one_gpu_ms_per_step": one_ms, "one_gpu_value": B / (one_ms * 1e-3),
+            "speedup_over_one_gpu": one_ms / step_ms,
+            "efficiency": one_ms / step_ms / world,
+            "gpu_launches_per_step": int(launches),
+            "timing": "CUDA events on the launching stream, max over ranks; the "
+                      "gather is synchronous (the step ends when the rows have arrived)"}
+
+
+def sweep_strong_leg(env, world, rank, dist, barrier, steps=3, warmup=3):
+    """Members of the GEMM sweep with M >= 4096, rows split over the ranks:
+    DynamicQuantizeLinear -> MatMulInteger -> dequant on M / world rows."""
+    import torch
+    rows = []
+    for K, N in SWEEP_KN:
+        for M in (4096, 16384):
+            m_rank = M // world
+            wl = LinearWorkload(env, "mmi_%dx%dx%d" % (M, K, N), 42 + rank,
+                                shape=(m_rank, K, N), e2e=False)
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                   for _ in range(steps)]
+            for _ in range(warmup):
+                env.flush_l2()
+                wl.step()
+            barrier()
+            for a, b in evs:
+                env.flush_l2()
+                a.record(env.stream)
+                wl.step()
+                b.record(env.stream)
+            barrier()
+            ms = sum(a.elapsed_time(b) for a, b in evs) / steps
+            (ms,) = _max_over_ranks(env, dist, world, [ms])
+            rows.append({"M": M, "K": K, "N": N, "rows_per_gpu": m_rank, "ms_per_step": ms,
+                         "tops": 2.0 * M * N * K / ms / 1e9})
+            del wl
+            torch.cuda.empty_cache()
+    return rows
+
+
+def run_strong_only(args, env, world, rank, dist):
+    """`--scaling strong`: the JSON line's value is the fixed-batch figure."""
+    import torch
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+    wl = EncoderWorkload(env, args.workload, 42 + rank, world, dist)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
+    launches0 = env.m.launch_count()
+    st = strong_scaling_leg(env, wl, world, rank, dist, barrier, steps=args.steps,
+                            warmup=args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        cfg = wl.config()
+        cfg.pop("batch_per_gpu")
+        cfg.update({"global_batch": st["global_batch"], "batch_per_gpu": st["batch_per_gpu"]})
+        emit({"metric": wl.metric, "value": st["value"], "unit": wl.unit, "n_gpus": world,
+              "steps": args.steps, "warmup": args.warmup, "ms_per_step": st["ms_per_step"],
+              "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+              "dtype": wl.dtype, "data": "synthetic", "config": cfg,
+              "gpu_launches": int(env.m.launch_count() - launches0), "clocks": clocks,
+              "strong": st})
+    dist.destroy_process_group()
+
+
+def extra_kernels(env, peaks):
+    """The other headline kernels, a fraction of a second each: the 4096^3
+    MatMulInteger GEMM (L2 flushed and warm), the QLinearMatMul GEMM of the
+    batched configuration, and DynamicQuantizeLinear alone on 64 Mi and 512 Mi
+    elements (two launches: range reduction, quantize)."""
+    import torch
+    dev = env.dev
+    int8_peak = 2.0 * peaks["bf16_tflops"]
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    out = {"timing": "CUDA events around the launch(es) on the launching stream, "
+                     "mean of 10 after 3 warm-ups"}
+
+    def time_gemm(wl, flush):
+        ts = []
+        for i in range(13):
+            wl.step()                       # refreshes xq / rowsum; not timed
+            if flush:
+                env.flush_l2()
+            a, b = ev(), ev()
+            a.record(env.stream)
+            dev.gemm_i8(wl.g, env.sptr())
+            b.record(env.stream)
+            if i >= 3:
+                ts.append((a, b))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in ts) / len(ts)
+
+    for name in ("mmi_4096", "qlinear_c2"):
+        wl = LinearWorkload(env, name, 42, e2e=False)
+        d = {}
+        for flush in (True, False):
+            ms = time_gemm(wl, flush)
+            tops = wl.ops / ms / 1e9
+            d["l2_flushed" if flush else "l2_warm"] = {
+                "gemm_ms": ms, "tops": tops, "frac_of_2x_bf16_burst": tops / int8_peak,
+                "frac_nominal": tops / 4500.0}
+        d["M"], d["N"], d["K"] = wl.M, wl.N, wl.K
+        out[name] = d
+        del wl
+        torch.cuda.empty_cache()
+    dql = {}
+    for n in (64 << 20, 512 << 20):
+        x = torch.randn(n, dtype=torch.float32, device=env.device)
+        y = torch.empty(n, dtype=torch.uint8, device=env.device)
+        sc = torch.empty(1, dtype=torch.float32, device=env.device)
+        zp = torch.empty(1, dtype=torch.uint8, device=env.device)
+        scr = torch.zeros(dev.dql_scratch_bytes(), dtype=torch.uint8, device=env.device)
+        ts = []
+        for i in range(13):
+            env.flush_l2()
+            a, b = ev(), ev()
+            a.record(env.stream)
+            dev.dynamic_quantize_linear(x.data_ptr(), n, y.data_ptr(), sc.data_ptr(),
+                                        zp.data_ptr(), scr.data_ptr(), env.sptr())
+            b.record(env.stream)
+            if i >= 3:
+                ts.append((a, b))
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in ts) / len(ts)
+        dql["%d_Mi_elements" % (n >> 20)] = {
+            "ms": ms, "gbs_at_5_bytes_per_element": 5.0 * n / ms / 1e6,
+            "gbs_at_9_bytes_per_element": 9.0 * n / ms / 1e6,
+            "hbm_frac_5": 5.0 * n / ms / 1e6 / peaks["hbm_gbs"],
+            "hbm_frac_9": 9.0 * n / ms / 1e6 / peaks["hbm_gbs"]}
+        del x, y
+        torch.cuda.empty_cache()
+    dql["note"] = ("5 B/element = read f32 once + write u8; a tensor larger than L2 has "
+                   "to be read twice (range, then quantize): 9 B/element is what the two "
+                   "launches move")
+    out["dynamic_quantize_linear"] = dql
+    return out
 
 
 SWEEP_M = (1, 16, 256, 4096, 16384)
@@ -673,7 +923,7 @@ def cpu_baseline(workload, wl=None, reps=1, long_sample=False):
             orc.encoder_layer(x, bs, c["S"], c["H"], c["heads"], c["F"], layer)
         dt = (time.perf_counter() - t0) / reps
         return {"value": bs / (dt * c["layers"]), "unit": "seq/s", "cores": threads,
-                "kind": "port", "seconds_per_rep": dt,
+                "kind": "port", "seconds_per_rep": dt, "sequences_timed": bs,
                 "sample": "one of %d layers on %d of %d sequences (%d x %.1f s), "
                           "scaled by the layer count; oracle ops with OpenMP"
                           % (c["layers"], bs, c["B"], reps, dt)}
@@ -690,7 +940,7 @@ def cpu_baseline(workload, wl=None, reps=1, long_sample=False):
         orc.ref_shaped_matmul_integer(A, W, 128, threads)
     dt = (time.perf_counter() - t0) / reps
     return {"value": 2.0 * rows * N * K / dt / 1e12, "unit": "TOPS",
-            "cores": threads, "kind": "port", "seconds_per_rep": dt,
+            "cores": threads, "kind": "port", "seconds_per_rep": dt, "rows_timed": rows,
             "sample": "%d of %d rows of the same [K=%d,N=%d] GEMM, reference-shaped "
                       "lowering (operands widened to i32, 4x8x8 register tile, "
                       "OpenMP over rows), %d x %.2f s" % (rows, M, K, N, reps, dt)}
@@ -710,12 +960,16 @@ def run_reference(args):
         c = EncoderWorkload.SHAPES[args.workload]
         config = {"workload": args.workload, "layers": c["layers"], "hidden": c["H"],
                   "heads": c["heads"], "ffn": c["F"], "seq_len": c["S"],
-                  "batch_per_gpu": c["B"]}
+                  "batch_per_gpu": c["B"],
+                  # what a step of this arm really times
+                  "layers_timed": 1, "sequences_timed": cb["sequences_timed"],
+                  "extrapolated": True}
         metric, dtype = EncoderWorkload.metric, EncoderWorkload.dtype
     else:
         M, N, K = {"mmi_4096": (4096, 4096, 4096),
                    "qlinear_c2": (16384, 4096, 1024)}[args.workload]
-        config = {"workload": args.workload, "M": M, "N": N, "K": K}
+        config = {"workload": args.workload, "M": M, "N": N, "K": K,
+                  "rows_timed": cb["rows_timed"], "extrapolated": cb["rows_timed"] != M}
         metric, dtype = LinearWorkload.metric, LinearWorkload.dtype
     dt = cb.pop("seconds_per_rep")
     emit({
@@ -757,6 +1011,11 @@ def main():
                     choices=["mmi_4096", "qlinear_c2", "bert_base", "bert_large",
                              "mmi_sweep"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the extra kernels of the default N = 1 run")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="N > 1, encoder workloads: weak = every rank runs the configured "
+                         "batch (default); strong = the configured batch is split")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "omcuda" else args.warmup
     if args.workload == "mmi_sweep":

@@ -100,9 +100,21 @@ void *omcudaDeviceAlloc(int64_t bytes);
 void omcudaDeviceFree(void *p);
 /* The stream krnl.call-level entry points launch on (a cudaStream_t).  A
  * caller may substitute its own for the calling thread; NULL restores the
- * library stream. */
+ * library stream.  Several host threads may be inside the library at once,
+ * each on the shared library stream or on a stream of its own (the
+ * run_main_graph of one model may be called concurrently,
+ * docs/mnist_example/README.md:117-150 of the reference): temporaries come
+ * from a pool whose reuse is ordered by stream (a block freed by one stream
+ * reaches another only behind an event), and a cached constant prepared on
+ * one stream is waited for by the others.  One omcudaEncoder object serves
+ * one run at a time. */
 void *omcudaGetStream(void);
 void omcudaSetStream(void *stream);
+/* A new non-blocking stream on the library's device for a host thread that
+ * wants its calls to run beside those of other threads (pass it to
+ * omcudaSetStream), without that thread linking the CUDA runtime itself. */
+void *omcudaStreamCreate(void);
+void omcudaStreamDestroy(void *stream);
 void omcudaSynchronize(void);
 /* Declares that a tensor's buffer is a model constant (krnl.global): its
  * prepared form (K-major copy and column sums of a MatMulInteger /
@@ -186,9 +198,9 @@ void omcudaAttention(OMTensor *y, const OMTensor *q, const OMTensor *k,
 /* Bytes of scratch omcudaDevDynamicQuantizeLinear needs for n elements. */
 int64_t omcudaDevDqlScratchBytes(int64_t n);
 /* DynamicQuantizeLinear on device buffers.  scratch: device memory of at
- * least omcudaDevDqlScratchBytes(n), zero-filled once before first use (the
- * kernel leaves it zeroed).  params_out (device, 2 floats, may be NULL)
- * receives {scale, zero point as float}. */
+ * least omcudaDevDqlScratchBytes(n) whose first 64 bytes are zero before the
+ * first use (the kernel leaves them zeroed); calls that overlap on the GPU
+ * need a scratch block each. */
 int omcudaDevDynamicQuantizeLinear(const float *x, int64_t n, uint8_t *y,
     float *y_scale, uint8_t *y_zp, void *scratch, void *stream);
 /* DynamicQuantizeLinear for callers that cannot allocate device memory (a
@@ -295,8 +307,28 @@ typedef struct {
   uint8_t *q_zp;
 } omcudaGemmArgs;
 
-/* Device status word the GEMM writes on a bounded-wait timeout. */
 int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream);
+
+/* Bounded device-side waits.  Every wait of the tensor-core kernels (int8
+ * GEMM, bf16 attention) on an mbarrier gives up after a limit -- two seconds
+ * without progress of that wait unless changed here (ns <= 0 restores the
+ * default) -- after which the CTA frees its tensor memory, raises a per-device
+ * status word and returns; nothing traps or spins without a limit.  The word
+ * is read (and cleared) by omcudaSynchronize, by every krnl.call-level entry
+ * point that returns host results, by omcudaTensorToHost and by
+ * omcudaEncoderWait, which then report OMCUDA_ETIMEDOUT (errno ETIMEDOUT).  A
+ * caller of the omcudaDev* entry points that synchronises its own stream must
+ * call omcudaSynchronize (on a thread whose stream it set with omcudaSetStream)
+ * to learn of a timeout.  Has no counterpart in the reference, whose CPU loops
+ * cannot wait on anything. */
+void omcudaDevSetWaitLimitNs(int64_t ns);
+/* Self test of that path: launches one CTA that allocates tensor memory and
+ * waits, with the configured limit (capped at one second), on a barrier that
+ * nothing signals.  The kernel returns by itself; afterwards the status word
+ * is raised, so the next omcudaSynchronize reports OMCUDA_ETIMEDOUT, and
+ * tensor memory is free again.  waited_ns (device pointer, may be NULL)
+ * receives how long the wait lasted. */
+int omcudaDevSelfTestBoundedWait(uint64_t *waited_ns, void *stream);
 
 /* S[n] = (a_scale * b_scale[n]) / y_scale on device
  * (QLinearMatMul.cpp:127). */
@@ -425,6 +457,27 @@ int omcudaEncoderRunDev(omcudaEncoder *enc, const float *x, int64_t batch,
 void omcudaEncoderSetProfiling(omcudaEncoder *enc, int on);
 int omcudaEncoderGemmStats(
     omcudaEncoder *enc, double *ms_total, double *ops_total, int64_t *launches);
+/* Parity-test tap (no counterpart in the reference, which is inspected with
+ * its own instrumentation passes instead): while a tap buffer is set, every
+ * run also copies each layer's intermediates into it, so that a test can feed
+ * the library's own input of every op to a checker and compare op by op
+ * instead of through the free-running chain.  Per layer l, at byte offset
+ * l * layer_stride + field: x (the layer input, f32 [T,H]) and xq_x (its
+ * uint8 quantization), ctx / xq_ctx (attention output), h1 / xq_h1 (first
+ * LayerNorm), f / xq_f (Gelu output, f32 / uint8 [T,F]) and y (the layer
+ * output); after the last layer, at `params`, 4 floats per quantize site
+ * (4 per layer in the order x, ctx, h1, f): scale, zero point as float, scale
+ * again as the op's y_scale output, and the zero point as uint8 in the first
+ * byte of the fourth word.  The buffer is device memory of at least `total`
+ * bytes for the batch and sequence length of the run; NULL switches the tap
+ * off.  The copies are ordered on the run's stream. */
+typedef struct {
+  int64_t x, xq_x, ctx, xq_ctx, h1, xq_h1, f, xq_f, y;
+  int64_t layer_stride, params, total;
+} omcudaEncoderTapLayout;
+int omcudaEncoderGetTapLayout(const omcudaEncoder *enc, int64_t batch,
+    int64_t seq, omcudaEncoderTapLayout *out);
+int omcudaEncoderSetTap(omcudaEncoder *enc, void *dev_buf, int64_t bytes);
 void omcudaEncoderDestroy(omcudaEncoder *enc);
 
 #ifdef __cplusplus

@@ -87,9 +87,16 @@ bool same_shape(const OMTensor *a, const OMTensor *b) {
 class Stage {
 public:
   explicit Stage(cudaStream_t st) : st_(st) {}
+  // Temporaries go back to the pool stream-ordered: whoever takes them next
+  // is queued behind the kernels of this call that still use them.
   ~Stage() {
     for (void *p : temps_)
-      pool_free(p);
+      pool_free_on(p, st_);
+  }
+  // Hands a pool block to this call for release at its end.
+  void adopt(void *p) {
+    if (p)
+      temps_.push_back(p);
   }
 
   bool ok() const { return rc_ == OMCUDA_OK; }
@@ -100,7 +107,7 @@ public:
   }
 
   void *scratch(size_t bytes) {
-    void *p = pool_alloc(bytes ? bytes : 1);
+    void *p = pool_alloc_on(bytes ? bytes : 1, st_);
     if (!p) {
       set(OMCUDA_ENOMEM);
       return nullptr;
@@ -170,23 +177,19 @@ private:
   int64_t h2d_ = 0;
 };
 
-// ---- per-stream DynamicQuantizeLinear scratch ----------------------------------------
+// ---- DynamicQuantizeLinear scratch ------------------------------------------------------
+//
+// One block per call (not per stream): two host threads may interleave their
+// launches on the shared library stream, and the reduction leaves the scale
+// and zero point in its scratch for the quantize pass that follows.
 
-std::mutex g_scratch_mutex;
-std::map<cudaStream_t, void *> g_dql_scratch;
-
-void *dql_scratch_for(cudaStream_t st) {
-  std::lock_guard<std::mutex> lock(g_scratch_mutex);
-  auto it = g_dql_scratch.find(st);
-  if (it != g_dql_scratch.end())
-    return it->second;
-  size_t bytes = (size_t)omcudaDevDqlScratchBytes(0);
-  void *p = nullptr;
-  if (check_cuda(cudaMalloc(&p, bytes), "cudaMalloc(dql scratch)") != OMCUDA_OK)
+void *dql_scratch_for(Stage &sg, cudaStream_t st) {
+  void *p = sg.scratch((size_t)omcudaDevDqlScratchBytes(0));
+  if (!p)
     return nullptr;
-  if (check_cuda(cudaMemset(p, 0, bytes), "cudaMemset") != OMCUDA_OK)
+  // Only the ticket line has to start at zero.
+  if (check_cuda(cudaMemsetAsync(p, 0, 64, st), "cudaMemsetAsync(dql scratch)") != OMCUDA_OK)
     return nullptr;
-  g_dql_scratch[st] = p;
   return p;
 }
 
@@ -194,6 +197,8 @@ void *dql_scratch_for(cudaStream_t st) {
 
 struct PreparedEntry {
   omcudaPreparedB pb;
+  cudaStream_t stream; // where the prepare kernels ran
+  cudaEvent_t ready;   // recorded behind them
 };
 std::mutex g_const_mutex;
 std::set<const void *> g_const_ptrs;
@@ -204,8 +209,10 @@ bool is_registered_constant(const void *p) {
   return g_const_ptrs.count(p) != 0;
 }
 
-// Returns a prepared form of B ([K,N], 8-bit).  `b_host_or_dev` is the tensor's
-// own pointer (the cache key); `b_dev` the staged device copy.
+// Returns a prepared form of B ([K,N], 8-bit).  `key_ptr` is the tensor's own
+// pointer (the cache key); `b_dev` the staged device copy.  A cache hit from a
+// stream other than the one that prepared the entry first waits for that
+// prepare to finish.
 int prepared_b(Stage &sg, const void *key_ptr, const void *b_dev, int b_signed,
     int64_t K, int64_t N, cudaStream_t st, omcudaPreparedB *out) {
   bool cacheable = is_registered_constant(key_ptr);
@@ -214,6 +221,8 @@ int prepared_b(Stage &sg, const void *key_ptr, const void *b_dev, int b_signed,
     std::lock_guard<std::mutex> lock(g_const_mutex);
     auto it = g_prepared.find(key);
     if (it != g_prepared.end()) {
+      if (it->second.stream != st && it->second.ready)
+        OMCUDA_CHECK(cudaStreamWaitEvent(st, it->second.ready, 0));
       *out = it->second.pb;
       return OMCUDA_OK;
     }
@@ -223,20 +232,49 @@ int prepared_b(Stage &sg, const void *key_ptr, const void *b_dev, int b_signed,
   omcudaPreparedB pb;
   memset(&pb, 0, sizeof(pb));
   if (cacheable) {
-    pb.bt = pool_alloc((size_t)bytes);
-    pb.colsum = (int32_t *)pool_alloc((size_t)N * sizeof(int32_t));
+    pb.bt = pool_alloc_on((size_t)bytes, st);
+    pb.colsum = (int32_t *)pool_alloc_on((size_t)N * sizeof(int32_t), st);
   } else {
     pb.bt = sg.scratch((size_t)bytes);
     pb.colsum = (int32_t *)sg.scratch((size_t)N * sizeof(int32_t));
   }
-  if (!pb.bt || !pb.colsum)
+  if (!pb.bt || !pb.colsum) {
+    if (cacheable) {
+      sg.adopt(pb.bt);
+      sg.adopt(pb.colsum);
+    }
     return OMCUDA_ENOMEM;
+  }
   int rc = omcudaDevPrepareB(b_dev, b_signed, K, N, &pb, st);
-  if (rc != OMCUDA_OK)
+  if (rc != OMCUDA_OK) {
+    if (cacheable) {
+      sg.adopt(pb.bt);
+      sg.adopt(pb.colsum);
+    }
     return rc;
+  }
   if (cacheable) {
+    cudaEvent_t ev = nullptr;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventRecord(ev, st) != cudaSuccess) {
+      (void)cudaGetLastError();
+      if (ev)
+        cudaEventDestroy(ev);
+      ev = nullptr;
+      // no event to order other streams behind: finish the prepare now
+      OMCUDA_CHECK(cudaStreamSynchronize(st));
+    }
     std::lock_guard<std::mutex> lock(g_const_mutex);
-    g_prepared[key] = PreparedEntry{pb};
+    if (g_prepared.count(key)) {
+      // Another thread prepared the same constant meanwhile: use ours for this
+      // call only and give it back at the end of the call.
+      sg.adopt(pb.bt);
+      sg.adopt(pb.colsum);
+      if (ev)
+        cudaEventDestroy(ev);
+    } else {
+      g_prepared[key] = PreparedEntry{pb, st, ev};
+    }
   }
   *out = pb;
   return OMCUDA_OK;
@@ -244,13 +282,18 @@ int prepared_b(Stage &sg, const void *key_ptr, const void *b_dev, int b_signed,
 
 bool begin_call() { return !sticky_error() && ensure_init() == OMCUDA_OK; }
 
+// numpy-style matmul shapes (src/Dialect/ONNX/ONNXOps/Math/MatMul.cpp:46-166):
+// a 1-D A is a row vector, a 1-D B a column vector, and the leading (batch)
+// dimensions of A [.., M, K] and B [.., K, N] broadcast against each other.
+// The result is a list of 2-D products: product i reads A at element offset
+// a_off[i], B at b_off[i] and writes Y at i * M * N.  An unbatched B folds all
+// of A's leading dimensions into M (one product).
 struct MatDims {
   int64_t batch, M, K, N;
   bool b_batched;
+  std::vector<int64_t> a_off, b_off;
 };
 
-// numpy-style matmul shapes restricted to what the quantized path produces:
-// A [.., M, K] (or [K]) times B [K, N] (or [K]), or equal leading batch dims.
 int matmul_dims(const OMTensor *A, const OMTensor *B, MatDims *d) {
   int64_t ra = omTensorGetRank(A), rb = omTensorGetRank(B);
   const int64_t *sa = omTensorGetShape(A), *sb = omTensorGetShape(B);
@@ -262,26 +305,52 @@ int matmul_dims(const OMTensor *A, const OMTensor *B, MatDims *d) {
   if (kb != d->K)
     return fail(OMCUDA_EINVAL, "matmul: inner dimensions differ (%lld vs %lld)",
         (long long)d->K, (long long)kb);
-  int64_t rows = 1;
-  for (int64_t i = 0; i + 1 < ra; ++i)
-    rows *= sa[i];
+  d->a_off.assign(1, 0);
+  d->b_off.assign(1, 0);
   if (rb <= 2) {
+    int64_t rows = 1;
+    for (int64_t i = 0; i + 1 < ra; ++i)
+      rows *= sa[i];
     d->batch = 1;
     d->M = rows;
     d->b_batched = false;
     return OMCUDA_OK;
   }
-  if (rb != ra)
-    return fail(OMCUDA_ENOTSUP, "matmul: broadcast batch dims are not supported");
-  int64_t batch = 1;
-  for (int64_t i = 0; i + 2 < ra; ++i) {
-    if (sa[i] != sb[i])
-      return fail(OMCUDA_ENOTSUP, "matmul: broadcast batch dims are not supported");
-    batch *= sa[i];
+  // Batch dimensions, right-aligned: A's are sa[0 .. ra-2) (none for a vector),
+  // B's are sb[0 .. rb-2).
+  const int64_t na = ra >= 2 ? ra - 2 : 0, nb = rb - 2;
+  const int64_t nd = na > nb ? na : nb;
+  d->M = ra >= 2 ? sa[ra - 2] : 1;
+  std::vector<int64_t> dims((size_t)nd), astr((size_t)nd), bstr((size_t)nd);
+  int64_t arun = d->M * d->K, brun = d->K * d->N, batch = 1;
+  for (int64_t i = nd - 1; i >= 0; --i) {
+    const int64_t ia = i - (nd - na), ib = i - (nd - nb);
+    const int64_t da = ia >= 0 ? sa[ia] : 1, db = ib >= 0 ? sb[ib] : 1;
+    if (da != db && da != 1 && db != 1)
+      return fail(OMCUDA_EINVAL, "matmul: batch dimensions %lld and %lld do not broadcast",
+          (long long)da, (long long)db);
+    dims[(size_t)i] = da == 1 ? db : da;
+    astr[(size_t)i] = da == 1 ? 0 : arun; // a broadcast dimension does not advance
+    bstr[(size_t)i] = db == 1 ? 0 : brun;
+    arun *= da;
+    brun *= db;
+    batch *= dims[(size_t)i];
   }
   d->batch = batch;
-  d->M = sa[ra - 2];
   d->b_batched = true;
+  d->a_off.assign((size_t)batch, 0);
+  d->b_off.assign((size_t)batch, 0);
+  for (int64_t i = 0; i < batch; ++i) {
+    int64_t rem = i, ao = 0, bo = 0;
+    for (int64_t k = nd - 1; k >= 0; --k) {
+      const int64_t idx = rem % dims[(size_t)k];
+      rem /= dims[(size_t)k];
+      ao += idx * astr[(size_t)k];
+      bo += idx * bstr[(size_t)k];
+    }
+    d->a_off[(size_t)i] = ao;
+    d->b_off[(size_t)i] = bo;
+  }
   return OMCUDA_OK;
 }
 
@@ -383,6 +452,10 @@ void omcudaRegisterConstant(const OMTensor *t) {
 void omcudaForgetConstants(void) {
   std::lock_guard<std::mutex> lock(g_const_mutex);
   for (auto &kv : g_prepared) {
+    if (kv.second.ready) {
+      cudaEventSynchronize(kv.second.ready);
+      cudaEventDestroy(kv.second.ready);
+    }
     pool_free(kv.second.pb.bt);
     pool_free(kv.second.pb.colsum);
   }
@@ -422,7 +495,7 @@ void omcudaDynamicQuantizeLinear(
   uint8_t *dy = (uint8_t *)sg.out(y);
   float *ds = (float *)sg.out(yScale);
   uint8_t *dz = (uint8_t *)sg.out(yZp);
-  void *scr = dql_scratch_for(st);
+  void *scr = dql_scratch_for(sg, st);
   if (!sg.ok() || !scr)
     return;
   sg.set(omcudaDevDynamicQuantizeLinear(
@@ -556,20 +629,28 @@ void omcudaMatMulInteger(OMTensor *Y, const OMTensor *A, const OMTensor *B,
   int32_t *dY = (int32_t *)sg.out(Y);
   if (!sg.ok())
     return;
+  // A B slice that several products share (a broadcast batch dimension) is
+  // prepared once.
+  std::map<int64_t, omcudaPreparedB> prepared;
   for (int64_t b = 0; b < d.batch && sg.ok(); ++b) {
     omcudaGemmArgs g;
     memset(&g, 0, sizeof(g));
     g.M = d.M;
     g.N = d.N;
     g.K = d.K;
-    g.A = dA + b * d.M * d.K;
+    g.A = dA + d.a_off[(size_t)b];
     g.a_signed = at == ONNX_TYPE_INT8;
-    const uint8_t *bsrc = dB + (d.b_batched ? b * d.K * d.N : 0);
-    const void *key = (const uint8_t *)omTensorGetDataPtr(B) +
-                      (d.b_batched ? b * d.K * d.N : 0);
-    sg.set(prepared_b(sg, key, bsrc, bt == ONNX_TYPE_INT8, d.K, d.N, st, &g.B));
-    if (!sg.ok())
-      break;
+    const int64_t bo = d.b_off[(size_t)b];
+    auto hit = prepared.find(bo);
+    if (hit != prepared.end()) {
+      g.B = hit->second;
+    } else {
+      const void *key = (const uint8_t *)omTensorGetDataPtr(B) + bo;
+      sg.set(prepared_b(sg, key, dB + bo, bt == ONNX_TYPE_INT8, d.K, d.N, st, &g.B));
+      if (!sg.ok())
+        break;
+      prepared[bo] = g.B;
+    }
     g.a_zp = dAz;
     g.a_zp_len = azn;
     g.b_zp = dBz;
@@ -744,7 +825,7 @@ void omcudaDynQuantLinear(OMTensor *Y, const OMTensor *X, const OMTensor *Wq,
   float *dY = (float *)sg.out(Y);
   uint8_t *xq = (uint8_t *)sg.scratch((size_t)(d.M * d.K));
   float *xs = (float *)sg.scratch(16);
-  void *scr = dql_scratch_for(st);
+  void *scr = dql_scratch_for(sg, st);
   if (!sg.ok() || !scr)
     return;
   uint8_t *xz = (uint8_t *)(xs + 1);
@@ -930,10 +1011,16 @@ void omcudaMatMulF32(OMTensor *y, const OMTensor *a, const OMTensor *b) {
   float *dy = (float *)sg.out(y);
   if (!sg.ok())
     return;
-  if (d.b_batched) {
+  bool uniform = true; // equal batch dimensions on both sides: one launch
+  for (int64_t b = 0; b < d.batch; ++b)
+    uniform = uniform && d.a_off[(size_t)b] == b * d.M * d.K &&
+              d.b_off[(size_t)b] == b * d.K * d.N;
+  if (uniform) {
     sg.set(omcudaDevMatMulF32(da, db, d.batch, d.M, d.N, d.K, dy, st));
   } else {
-    sg.set(omcudaDevMatMulF32(da, db, 1, d.M, d.N, d.K, dy, st));
+    for (int64_t b = 0; b < d.batch && sg.ok(); ++b)
+      sg.set(omcudaDevMatMulF32(da + d.a_off[(size_t)b], db + d.b_off[(size_t)b], 1,
+          d.M, d.N, d.K, dy + b * d.M * d.N, st));
   }
   sg.finish(false);
 }
@@ -958,7 +1045,10 @@ void omcudaAttention(OMTensor *y, const OMTensor *q, const OMTensor *k,
   if (!sg.ok())
     return;
   const int64_t B = s[0], S = s[1], H = s[2], dh = H / heads, T = B * S;
-  if (omcudaDevAttentionBf16Supported(B, S, heads, dh, 3 * H, H) &&
+  // (the tensor-core kernel needs a positive finite scale; any other constant
+  // of the graph's Mul goes to the fp32 kernels, which scale before the max)
+  const bool tc_scale = scale > 0.0 && (float)scale < INFINITY;
+  if (tc_scale && omcudaDevAttentionBf16Supported(B, S, heads, dh, 3 * H, H) &&
       ((((uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv | (uintptr_t)dy) & 15u) == 0)) {
     // Tensor-core path: split the operands into bf16 hi/lo planes [T, 3H]
     // (Q | K | V side by side, the layout the fused QKV projection writes).

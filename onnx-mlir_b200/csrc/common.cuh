@@ -86,29 +86,57 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // Gelu with the exact (erf) formula of the reference,
 // 0.5 * x * (1 + erf(x / sqrt(2))) (src/Conversion/ONNXToKrnl/Math/Elementwise.cpp:358-388),
-// with erf evaluated without a branch as
-//   erf(t) = 1 - 2^(t * Q(t)),  t = min(|x| / sqrt(2), 4),  sign restored,
-// Q a degree-7 polynomial fitted (weighted least squares on [0, 4], weights
-// following the sensitivity of erf to Q) to log2(erfc(t)) / t.  Absolute
-// error of erf below 2e-7 (polynomial 8.5e-8 plus the 2^x approximation), of
-// Gelu below 4e-7 on [-8, 8]; beyond t = 4 erf is 1 in fp32.  About 15
-// instructions against the 35-40 of the library erff with both of its
-// branches taken in a warp, which matters in the GEMM epilogue.  Every Gelu
-// of the library (fused tail and standalone op) goes through this function.
+// evaluated without a branch and without the cancellation of 1 + erf for
+// negative x.  With t = min(|x| / sqrt(2), 4) and E(t) = 2^(t * Q(t)) an
+// approximation of erfc(t) (Q a degree-8 polynomial fitted to
+// log2(erfc(t)) / t on [0, 4] so that the error of the exponent t * Q(t), i.e.
+// the relative error of E, is uniform: 8e-7),
+//   x >= 0:  0.5 x (1 + erf)  = x - (t / sqrt(2)) E(t)
+//   x <  0:  0.5 x erfc(|x|/sqrt(2)) = - (t / sqrt(2)) E(t)
+// both of which are  max(x, 0) - (t / sqrt(2)) E(t)  (one fused multiply-add).
+// Relative error against the exactly rounded formula: below 4e-6 everywhere
+// the reference's own result is meaningful.  For x < 0 the reference rounds
+// erff to fp32 before adding 1, which quantizes its result to multiples of
+// 0.5 |x| 2^-24; this function does not reproduce that rounding step, so the
+// two differ by up to half such a step there (and the reference's result is
+// exactly -0 below x = -5.6, where this one is about -4e-8).  NaN gives NaN,
+// +inf gives +inf; -inf gives -4e-8 where the reference's 0 * inf gives NaN.
+// About 14 instructions against the 35-40 of the library erff with both of
+// its branches taken in a warp, which matters in the GEMM epilogue.  Every
+// Gelu of the library (fused tail and standalone op) goes through this
+// function or its two-lane form below.
+#define OMCUDA_GELU_Q0 -1.627946138381958f
+#define OMCUDA_GELU_Q1 -0.9180199503898621f
+#define OMCUDA_GELU_Q2 -0.14988861978054047f
+#define OMCUDA_GELU_Q3 0.030609266832470894f
+#define OMCUDA_GELU_Q4 -0.002864620415493846f
+#define OMCUDA_GELU_Q5 -0.0004925866960547864f
+#define OMCUDA_GELU_Q6 0.00021463484154082835f
+#define OMCUDA_GELU_Q7 -3.0283568776212633e-05f
+#define OMCUDA_GELU_Q8 1.6220828911173157e-06f
+
+// max(x, 0) that keeps a NaN (fmaxf would drop it).
+__device__ __forceinline__ float relu_keep_nan(float x) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(0.0f));
+  return r;
+}
+
 __device__ __forceinline__ float gelu_erf(float x) {
-  const float t = fminf(fabsf(__fmul_rn(x, 0.70710678118654752440f)), 4.0f);
-  float q = -4.5358585339272395e-05f;
-  q = __fmaf_rn(q, t, 0.00044550743768922985f);
-  q = __fmaf_rn(q, t, -0.0014894406776875257f);
-  q = __fmaf_rn(q, t, -0.0007746315677650273f);
-  q = __fmaf_rn(q, t, 0.02825368382036686f);
-  q = __fmaf_rn(q, t, -0.14848162233829498f);
-  q = __fmaf_rn(q, t, -0.9184163808822632f);
-  q = __fmaf_rn(q, t, -1.6279085874557495f);
+  const float c = 0.70710678118654752440f;
+  const float t = fminf(fabsf(__fmul_rn(x, c)), 4.0f);
+  float q = OMCUDA_GELU_Q8;
+  q = __fmaf_rn(q, t, OMCUDA_GELU_Q7);
+  q = __fmaf_rn(q, t, OMCUDA_GELU_Q6);
+  q = __fmaf_rn(q, t, OMCUDA_GELU_Q5);
+  q = __fmaf_rn(q, t, OMCUDA_GELU_Q4);
+  q = __fmaf_rn(q, t, OMCUDA_GELU_Q3);
+  q = __fmaf_rn(q, t, OMCUDA_GELU_Q2);
+  q = __fmaf_rn(q, t, OMCUDA_GELU_Q1);
+  q = __fmaf_rn(q, t, OMCUDA_GELU_Q0);
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(q, t)));
-  const float r = copysignf(__fsub_rn(1.0f, e), x);
-  return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, r));
+  return __fmaf_rn(__fmul_rn(t, -c), e, relu_keep_nan(x));
 }
 
 // Three-input fp32 min / max of sm_100 (same result as two fminf / fmaxf:
@@ -154,32 +182,30 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
 }
 
 __device__ __forceinline__ void gelu_erf_x2(float &x0, float &x1) {
-  const uint64_t x = pack_f32x2(x0, x1);
-  float t0, t1;
-  unpack_f32x2(mul_f32x2(x, pack_f32x2(0.70710678118654752440f, 0.70710678118654752440f)),
-      t0, t1);
-  const uint64_t t = pack_f32x2(fminf(fabsf(t0), 4.0f), fminf(fabsf(t1), 4.0f));
 #define OMCUDA_C2(c) pack_f32x2(c, c)
-  uint64_t q = OMCUDA_C2(-4.5358585339272395e-05f);
-  q = fma_f32x2(q, t, OMCUDA_C2(0.00044550743768922985f));
-  q = fma_f32x2(q, t, OMCUDA_C2(-0.0014894406776875257f));
-  q = fma_f32x2(q, t, OMCUDA_C2(-0.0007746315677650273f));
-  q = fma_f32x2(q, t, OMCUDA_C2(0.02825368382036686f));
-  q = fma_f32x2(q, t, OMCUDA_C2(-0.14848162233829498f));
-  q = fma_f32x2(q, t, OMCUDA_C2(-0.9184163808822632f));
-  q = fma_f32x2(q, t, OMCUDA_C2(-1.6279085874557495f));
+  const float c = 0.70710678118654752440f;
+  float t0, t1;
+  unpack_f32x2(mul_f32x2(pack_f32x2(x0, x1), OMCUDA_C2(c)), t0, t1);
+  const uint64_t t = pack_f32x2(fminf(fabsf(t0), 4.0f), fminf(fabsf(t1), 4.0f));
+  uint64_t q = OMCUDA_C2(OMCUDA_GELU_Q8);
+  q = fma_f32x2(q, t, OMCUDA_C2(OMCUDA_GELU_Q7));
+  q = fma_f32x2(q, t, OMCUDA_C2(OMCUDA_GELU_Q6));
+  q = fma_f32x2(q, t, OMCUDA_C2(OMCUDA_GELU_Q5));
+  q = fma_f32x2(q, t, OMCUDA_C2(OMCUDA_GELU_Q4));
+  q = fma_f32x2(q, t, OMCUDA_C2(OMCUDA_GELU_Q3));
+  q = fma_f32x2(q, t, OMCUDA_C2(OMCUDA_GELU_Q2));
+  q = fma_f32x2(q, t, OMCUDA_C2(OMCUDA_GELU_Q1));
+  q = fma_f32x2(q, t, OMCUDA_C2(OMCUDA_GELU_Q0));
   float a0, a1;
   unpack_f32x2(mul_f32x2(q, t), a0, a1);
   float e0, e1;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(a0));
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(a1));
-  // 1 - e, sign of x restored, then 0.5 x (1 + r)
-  const float r0 = copysignf(__fsub_rn(1.0f, e0), x0);
-  const float r1 = copysignf(__fsub_rn(1.0f, e1), x1);
-  const uint64_t h = mul_f32x2(OMCUDA_C2(0.5f), x);
-  const uint64_t s = add_f32x2(OMCUDA_C2(1.0f), pack_f32x2(r0, r1));
+  // max(x, 0) - (t / sqrt(2)) e
+  const uint64_t na = mul_f32x2(t, OMCUDA_C2(-c));
+  const uint64_t m = pack_f32x2(relu_keep_nan(x0), relu_keep_nan(x1));
 #undef OMCUDA_C2
-  unpack_f32x2(mul_f32x2(h, s), x0, x1);
+  unpack_f32x2(fma_f32x2(na, pack_f32x2(e0, e1), m), x0, x1);
 }
 
 // Order-preserving float <-> uint mapping so running min/max can use integer

@@ -299,11 +299,11 @@ int launch_attention_mma(const float *Q, const float *K, const float *V,
     attention_mma_kernel<32><<<grid, 128, smem, st>>>(
         Q, K, V, S, heads, scale, out, ld_in, ld_out, rng);
   } else {
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceInt attr_set;
+    if (!attr_set.get()) {
       OMCUDA_CHECK(cudaFuncSetAttribute(attention_mma_kernel<128>,
           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_set = true;
+      attr_set.set(1);
     }
     attention_mma_kernel<128><<<grid, 128, smem, st>>>(
         Q, K, V, S, heads, scale, out, ld_in, ld_out, rng);

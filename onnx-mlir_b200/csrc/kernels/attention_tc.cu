@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
         const __grid_constant__ CUtensorMap map_lo,
         const __grid_constant__ CUtensorMap map_out, int32_t q_col, int32_t k_col,
         int32_t v_col, int64_t S, int64_t heads, int64_t n_items, float scale_log2e,
-        uint32_t *__restrict__ out_range, int *status) {
+        uint32_t *__restrict__ out_range, int *status, uint64_t wait_ns) {
   extern __shared__ uint8_t att_tc_smem[];
   __shared__ uint64_t bar_q, bar_k, bar_v, bar_s, bar_o;
   __shared__ uint32_t tmem_slot;
@@ -214,7 +214,6 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
   // the rest.
   const int quad = warp & 3, half = warp >> 2;
   const int row = quad * 32 + lane;
-  const uint64_t t0 = global_timer();
   const int nkb = (int)(S / kTK);
   const int nq = (int)(S / kTQ);
 
@@ -300,8 +299,8 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
       // ---- S = Q K_j^T ----
       if (tid == 0) {
         if (j == 0)
-          ok = mbar_wait(smem_u32(&bar_q), nitem & 1u, abortp, t0);
-        ok = ok && mbar_wait(smem_u32(&bar_k), ph, abortp, t0);
+          ok = mbar_wait(smem_u32(&bar_q), nitem & 1u, abortp, wait_ns);
+        ok = ok && mbar_wait(smem_u32(&bar_k), ph, abortp, wait_ns);
         if (ok) {
           tcgen05_fence_after();
           // small terms first: Ql Kh, Qh Kl, then Qh Kh
@@ -321,7 +320,7 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
             tma_load_2d(s_vh, &map_hi, it.cv, it.row_kv, smem_u32(&bar_v));
             tma_load_2d(s_vl, &map_lo, it.cv, it.row_kv, smem_u32(&bar_v));
           }
-          ok = mbar_wait(smem_u32(&bar_s), ph, abortp, t0);
+          ok = mbar_wait(smem_u32(&bar_s), ph, abortp, wait_ns);
           if (ok && j + 1 < nkb) { // the K buffers are free again
             mbar_expect_tx(smem_u32(&bar_k), 2 * kTile);
             tma_load_2d(s_kh, &map_hi, it.ck, it.row_kv + (j + 1) * kTK, smem_u32(&bar_k));
@@ -439,7 +438,7 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
       // ---- O_j = P V_j ----
       if (tid == 0) {
         tcgen05_fence_after();
-        ok = mbar_wait(smem_u32(&bar_v), ph, abortp, t0);
+        ok = mbar_wait(smem_u32(&bar_v), ph, abortp, wait_ns);
         if (ok) {
           tcgen05_fence_after();
           static_assert(kTK == 128, "two groups of four 16-key slices per block");
@@ -452,7 +451,7 @@ __global__ void __launch_bounds__(kTcAttThreads, 2)
           umma_bf16_ts_x4(t_o, t_s + 16u, dvh, kIdescPV, 1u);
           umma_bf16_ts_x4(t_o, t_s + 64u + 16u, dvh + 512, kIdescPV, 1u);
           umma_commit(smem_u32(&bar_o));
-          ok = mbar_wait(smem_u32(&bar_o), ph, abortp, t0);
+          ok = mbar_wait(smem_u32(&bar_o), ph, abortp, wait_ns);
           if (ok && j + 1 < nkb) { // the V buffers are free again
             mbar_expect_tx(smem_u32(&bar_v), 2 * kTile);
             tma_load_2d(s_vh, &map_hi, it.cv, it.row_kv + (j + 1) * kTK, smem_u32(&bar_v));
@@ -579,11 +578,11 @@ int launch_attention_tc(const void *hi, const void *lo, int64_t ld_planes,
     cudaStream_t st) {
   if ((q_col | k_col | v_col) % 8 != 0)
     return fail(OMCUDA_EINVAL, "Attention: column offsets must be multiples of 8");
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceInt attr_set;
+  if (!attr_set.get()) {
     OMCUDA_CHECK(cudaFuncSetAttribute(attention_tc_kernel,
         cudaFuncAttributeMaxDynamicSharedMemorySize, kTcAttSmem));
-    attr_set = true;
+    attr_set.set(1);
   }
   const int64_t T = B * S;
   CUtensorMap map_hi, map_lo, map_out;
@@ -608,7 +607,7 @@ int launch_attention_tc(const void *hi, const void *lo, int64_t ld_planes,
   const unsigned grid = (unsigned)(n_items < resident ? n_items : resident);
   attention_tc_kernel<<<grid, kTcAttThreads, kTcAttSmem, st>>>(map_hi, map_lo, map_out,
       (int32_t)q_col, (int32_t)k_col, (int32_t)v_col, S, heads, n_items, scale_log2e,
-      (uint32_t *)out_range, status);
+      (uint32_t *)out_range, status, tc_wait_limit_ns());
   OMCUDA_CHECK_LAUNCH("attention_tc_kernel");
   return OMCUDA_OK;
 }
@@ -660,6 +659,13 @@ extern "C" int omcudaDevAttentionBf16(const void *hi, const void *lo,
       ld_planes < heads * dh + (q_col > k_col ? (q_col > v_col ? q_col : v_col)
                                                : (k_col > v_col ? k_col : v_col)))
     return fail(OMCUDA_EINVAL, "AttentionBf16: bad argument");
+  // The kernel takes the row maximum of the raw scores and scales it
+  // afterwards, which equals the maximum of the scaled scores only for a
+  // positive scale.
+  if (!(scale > 0.0f) || !(scale < INFINITY))
+    return fail(OMCUDA_EINVAL,
+        "AttentionBf16: the scale must be positive and finite (got %g); "
+        "omcudaDevAttention takes any scale", (double)scale);
   if (B == 0)
     return OMCUDA_OK;
   if (!attention_tc_supported(B, S, heads, dh, ld_planes, ld_out, hi, lo, out))

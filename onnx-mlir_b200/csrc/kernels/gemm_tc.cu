@@ -26,14 +26,17 @@
 // The two accumulator buffers let the epilogue of tile i overlap the MMAs of
 // tile i+1.
 //
-// Every wait on an mbarrier is bounded: after about two seconds without
-// progress the waiting thread raises a CTA-wide abort flag, the kernel writes
-// a non-zero word to *status, releases its tensor memory and returns.
+// Every wait on an mbarrier is bounded: after wait_ns (two seconds unless
+// omcudaDevSetWaitLimitNs changed it) without progress of that one wait, the
+// waiting thread raises a CTA-wide abort flag, the kernel writes a non-zero
+// word to *status, releases its tensor memory and returns.
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "../runtime/internal.h"
 #include "gemm_epilogue.cuh"
@@ -478,7 +481,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         const __grid_constant__ CUtensorMap map_b,
         const __grid_constant__ CUtensorMap map_y,
         const __grid_constant__ CUtensorMap map_y2, EpiParams p, uint32_t idesc,
-        int *status) {
+        int *status, uint64_t wait_ns) {
   using Cfg = TcConfig<BN, EW>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kHalfCols = epi_cols_per_warp(BN, EW); // columns per epilogue warp of a lane quadrant
@@ -493,7 +496,6 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint64_t t0 = global_timer();
 
   // 128-byte-swizzled tiles must start on a 1024-byte boundary.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -543,7 +545,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         const int32_t m0 = (int32_t)((t / tiles_n) * kBM);
         const int32_t n0 = (int32_t)((t % tiles_n) * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, t0)) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, wait_ns)) {
             ok = false;
             break;
           }
@@ -574,14 +576,14 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
         const int buf = (int)(it & 1);
         const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
-        if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp, t0)) {
+        if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp, wait_ns)) {
           ok = false;
           break;
         }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!landed && !mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, t0)) {
+          if (!landed && !mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, wait_ns)) {
             ok = false;
             break;
           }
@@ -644,7 +646,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(rr + c));
         }
       }
-      if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase, abortp, t0)) {
+      if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase, abortp, wait_ns)) {
         ok = false;
         break;
       }
@@ -729,7 +731,8 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         const __grid_constant__ CUtensorMap map_b_half,
         const __grid_constant__ CUtensorMap map_y,
         const __grid_constant__ CUtensorMap map_y2, EpiParams p, uint32_t idesc,
-        uint32_t idesc_half, int64_t full_units, int64_t num_units, int *status) {
+        uint32_t idesc_half, int64_t full_units, int64_t num_units, int *status,
+        uint64_t wait_ns) {
   constexpr int BN = 256;
   constexpr int kABytes = kBM * kBK;
   constexpr int kBHalfBytes = (BN / 2) * kBK;
@@ -749,7 +752,6 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint64_t t0 = global_timer();
   const uint32_t rank = cluster_ctarank(); // 0 = leader
   const int64_t cluster_id = blockIdx.x >> 1;
   const int64_t num_clusters = gridDim.x >> 1;
@@ -805,7 +807,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
                                : (int32_t)((t % tiles_n) * BN + rank * (BN / 2));
         const uint32_t stage_tx = un.narrow ? kABytes + kBHalfBytes / 2 : kStageBytes;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, t0)) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, wait_ns)) {
             ok = false;
             break;
           }
@@ -835,14 +837,14 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         const uint32_t unit_idesc = u < full_units ? idesc : idesc_half;
         const int buf = (int)(it & 1);
         const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
-        if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp, t0)) {
+        if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp, wait_ns)) {
           ok = false;
           break;
         }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!landed && !mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, t0)) {
+          if (!landed && !mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, wait_ns)) {
             ok = false;
             break;
           }
@@ -907,7 +909,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(rr + c));
         }
       }
-      if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase, abortp, t0)) {
+      if (!mbar_wait(smem_u32(&bar_acc_full[buf]), acc_phase, abortp, wait_ns)) {
         ok = false;
         break;
       }
@@ -961,16 +963,15 @@ int make_tma_map_2d(CUtensorMap *map, const void *base, int64_t rows,
       const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
   static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static std::once_flag looked_up;
+  std::call_once(looked_up, [] {
     void *sym = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault,
             &qres) == cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
       fn = (EncodeTiledFn)sym;
-  }
+  });
   if (!fn)
     return fail(OMCUDA_ECUDA, "cuTensorMapEncodeTiled is not available");
   // A box row must span exactly the swizzle width, so that rows are packed
@@ -997,18 +998,34 @@ int make_tma_map_2d(CUtensorMap *map, const void *base, int64_t rows,
   return OMCUDA_OK;
 }
 
-// One device word shared by the tensor-core kernels: set to non-zero by a CTA
-// whose bounded wait gave up.
-static int *g_status_word = nullptr;
+// State the tensor-core launchers keep per device (the device current on the
+// calling thread): the status word a CTA whose bounded wait gave up sets to
+// non-zero, and which kernels already had their launch attributes set.
+// Guarded by one mutex; the launch path takes it only for a table look-up.
+static std::mutex g_dev_mutex;
+static int *g_status_words[kMaxDevices] = {nullptr};
+static std::atomic<uint64_t> g_wait_limit_ns{kWaitLimitNs};
+
 
 int *tc_status_word() {
-  if (!g_status_word) {
-    if (cudaMalloc(&g_status_word, sizeof(int)) != cudaSuccess)
+  const int dev = current_device_index();
+  if (dev < 0)
+    return nullptr;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!g_status_words[dev]) {
+    int *w = nullptr;
+    if (cudaMalloc(&w, sizeof(int)) != cudaSuccess)
       return nullptr;
-    cudaMemset(g_status_word, 0, sizeof(int));
+    if (cudaMemset(w, 0, sizeof(int)) != cudaSuccess) {
+      cudaFree(w);
+      return nullptr;
+    }
+    g_status_words[dev] = w;
   }
-  return g_status_word;
+  return g_status_words[dev];
 }
+
+uint64_t tc_wait_limit_ns() { return g_wait_limit_ns.load(std::memory_order_relaxed); }
 
 namespace {
 
@@ -1074,11 +1091,11 @@ int make_y_maps(const omcudaGemmArgs &a, int half_cols, bool line_store,
 template <int BN, int EPI, int EW>
 int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   using Cfg = TcConfig<BN, EW>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceInt attr_set;
+  if (!attr_set.get()) {
     OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc_kernel<BN, EPI, EW>,
         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-    attr_set = true;
+    attr_set.set(1);
   }
   CUtensorMap map_a, map_b;
   int rc = make_map(&map_a, a.A, a.M, a.K, a.K, kBM);
@@ -1100,7 +1117,7 @@ int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   uint32_t idesc = make_idesc(a.a_signed, a.B.b_signed, BN);
   gemm_i8_tc_kernel<BN, EPI, EW><<<grid, tc_threads(EW), Cfg::kSmemBytes, st>>>(
-      map_a, map_b, map_y, map_y2, p, idesc, status);
+      map_a, map_b, map_y, map_y2, p, idesc, status, tc_wait_limit_ns());
   OMCUDA_CHECK_LAUNCH("gemm_i8_tc_kernel");
   return OMCUDA_OK;
 }
@@ -1161,7 +1178,8 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   constexpr int kPairSmemBytes =
       tc_stages(kBM * kBK + 128 * kBK, EW) * (kBM * kBK + 128 * kBK) +
       EW * 32 * 128 + 1024;
-  static int max_clusters = 0;
+  static PerDeviceInt max_clusters_dev;
+  int max_clusters = max_clusters_dev.get();
   if (max_clusters == 0) {
     OMCUDA_CHECK(cudaFuncSetAttribute(gemm_i8_tc2_kernel<EPI, EW>,
         cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes));
@@ -1179,6 +1197,7 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
     int n = 0;
     OMCUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, gemm_i8_tc2_kernel<EPI, EW>, &q));
     max_clusters = n > 0 ? n : 1;
+    max_clusters_dev.set(max_clusters);
   }
   CUtensorMap map_a, map_b;
   int rc = make_map(&map_a, a.A, a.M, a.K, a.K, kBM);
@@ -1227,7 +1246,8 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   if (rc != OMCUDA_OK)
     return rc;
   OMCUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_i8_tc2_kernel<EPI, EW>, map_a, map_b,
-      map_b_half, map_y, map_y2, p, idesc, idesc_half, full_units, num_units, status));
+      map_b_half, map_y, map_y2, p, idesc, idesc_half, full_units, num_units, status,
+      tc_wait_limit_ns()));
   count_launch();
   return OMCUDA_OK;
 }
@@ -1293,21 +1313,86 @@ int launch_gemm_tc(const omcudaGemmArgs &a, cudaStream_t st) {
   return launch_bn<64>(a, st);
 }
 
-// Reads (and clears) the word the GEMM kernels raise when a bounded wait gave
-// up.  Synchronises the stream.
+// Reads (and clears) the word the tensor-core kernels raise when a bounded
+// wait gave up.  Synchronises the stream.
 int gemm_tc_check_status(cudaStream_t st) {
-  if (!g_status_word)
+  int *word = nullptr;
+  {
+    const int dev = current_device_index();
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    word = dev >= 0 ? g_status_words[dev] : nullptr;
+  }
+  if (!word)
     return OMCUDA_OK;
   int h = 0;
-  OMCUDA_CHECK(cudaMemcpyAsync(&h, g_status_word, sizeof(int),
-      cudaMemcpyDeviceToHost, st));
+  OMCUDA_CHECK(cudaMemcpyAsync(&h, word, sizeof(int), cudaMemcpyDeviceToHost, st));
   OMCUDA_CHECK(cudaStreamSynchronize(st));
   if (h != 0) {
-    cudaMemsetAsync(g_status_word, 0, sizeof(int), st);
+    cudaMemsetAsync(word, 0, sizeof(int), st);
     return fail(OMCUDA_ETIMEDOUT,
-        "int8 GEMM: a device-side wait on the TMA/MMA pipeline timed out");
+        "a device-side wait on the TMA/MMA pipeline of a tensor-core kernel timed out");
   }
   return OMCUDA_OK;
 }
 
+// ---- bounded-wait self test ---------------------------------------------------------
+//
+// One CTA that does what the GEMM kernels do around a wait -- allocate tensor
+// memory, arm an mbarrier, wait on it with mbar_wait -- except that nobody ever
+// signals the barrier.  The wait must give up after wait_ns by itself, the CTA
+// must free its tensor memory, raise the status word and return.
+__global__ void __launch_bounds__(64, 1)
+    bounded_wait_selftest_kernel(int *status, uint64_t wait_ns, uint64_t *waited_ns) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1)
+    tmem_alloc(smem_u32(&tmem_base_slot), 64);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  if (threadIdx.x == 0) {
+    const uint64_t t0 = global_timer();
+    (void)mbar_wait(smem_u32(&bar), 0, &abort_flag, wait_ns); // phase 0 never completes
+    if (waited_ns)
+      *waited_ns = global_timer() - t0;
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 64);
+  }
+  if (threadIdx.x == 0 && abort_flag)
+    atomicExch(status, 1);
+}
+
 } // namespace omcuda
+
+extern "C" void omcudaDevSetWaitLimitNs(int64_t ns) {
+  omcuda::g_wait_limit_ns.store(
+      ns > 0 ? (uint64_t)ns : omcuda::kWaitLimitNs, std::memory_order_relaxed);
+}
+
+extern "C" int omcudaDevSelfTestBoundedWait(uint64_t *waited_ns_dev, void *stream) {
+  using namespace omcuda;
+  if (ensure_init() != OMCUDA_OK)
+    return omcudaGetLastError();
+  int *status = tc_status_word();
+  if (!status)
+    return fail(OMCUDA_ENOMEM, "SelfTestBoundedWait: cannot allocate the status word");
+  // Never wait longer than a second here, whatever the configured limit.
+  uint64_t ns = tc_wait_limit_ns();
+  if (ns > 1000000000ull)
+    ns = 1000000000ull;
+  bounded_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(status, ns, waited_ns_dev);
+  OMCUDA_CHECK_LAUNCH("bounded_wait_selftest_kernel");
+  return OMCUDA_OK;
+}

@@ -11,7 +11,8 @@ namespace omcuda {
 
 namespace {
 
-// Upper bound of any device-side wait, in nanoseconds of %globaltimer.
+// Default upper bound of one device-side wait, in nanoseconds of %globaltimer
+// (omcudaDevSetWaitLimitNs changes it; the kernels receive it as an argument).
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 // ---- PTX wrappers -------------------------------------------------------------
@@ -69,15 +70,22 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false when the CTA is aborting.
+// Bounded wait.  Returns false when the CTA is aborting.  The clock starts
+// with this wait (it is first read after 256 failed polls, so a wait that
+// succeeds at once never touches it): the limit is time without progress, not
+// kernel lifetime, and a long persistent launch is not cut short.
 __device__ __forceinline__ bool mbar_wait(
-    uint32_t bar, uint32_t parity, volatile int *abort_flag, uint64_t t0) {
+    uint32_t bar, uint32_t parity, volatile int *abort_flag, uint64_t limit_ns) {
   uint32_t spins = 0;
+  uint64_t t_start = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xffu) == 0) {
       if (*abort_flag)
         return false;
-      if (global_timer() - t0 > kWaitLimitNs) {
+      const uint64_t now = global_timer();
+      if (t_start == 0) {
+        t_start = now;
+      } else if (now - t_start > limit_ns) {
         *abort_flag = 1;
         return false;
       }
@@ -336,6 +344,9 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask
 int make_tma_map_2d(CUtensorMap *map, const void *base, int64_t rows,
     int64_t cols, int64_t pitch, int box_cols, int box_rows, int esize,
     int swizzle_bytes);
+// Per-device status word the tensor-core kernels raise on a bounded-wait
+// timeout (device of the calling thread), and the wait limit they are given.
 int *tc_status_word();
+uint64_t tc_wait_limit_ns();
 
 } // namespace omcuda

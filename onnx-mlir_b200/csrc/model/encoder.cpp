@@ -46,12 +46,14 @@ namespace {
 struct DevBuf {
   void *p = nullptr;
   size_t bytes = 0;
-  void ensure(size_t n) {
+  // st: the stream the buffer is (and was) used on, for the pool's
+  // stream-ordered reuse.
+  void ensure(size_t n, cudaStream_t st = current_stream()) {
     if (n <= bytes)
       return;
     if (p)
-      pool_free(p);
-    p = pool_alloc(n);
+      pool_free_on(p, st);
+    p = pool_alloc_on(n, st);
     bytes = p ? n : 0;
   }
   void release() {
@@ -98,6 +100,9 @@ struct omcudaEncoder {
   std::vector<cudaEvent_t> ev;   // start/end pairs, recorded on the run stream
   size_t ev_used = 0;
   double gemm_ops = 0.0;         // 2*M*N*K summed over the recorded launches
+  // optional copy of every layer's intermediates (omcudaEncoderSetTap)
+  uint8_t *tap = nullptr;
+  int64_t tap_bytes = 0;
 };
 
 namespace {
@@ -208,6 +213,35 @@ int gemm(omcudaEncoder *e, const uint8_t *A, const uint8_t *a_zp,
   return rc;
 }
 
+int64_t up16(int64_t v) { return (v + 15) & ~int64_t(15); }
+
+void tap_layout(const omcudaEncoderConfig &c, int64_t T, omcudaEncoderTapLayout *o) {
+  const int64_t th4 = up16(T * c.hidden * 4), th1 = up16(T * c.hidden);
+  const int64_t tf4 = up16(T * c.ffn * 4), tf1 = up16(T * c.ffn);
+  int64_t at = 0;
+  o->x = at, at += th4;
+  o->xq_x = at, at += th1;
+  o->ctx = at, at += th4;
+  o->xq_ctx = at, at += th1;
+  o->h1 = at, at += th4;
+  o->xq_h1 = at, at += th1;
+  o->f = at, at += tf4;
+  o->xq_f = at, at += tf1;
+  o->y = at, at += th4;
+  o->layer_stride = at;
+  o->params = at * c.layers;
+  o->total = o->params + up16((4 * c.layers + 1) * 16);
+}
+
+int tap_copy(omcudaEncoder *e, int64_t off, const void *src, int64_t bytes,
+    cudaStream_t st) {
+  if (!e->tap)
+    return OMCUDA_OK;
+  return check_cuda(cudaMemcpyAsync(e->tap + off, src, (size_t)bytes,
+                        cudaMemcpyDeviceToDevice, st),
+      "encoder: tap copy");
+}
+
 // Off unless OMCUDA_FFN_TWO_PASS=1: on B200 the two passes over the product
 // measured slower than one pass that writes f32 plus the quantize pass (the
 // Gelu tail is bound by instruction issue, not by the f32 traffic it saves).
@@ -219,19 +253,19 @@ bool ffn_two_pass_wanted() {
   return on;
 }
 
-int ensure_workspace(omcudaEncoder *e, int64_t T) {
+int ensure_workspace(omcudaEncoder *e, int64_t T, cudaStream_t st) {
   const int64_t H = e->cfg.hidden, F = e->cfg.ffn;
   const int64_t maxk = H > F ? H : F;
   if (T > e->tokens) {
-    e->xq.ensure((size_t)(T * maxk));
-    e->qkv.ensure((size_t)(T * 3 * H) * 4);
-    e->ctx.ensure((size_t)(T * H) * 4);
-    e->a.ensure((size_t)(T * H) * 4);
-    e->h1.ensure((size_t)(T * H) * 4);
-    e->f.ensure((size_t)(T * F) * 4);
-    e->o.ensure((size_t)(T * H) * 4);
-    e->ybuf[0].ensure((size_t)(T * H) * 4);
-    e->ybuf[1].ensure((size_t)(T * H) * 4);
+    e->xq.ensure((size_t)(T * maxk), st);
+    e->qkv.ensure((size_t)(T * 3 * H) * 4, st);
+    e->ctx.ensure((size_t)(T * H) * 4, st);
+    e->a.ensure((size_t)(T * H) * 4, st);
+    e->h1.ensure((size_t)(T * H) * 4, st);
+    e->f.ensure((size_t)(T * F) * 4, st);
+    e->o.ensure((size_t)(T * H) * 4, st);
+    e->ybuf[0].ensure((size_t)(T * H) * 4, st);
+    e->ybuf[1].ensure((size_t)(T * H) * 4, st);
     if (!e->xq.p || !e->qkv.p || !e->ctx.p || !e->a.p || !e->h1.p || !e->f.p ||
         !e->o.p || !e->ybuf[0].p || !e->ybuf[1].p)
       return OMCUDA_ENOMEM;
@@ -239,12 +273,12 @@ int ensure_workspace(omcudaEncoder *e, int64_t T) {
   }
   if (!e->ranges.p) {
     size_t nr = (size_t)(4 * e->cfg.layers + 1);
-    e->ranges.ensure(nr * 8);
-    e->params.ensure(nr * 16);
-    e->dql_scratch.ensure((size_t)omcudaDevDqlScratchBytes(0));
+    e->ranges.ensure(nr * 8, st);
+    e->params.ensure(nr * 16, st);
+    e->dql_scratch.ensure((size_t)omcudaDevDqlScratchBytes(0), st);
     if (!e->ranges.p || !e->params.p || !e->dql_scratch.p)
       return OMCUDA_ENOMEM;
-    int rc = check_cuda(cudaMemset(e->dql_scratch.p, 0, e->dql_scratch.bytes),
+    int rc = check_cuda(cudaMemsetAsync(e->dql_scratch.p, 0, e->dql_scratch.bytes, st),
         "encoder: scratch");
     if (rc != OMCUDA_OK)
       return rc;
@@ -379,10 +413,10 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
       return fail(OMCUDA_EINVAL, "EncoderRun: a layer has no weights");
   const int64_t H = e->cfg.hidden, F = e->cfg.ffn, heads = e->cfg.heads;
   const int64_t dh = H / heads, T = batch * seq;
-  int rc = ensure_workspace(e, T);
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc = ensure_workspace(e, T, st);
   if (rc != OMCUDA_OK)
     return rc;
-  cudaStream_t st = (cudaStream_t)stream;
   const float att_scale = 1.0f / sqrtf((float)dh);
   const float eps = (float)e->cfg.epsilon;
   const int64_t nranges = 4 * e->cfg.layers + 1;
@@ -400,6 +434,12 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
   // the range of the activations, once to quantize them on the way out.
   // Same values, same bytes (an experiment switch, see ffn_two_pass_wanted).
   const bool ffn_two_pass = ffn_two_pass_wanted();
+  omcudaEncoderTapLayout tl;
+  tap_layout(e->cfg, T, &tl);
+  if (e->tap && (ffn_two_pass || e->tap_bytes < tl.total))
+    return fail(OMCUDA_EINVAL,
+        "EncoderRun: the tap buffer holds %lld bytes, this run needs %lld",
+        (long long)e->tap_bytes, (long long)tl.total);
   uint8_t *fq = (uint8_t *)e->f.p; // uint8 [T,F] in the two-pass form
   void *planes_hi = e->qkv.p;
   void *planes_lo = (uint8_t *)e->qkv.p + (size_t)(T * 3 * H) * 2;
@@ -432,6 +472,9 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
     if (l > 0)
       RUN(omcudaDevQuantizeFromRange(cur, T * H, r_x, xq, p_x, p_x + 2,
           (uint8_t *)(p_x + 3), st));
+    const int64_t tb = l * tl.layer_stride;
+    RUN(tap_copy(e, tb + tl.x, cur, T * H * 4, st));
+    RUN(tap_copy(e, tb + tl.xq_x, xq, T * H, st));
     if (use_tc_attention) {
       // The projection writes q | k | v straight into the bf16 hi/lo planes
       // the attention kernel reads; the f32 values never reach HBM.
@@ -450,6 +493,8 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
     }
     RUN(omcudaDevQuantizeFromRange((const float *)e->ctx.p, T * H, r_ctx, xq,
         p_ctx, p_ctx + 2, (uint8_t *)(p_ctx + 3), st));
+    RUN(tap_copy(e, tb + tl.ctx, e->ctx.p, T * H * 4, st));
+    RUN(tap_copy(e, tb + tl.xq_ctx, xq, T * H, st));
     // a = [x +] Linear(ctx): the residual add rides in the GEMM's tail when
     // the activations are too large for L2 (it saves LayerNorm one pass over
     // HBM); small ones are cheaper to add inside LayerNorm.  Same fp32 add
@@ -463,6 +508,8 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
         eps, (float *)e->h1.p, r_h1, st));
     RUN(omcudaDevQuantizeFromRange((const float *)e->h1.p, T * H, r_h1, xq,
         p_h1, p_h1 + 2, (uint8_t *)(p_h1 + 3), st));
+    RUN(tap_copy(e, tb + tl.h1, e->h1.p, T * H * 4, st));
+    RUN(tap_copy(e, tb + tl.xq_h1, xq, T * H, st));
     if (ffn_two_pass) {
       RUN(gemm(e, xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
           (const float *)L.scal.p + 1, 1, (const float *)L.b1.p, 1, nullptr, r_f,
@@ -476,6 +523,8 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
           (float *)e->f.p, r_f, st));
       RUN(omcudaDevQuantizeFromRange((const float *)e->f.p, T * F, r_f, xq, p_f,
           p_f + 2, (uint8_t *)(p_f + 3), st));
+      RUN(tap_copy(e, tb + tl.f, e->f.p, T * F * 4, st));
+      RUN(tap_copy(e, tb + tl.xq_f, xq, T * F, st));
     }
     RUN(gemm(e, ffn_two_pass ? fq : xq, (const uint8_t *)(p_f + 3), p_f + 2, L.w2, T,
         (const float *)L.scal.p + 2, 1, (const float *)L.b2.p, 0,
@@ -485,8 +534,10 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
         fuse_residual ? nullptr : (const float *)e->o.p, T, H,
         (const float *)L.ln2g.p, L.has_ln2b ? (const float *)L.ln2b.p : nullptr,
         eps, nxt, r_y, st));
+    RUN(tap_copy(e, tb + tl.y, nxt, T * H * 4, st));
     cur = nxt;
   }
+  RUN(tap_copy(e, tl.params, params, (4 * e->cfg.layers + 1) * 16, st));
 #undef RUN
   return OMCUDA_OK;
 }
@@ -682,6 +733,22 @@ extern "C" int omcudaEncoderWait(omcudaEncoder *e) {
   }
   omcudaSynchronize(); // surfaces a bounded-wait timeout of the kernels
   return sticky_error() ? omcudaGetLastError() : OMCUDA_OK;
+}
+
+extern "C" int omcudaEncoderGetTapLayout(const omcudaEncoder *e, int64_t batch,
+    int64_t seq, omcudaEncoderTapLayout *out) {
+  if (!e || !out || batch <= 0 || seq <= 0)
+    return fail(OMCUDA_EINVAL, "EncoderGetTapLayout: bad argument");
+  tap_layout(e->cfg, batch * seq, out);
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaEncoderSetTap(omcudaEncoder *e, void *dev_buf, int64_t bytes) {
+  if (!e || (dev_buf && bytes <= 0))
+    return fail(OMCUDA_EINVAL, "EncoderSetTap: bad argument");
+  e->tap = (uint8_t *)dev_buf;
+  e->tap_bytes = dev_buf ? bytes : 0;
+  return OMCUDA_OK;
 }
 
 extern "C" void omcudaEncoderSetProfiling(omcudaEncoder *e, int on) {

@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "../common.cuh"
+#include "internal.h"
 
 extern "C" {
 long OMIsInitAccelCUDA = 0;
@@ -46,12 +47,34 @@ int g_sm_count = 0;
 std::atomic<int64_t> g_launches{0};
 
 // Caching pool.  Blocks are reused only for requests of the same rounded
-// size; everything the library launches for one calling thread goes to one
-// stream, so a freed block is safe to hand out again without an event.
+// size.  Reuse is stream-ordered: a freed block remembers the stream it was
+// last used on and an event recorded there at the time of the free.  The same
+// stream may take it again at once (its earlier work is ahead in the queue);
+// another stream gets it only after the event has completed, or is made to
+// wait for the event first.
+struct FreeBlock {
+  void *p;
+  cudaStream_t stream;
+  cudaEvent_t done; // may be null: nothing was in flight (or no stream known)
+};
 std::mutex g_pool_mutex;
-std::multimap<size_t, void *> g_free_blocks;
+std::multimap<size_t, FreeBlock> g_free_blocks;
 std::unordered_map<void *, size_t> g_live_blocks;
-std::unordered_map<void *, size_t> g_pinned;
+std::vector<cudaEvent_t> g_spare_events;
+
+cudaEvent_t take_event_locked() {
+  if (!g_spare_events.empty()) {
+    cudaEvent_t e = g_spare_events.back();
+    g_spare_events.pop_back();
+    return e;
+  }
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return e;
+}
 
 size_t round_size(size_t b) {
   if (b < 512)
@@ -78,6 +101,8 @@ int errno_for(int code) {
 
 } // namespace
 
+void pool_release_all();
+
 int fail(int code, const char *fmt, ...) {
   if (t_status.code == OMCUDA_OK) {
     t_status.code = code;
@@ -97,6 +122,35 @@ int check_cuda(cudaError_t e, const char *what) {
     return OMCUDA_OK;
   int code = (e == cudaErrorMemoryAllocation) ? OMCUDA_ENOMEM : OMCUDA_ECUDA;
   return fail(code, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int current_device_index() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  return dev;
+}
+
+namespace {
+std::mutex g_per_device_mutex;
+}
+
+int PerDeviceInt::get() {
+  const int dev = current_device_index();
+  if (dev < 0)
+    return 0;
+  std::lock_guard<std::mutex> lock(g_per_device_mutex);
+  return v[dev];
+}
+
+void PerDeviceInt::set(int x) {
+  const int dev = current_device_index();
+  if (dev < 0)
+    return;
+  std::lock_guard<std::mutex> lock(g_per_device_mutex);
+  v[dev] = x;
 }
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -147,18 +201,39 @@ cudaStream_t current_stream() {
   return g_stream;
 }
 
-void *pool_alloc(size_t bytes) {
+void *pool_alloc_on(size_t bytes, cudaStream_t st) {
   if (ensure_init() != OMCUDA_OK)
     return nullptr;
   size_t sz = round_size(bytes);
   {
     std::lock_guard<std::mutex> lock(g_pool_mutex);
-    auto it = g_free_blocks.find(sz);
-    if (it != g_free_blocks.end()) {
-      void *p = it->second;
-      g_free_blocks.erase(it);
-      g_live_blocks[p] = sz;
-      return p;
+    auto range = g_free_blocks.equal_range(sz);
+    auto pick = range.second;
+    // First choice: a block this stream freed itself, or one that is idle.
+    for (auto it = range.first; it != range.second; ++it) {
+      const FreeBlock &fb = it->second;
+      if (!fb.done || fb.stream == st || cudaEventQuery(fb.done) == cudaSuccess) {
+        pick = it;
+        break;
+      }
+    }
+    (void)cudaGetLastError(); // cudaEventQuery's cudaErrorNotReady is not an error
+    bool wait = false;
+    if (pick == range.second && range.first != range.second) {
+      pick = range.first; // busy on another stream: order this stream behind it
+      wait = true;
+    }
+    if (pick != range.second) {
+      FreeBlock fb = pick->second;
+      g_free_blocks.erase(pick);
+      if (wait && cudaStreamWaitEvent(st, fb.done, 0) != cudaSuccess) {
+        (void)cudaGetLastError();
+        cudaEventSynchronize(fb.done);
+      }
+      if (fb.done)
+        g_spare_events.push_back(fb.done);
+      g_live_blocks[fb.p] = sz;
+      return fb.p;
     }
   }
   void *p = nullptr;
@@ -166,12 +241,7 @@ void *pool_alloc(size_t bytes) {
   if (e != cudaSuccess) {
     // Give cached blocks back to the driver and try once more.
     (void)cudaGetLastError();
-    {
-      std::lock_guard<std::mutex> lock(g_pool_mutex);
-      for (auto &kv : g_free_blocks)
-        cudaFree(kv.second);
-      g_free_blocks.clear();
-    }
+    pool_release_all();
     e = cudaMalloc(&p, sz);
     if (e != cudaSuccess) {
       check_cuda(e, "cudaMalloc");
@@ -183,16 +253,30 @@ void *pool_alloc(size_t bytes) {
   return p;
 }
 
-void pool_free(void *p) {
+void *pool_alloc(size_t bytes) { return pool_alloc_on(bytes, current_stream()); }
+
+void pool_free_on(void *p, cudaStream_t st) {
   if (!p)
     return;
   std::lock_guard<std::mutex> lock(g_pool_mutex);
   auto it = g_live_blocks.find(p);
   if (it == g_live_blocks.end())
     return; // not ours
-  g_free_blocks.emplace(it->second, p);
+  FreeBlock fb{p, st, take_event_locked()};
+  if (fb.done && cudaEventRecord(fb.done, st) != cudaSuccess) {
+    (void)cudaGetLastError();
+    g_spare_events.push_back(fb.done);
+    fb.done = nullptr;
+  }
+  if (!fb.done) {
+    // No event to order a later user behind: make the block idle now.
+    cudaStreamSynchronize(st);
+  }
+  g_free_blocks.emplace(it->second, fb);
   g_live_blocks.erase(it);
 }
+
+void pool_free(void *p) { pool_free_on(p, current_stream()); }
 
 bool pool_owns(const void *p) {
   std::lock_guard<std::mutex> lock(g_pool_mutex);
@@ -201,9 +285,17 @@ bool pool_owns(const void *p) {
 
 void pool_release_all() {
   std::lock_guard<std::mutex> lock(g_pool_mutex);
-  for (auto &kv : g_free_blocks)
-    cudaFree(kv.second);
+  for (auto &kv : g_free_blocks) {
+    if (kv.second.done) {
+      cudaEventSynchronize(kv.second.done);
+      cudaEventDestroy(kv.second.done);
+    }
+    cudaFree(kv.second.p);
+  }
   g_free_blocks.clear();
+  for (cudaEvent_t e : g_spare_events)
+    cudaEventDestroy(e);
+  g_spare_events.clear();
 }
 
 } // namespace omcuda
@@ -263,6 +355,25 @@ void omcudaSetStream(void *stream) {
   } else {
     t_status.has_override = false;
   }
+}
+
+void *omcudaStreamCreate(void) {
+  if (ensure_init() != OMCUDA_OK)
+    return nullptr;
+  cudaStream_t st = nullptr;
+  if (check_cuda(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking),
+          "cudaStreamCreate") != OMCUDA_OK)
+    return nullptr;
+  return (void *)st;
+}
+
+void omcudaStreamDestroy(void *stream) {
+  if (!stream)
+    return;
+  if (t_status.has_override && t_status.stream_override == (cudaStream_t)stream)
+    t_status.has_override = false;
+  cudaStreamSynchronize((cudaStream_t)stream);
+  cudaStreamDestroy((cudaStream_t)stream);
 }
 
 void omcudaSynchronize(void) {

@@ -12,9 +12,26 @@ namespace omcuda {
 int ensure_init();
 bool sticky_error();
 cudaStream_t current_stream();
+// Device-memory pool with stream-ordered reuse.  The plain forms use the
+// calling thread's stream (omcudaGetStream); the _on forms name the stream the
+// block will be / was last used on.
 void *pool_alloc(size_t bytes);
 void pool_free(void *p);
+void *pool_alloc_on(size_t bytes, cudaStream_t st);
+void pool_free_on(void *p, cudaStream_t st);
 bool pool_owns(const void *p);
+
+// Index of the device current on the calling thread, or -1.
+constexpr int kMaxDevices = 64;
+int current_device_index();
+// A value a kernel's launcher computes once per device (launch attributes
+// set, cluster occupancy); 0 means "not yet".  Safe to use from several host
+// threads and with several devices in one process.
+struct PerDeviceInt {
+  int v[kMaxDevices] = {0};
+  int get();
+  void set(int x);
+};
 
 // dql.cu
 int launch_quantize_with_params(const float *x, int64_t n, uint8_t *y,

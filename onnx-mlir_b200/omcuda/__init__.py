@@ -102,6 +102,8 @@ def lib():
         L.omcudaDeviceAlloc.argtypes = [i64]
         L.omcudaDeviceFree.argtypes = [vp]
         L.omcudaGetStream.restype = vp
+        L.omcudaStreamCreate.restype = vp
+        L.omcudaStreamDestroy.argtypes = [vp]
         L.omcudaSetStream.argtypes = [vp]
         L.omcudaRegisterConstant.argtypes = [vp]
         L.omcudaLaunchCount.restype = i64
@@ -293,7 +295,13 @@ def _matmul_shape(a_shape, b_shape):
         return tuple(a_shape[:-1])
     if len(a_shape) == 1:
         return tuple(b_shape[:-2]) + (b_shape[-1],)
-    return tuple(a_shape[:-1]) + (b_shape[-1],)
+    if len(b_shape) <= 2:
+        return tuple(a_shape[:-1]) + (b_shape[-1],)
+    try:
+        batch = np.broadcast_shapes(tuple(a_shape[:-2]), tuple(b_shape[:-2]))
+    except ValueError:  # let the library report the mismatch
+        batch = tuple(a_shape[:-2])
+    return tuple(batch) + (a_shape[-2], b_shape[-1])
 
 
 def matmul_integer(A, B, a_zp=None, b_zp=None, device=False):
@@ -507,6 +515,56 @@ class Encoder:
         if rc != 0:
             check()
             raise OmcudaError(rc, "omcudaEncoderRunDev failed")
+
+    def run_tapped(self, x):
+        """Runs numpy x [B,S,H] with the parity-test tap on (omcudaEncoderSetTap)
+        and returns (y, taps): taps[l] maps x, xq_x, ctx, xq_ctx, h1, xq_h1, f,
+        xq_f, y to numpy arrays of layer l, and taps[l]["sites"] lists, for the
+        four quantize sites x, ctx, h1, f, the (scale, zero point) the library
+        derived, as (np.float32, np.uint8)."""
+        L = lib()
+        L.omcudaEncoderGetTapLayout.argtypes = [ctypes.c_void_p, ctypes.c_int64,
+                                                ctypes.c_int64, ctypes.c_void_p]
+        L.omcudaEncoderSetTap.argtypes = [ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_int64]
+        x = _c(x, np.float32)
+        B, S, H = x.shape
+        lay = (ctypes.c_int64 * 12)()
+        rc = L.omcudaEncoderGetTapLayout(self.handle, B, S, lay)
+        if rc != 0:
+            check()
+        names = ("x", "xq_x", "ctx", "xq_ctx", "h1", "xq_h1", "f", "xq_f", "y")
+        off = dict(zip(names, lay[:9]))
+        stride, p_off, total = lay[9], lay[10], lay[11]
+        buf = Tensor.device_empty((total,), np.uint8)
+        rc = L.omcudaEncoderSetTap(self.handle, buf.data_ptr, total)
+        if rc != 0:
+            check()
+        try:
+            y = self.run(x)
+        finally:
+            L.omcudaEncoderSetTap(self.handle, None, 0)
+        raw = buf.numpy()
+        buf.free()
+        T = B * S
+        nl = (p_off // stride) if stride else 0
+        F = (off["xq_f"] - off["f"]) // (4 * T)
+        params = raw[p_off:p_off + (4 * nl + 1) * 16]
+        taps = []
+        for l in range(nl):
+            d = {}
+            for n in names:
+                cols = F if n in ("f", "xq_f") else H
+                dt, esz = (np.uint8, 1) if n.startswith("xq") else (np.float32, 4)
+                a = l * stride + off[n]
+                d[n] = raw[a:a + T * cols * esz].view(dt).reshape(T, cols)
+            sites = []
+            for k in range(4):
+                slot = params[(4 * l + k) * 16:(4 * l + k + 1) * 16]
+                sites.append((slot[8:12].view(np.float32)[0], slot[12]))
+            d["sites"] = sites
+            taps.append(d)
+        return y, taps
 
     def set_profiling(self, on):
         lib().omcudaEncoderSetProfiling.argtypes = [ctypes.c_void_p, ctypes.c_int]

@@ -75,6 +75,9 @@ def _bind():
     L.omcudaDevAttentionBf16Supported.argtypes = [_i64] * 6
     L.omcudaDevAttentionBf16.argtypes = [_vp, _vp] + [_i64] * 8 + [
         ctypes.c_float, _vp, _i64, _vp, _vp]
+    L.omcudaDevSetWaitLimitNs.argtypes = [_i64]
+    L.omcudaDevSetWaitLimitNs.restype = None
+    L.omcudaDevSelfTestBoundedWait.argtypes = [_vp, _vp]
     _bound = True
     return L
 
@@ -163,3 +166,13 @@ def attention_bf16(hi, lo, ld_planes, q_col, k_col, v_col, B, S, heads, dh, scal
     _ok(_bind().omcudaDevAttentionBf16(hi, lo, ld_planes, q_col, k_col, v_col, B,
                                        S, heads, dh, scale, out, ld_out,
                                        out_range, stream))
+
+
+def set_wait_limit_ns(ns):
+    """Limit of every device-side wait of the tensor-core kernels (0: default)."""
+    _bind().omcudaDevSetWaitLimitNs(int(ns))
+
+
+def selftest_bounded_wait(waited_ns, stream):
+    """Launches the one-CTA kernel that waits on a barrier nothing signals."""
+    _ok(_bind().omcudaDevSelfTestBoundedWait(waited_ns, stream))

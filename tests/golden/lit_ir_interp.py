@@ -9,6 +9,14 @@ op sequence rather than from this repository's reading of it.  Used only by
 make_lit_ir_golden.py to (re)generate fixtures; the test-suite reads the
 fixtures, not the reference tree.
 
+The fp32 ops of the encoder graphs (Softmax, MatMul, Gelu, LayerNormalization)
+are covered the same way; their IR adds math.{exp,erf,sqrt} (evaluated with
+the host libm's expf / erff, which is what a compiled model calls,
+src/Conversion/KrnlToLLVM/KrnlUnaryMath.cpp:39-45), the vector dialect ops the
+SIMD lowering of LayerNormalization uses (vector.{load,store,shuffle,
+broadcast}, dense vector constants), scf.for, memref.{load,store} and
+krnl.block (loop tiling).
+
 Supported: krnl.global (dense constants), arith.{constant,addf,subf,mulf,divf,minnumf,maxnumf,cmpf,select,
 addi,subi,muli,extsi,extui,trunci,sitofp,uitofp,fptosi,fptoui}, math.floor,
 builtin.unrealized_conversion_cast, memref.{alloc,dim,reshape,reinterpret_cast}, affine.apply
@@ -17,9 +25,23 @@ and without iter_args),get_induction_var_value,load,store,memset,yield}.
 fp32 arithmetic is done with numpy float32 scalars (one rounding per op);
 integers wrap to their bit width.
 """
+import ctypes
+import ctypes.util
 import re
 
 import numpy as np
+
+_libm = ctypes.CDLL(ctypes.util.find_library("m"))
+for _f in ("expf", "erff"):
+    getattr(_libm, _f).restype = ctypes.c_float
+    getattr(_libm, _f).argtypes = [ctypes.c_float]
+
+
+def _libm_map(fn, x):
+    """Applies a libm float function to a float32 scalar or vector."""
+    if np.ndim(x) == 0:
+        return np.float32(fn(float(x)))
+    return np.array([fn(float(v)) for v in x], np.float32)
 
 _NP = {"f32": np.float32, "i8": np.int8, "ui8": np.uint8, "i16": np.int16,
        "i32": np.int32, "ui32": np.uint32, "i64": np.int64, "index": np.int64}
@@ -48,10 +70,11 @@ def extract_functions(text):
         if mm:
             maps[mm.group(1)] = mm.group(2)
             continue
-        lab = re.match(r"\s*func\.func @(\w+)", line)
+        lab = re.match(r"\s*func\.func (?:private )?@(\w+)", line)
         if lab:
             cur = lab.group(1)
-            funcs[cur] = {"stmts": [], "maps": dict(maps), "params": [], "results": []}
+            funcs[cur] = {"stmts": [], "maps": dict(maps), "params": [], "results": [],
+                          "param_names": []}
             continue
         if cur is None:
             continue
@@ -59,6 +82,7 @@ def extract_functions(text):
             sig, res = norm.rsplit("->", 1)
             mt = r"memref<((?:[\d?]+x)*)(\w+)>"
             funcs[cur]["params"] = [(a.rstrip("x"), b) for a, b in re.findall(mt, sig)]
+            funcs[cur]["param_names"] = re.findall(r"(%\w+)\s*:\s*memref<", sig)
             funcs[cur]["results"] = [(a.rstrip("x"), b) for a, b in re.findall(mt, res)]
             continue
         funcs[cur]["stmts"].append(norm)
@@ -81,6 +105,7 @@ class Interp:
         self.env = {}
         self.loop_bounds = {}
         self.loop_iv = {}
+        self.blocks = {}   # tile loop -> (parent loop, tile size)
 
     # ---- values ---------------------------------------------------------
     def val(self, tok):
@@ -101,10 +126,11 @@ class Interp:
         return v
 
     # ---- execution --------------------------------------------------------
-    def run(self, params):
-        """params: list of numpy arrays bound to %PARAM_0_, %PARAM_1_, ..."""
+    def run(self, params, names=None):
+        """params: list of numpy arrays bound to the signature's names (or to
+        %PARAM_0_, %PARAM_1_, ... when no names are given)."""
         for i, a in enumerate(params):
-            self.env["%%PARAM_%d_" % i] = a
+            self.env[names[i] if names else "%%PARAM_%d_" % i] = a
         self.result = None
         self.block(0, len(self.stmts))
         return self.result
@@ -126,15 +152,29 @@ class Interp:
         yielded = None
         while i < hi:
             s = self.stmts[i]
+            if "krnl.iterate() with ()" in s and s.endswith("{"):
+                end = self.find_end(i)      # a loop nest of depth 0: run the body once
+                self.block(i + 1, end)
+                i = end + 1
+                continue
             if "krnl.iterate(" in s and s.endswith("{"):
                 end = self.find_end(i)
                 self.iterate(s, i + 1, end)
                 i = end + 1
                 continue
+            if s.startswith("scf.for") and s.endswith("{"):
+                end = self.find_end(i)
+                m = re.match(r"scf\.for (%\w+) = (%?\w+) to (%?\w+) step (%?\w+)", s)
+                for v in range(int(self.val(m.group(2))), int(self.val(m.group(3))),
+                               int(self.val(m.group(4)))):
+                    self.env[m.group(1)] = v
+                    self.block(i + 1, end)
+                i = end + 1
+                continue
             if s.startswith("krnl.yield"):
                 yielded = self.val(s.split()[1])
-            elif s.startswith("return"):
-                names = [t.strip() for t in s[len("return"):].split(":")[0].split(",")]
+            elif s.startswith("return") or s.startswith("onnx.Return"):
+                names = [t.strip() for t in s.split(None, 1)[1].split(":")[0].split(",")]
                 self.result = names
             elif s not in ("}", ""):
                 self.stmt(s)
@@ -165,8 +205,10 @@ class Interp:
         acc_name, acc = (ia.group(1), self.val(ia.group(2))) if ia else (None, None)
         ranges = []
         for L in loops:
-            a, b = self.loop_bounds[L]
-            ranges.append((L, int(self.bound(a)), int(self.bound(b))))
+            # a tile loop made by krnl.block walks its parent's range in steps
+            parent, step = self.blocks.get(L, (L, 1))
+            a, b = self.loop_bounds[parent]
+            ranges.append((L, int(self.bound(a)), int(self.bound(b)), step))
 
         def rec(k):
             nonlocal acc
@@ -177,8 +219,8 @@ class Interp:
                 if acc_name:
                     acc = y
                 return
-            L, a, b = ranges[k]
-            for v in range(a, b):
+            L, a, b, step = ranges[k]
+            for v in range(a, b, step):
                 self.loop_iv[L] = v
                 rec(k + 1)
         rec(0)
@@ -202,9 +244,15 @@ class Interp:
         idx = tuple(int(self.val(t)) for t in inner.split(",") if t.strip())
         return name, idx
 
+    def flat_at(self, name, idx):
+        """(flat view of the buffer, flat offset of idx): vector accesses start
+        at an element and run along the innermost dimension."""
+        a = self.env[name]
+        return a.reshape(-1), int(np.ravel_multi_index(idx, a.shape)) if idx else 0
+
     def stmt(self, s):
-        if s.startswith("krnl.store"):
-            m = re.match(r"krnl\.store (%\w+), (.+?) : memref", s)
+        if s.startswith("krnl.store") or s.startswith("memref.store"):
+            m = re.match(r"(?:krnl|memref)\.store (%\w+), (.+?) : memref", s)
             name, idx = self.memref_index(m.group(2))
             self.env[name][idx] = self.val(m.group(1))
             return
@@ -212,6 +260,16 @@ class Interp:
             m = re.match(r"affine\.store (%\w+), (.+?) : memref", s)
             name, idx = self.memref_index(m.group(2))
             self.env[name][idx] = self.val(m.group(1))
+            return
+        if s.startswith("vector.store"):
+            m = re.match(r"vector\.store (%\w+), (.+?) : memref<[^>]*>, vector<(\d+)x", s)
+            name, idx = self.memref_index(m.group(2))
+            flat, at = self.flat_at(name, idx)
+            flat[at:at + int(m.group(3))] = self.val(m.group(1))
+            return
+        mb = re.match(r"(%\w+), (%\w+) = krnl\.block (%\w+(?:#\d+)?) (\d+)", s)
+        if mb:
+            self.blocks[mb.group(1)] = (mb.group(3), int(mb.group(4)))
             return
         if s.startswith("krnl.memset"):
             m = re.match(r"krnl\.memset (%\w+), (%\w+)", s)
@@ -240,6 +298,10 @@ class Interp:
             return
         ty = rhs.rsplit(":", 1)[1].strip() if ":" in rhs else ""
         args = rhs[rhs.index(op) + len(op):].lstrip('"').rsplit(":", 1)[0]
+        if op == "arith.constant" and "dense<" in rhs:
+            g = re.search(r"dense<(.+?)> : vector<(\d+)xf32>", rhs)
+            self.env[dst] = np.full(int(g.group(2)), np.float32(float(g.group(1))), np.float32)
+            return
         if op == "arith.constant":
             lit, cty = rhs[rhs.index(op) + len(op):].rsplit(":", 1)
             lit, cty = lit.strip(), cty.strip()
@@ -265,7 +327,9 @@ class Interp:
             return
         if op == "memref.reshape":
             src = re.match(r"\s*(%\w+)", args).group(1)
-            self.env[dst] = self.env[src].reshape(-1)   # flat view of the same buffer
+            to = re.search(r"->\s*memref<((?:\d+x)+)\w+>\s*$", rhs)
+            shape = [int(d) for d in to.group(1).split("x") if d] if to else [-1]
+            self.env[dst] = self.env[src].reshape(shape)   # a view of the same buffer
             return
         if op == "memref.reinterpret_cast":
             src = re.match(r"\s*(%\w+)", args).group(1)
@@ -278,7 +342,22 @@ class Interp:
             syms = [self.val(t) for t in (m2.group(3) or "").split(",") if t.strip()]
             self.env[dst] = self.apply_map(m2.group(1), dims, syms)
             return
-        if op == "krnl.load":
+        if op == "vector.load":
+            m2 = re.match(r"(.+?) : memref<[^>]*>, vector<(\d+)x", rhs[rhs.index(op) + len(op):])
+            name, idx = self.memref_index(m2.group(1).strip())
+            flat, at = self.flat_at(name, idx)
+            self.env[dst] = flat[at:at + int(m2.group(2))].copy()
+            return
+        if op == "vector.shuffle":
+            m2 = re.match(r"\s*(%\w+), (%\w+) \[([\d, ]+)\]", rhs[rhs.index(op) + len(op):])
+            both = np.concatenate([self.val(m2.group(1)), self.val(m2.group(2))])
+            self.env[dst] = both[[int(t) for t in m2.group(3).split(",")]].astype(np.float32)
+            return
+        if op == "vector.broadcast":
+            m2 = re.match(r"\s*(%\w+) : f32 to vector<(\d+)xf32>", rhs[rhs.index(op) + len(op):])
+            self.env[dst] = np.full(int(m2.group(2)), np.float32(self.val(m2.group(1))), np.float32)
+            return
+        if op in ("krnl.load", "memref.load"):
             name, idx = self.memref_index(args.strip())
             v = self.env[name][idx]
             self.env[dst] = np.float32(v) if self.env[name].dtype == np.float32 else int(v)
@@ -294,6 +373,12 @@ class Interp:
             x, y = f32(self.val(a[0])), f32(self.val(a[1]))
             fn = np.fmin if op.endswith("minnumf") else np.fmax   # NaN-ignoring
             self.env[dst] = f32(fn(x, y))
+        elif op == "math.exp":
+            self.env[dst] = _libm_map(_libm.expf, f32(self.val(a[0])))
+        elif op == "math.erf":
+            self.env[dst] = _libm_map(_libm.erff, f32(self.val(a[0])))
+        elif op == "math.sqrt":
+            self.env[dst] = f32(np.sqrt(f32(self.val(a[0]))))
         elif op == "math.floor":
             self.env[dst] = f32(np.floor(f32(self.val(a[0]))))
         elif op == "arith.cmpf":
@@ -333,7 +418,7 @@ class Interp:
             raise NotImplementedError(op + " in: " + s)
 
 
-def run_lit_function(stmts, params, maps=None):
+def run_lit_function(stmts, params, maps=None, param_names=None):
     it = Interp(stmts, maps)
-    names = it.run(params)
+    names = it.run(params, param_names)
     return it, names

@@ -87,3 +87,87 @@ def assert_same(got, want):
         g = np.asarray(g)
         assert g.dtype == w.dtype, (g.dtype, w.dtype)
         assert g.reshape(-1).tobytes() == w.reshape(-1).tobytes(), (g.reshape(-1)[:8], w.reshape(-1)[:8])
+
+
+# ---- fp32 ops of the encoder graphs (tests/golden/lit_ir_golden_fp32.json) ----------
+
+import base64  # noqa: E402
+
+FP32_CASES = json.load(open(os.path.join(HERE, "golden", "lit_ir_golden_fp32.json")))["cases"]
+
+
+def _f32(t):
+    return np.frombuffer(base64.b64decode(t["f32_le_b64"]), "<f4").reshape(t["shape"]).copy()
+
+
+def fp32_case_id(c):
+    return c["function"]
+
+
+def run_fp32_case(c, backend):
+    """backend: object with softmax (last axis), matmul_f32 (numpy matmul
+    broadcasting), gelu and layernorm (last axis, [C] parameters, epsilon).
+    Returns (got, want, kind) with kind in softmax / matmul / gelu / layernorm;
+    for gelu also the input (its bound depends on it)."""
+    ins = [_f32(t) for t in c["inputs"]]
+    want = _f32(c["outputs"][0])
+    fn = c["function"]
+    if fn == "test_softmax_v13":          # axis = 1 of [10,20,30]
+        x = np.ascontiguousarray(ins[0].transpose(0, 2, 1))
+        return backend.softmax(x).transpose(0, 2, 1), want, "softmax", None
+    if fn == "test_softmax_v11":          # opset 11: axis = 1 coerces to [10, 600]
+        return backend.softmax(ins[0].reshape(10, 600)).reshape(want.shape), want, "softmax", None
+    if fn.startswith("test_matmul"):
+        return backend.matmul_f32(ins[0], ins[1]).reshape(want.shape), want, "matmul", None
+    if fn == "test_gelu_none":
+        return backend.gelu(ins[0]), want, "gelu", ins[0]
+    if fn.startswith("layernorm"):        # axis = -2 of [2,64,31,3]: rows of 93
+        x = ins[0].reshape(128, 93)
+        got = backend.layernorm(x, ins[1].reshape(-1), ins[2].reshape(-1), 9.99999974e-6)
+        return got.reshape(want.shape), want, "layernorm", None
+    raise KeyError(fn)
+
+
+class OracleFp32Backend:
+    def __init__(self, orc):
+        self.o = orc
+
+    def softmax(self, x):
+        return self.o.softmax(x)
+
+    def matmul_f32(self, a, b):
+        a1, b1 = a.ndim == 1, b.ndim == 1
+        a2 = a[None, :] if a1 else a
+        b2 = b[:, None] if b1 else b
+        bs = np.broadcast_shapes(a2.shape[:-2], b2.shape[:-2])
+        ab = np.ascontiguousarray(np.broadcast_to(a2, bs + a2.shape[-2:]))
+        bb = np.ascontiguousarray(np.broadcast_to(b2, bs + b2.shape[-2:]))
+        out = self.o.matmul_f32(ab, bb)
+        if a1:
+            out = out[..., 0, :]
+        if b1:
+            out = out[..., 0]
+        return out
+
+    def gelu(self, x):
+        return self.o.gelu(x)
+
+    def layernorm(self, x, g, b, eps):
+        return self.o.layernorm(x, g, b, eps)
+
+
+class GpuFp32Backend:
+    def __init__(self, m):
+        self.m = m
+
+    def softmax(self, x):
+        return self.m.softmax(x)
+
+    def matmul_f32(self, a, b):
+        return self.m.matmul_f32(a, b)
+
+    def gelu(self, x):
+        return self.m.gelu(x)
+
+    def layernorm(self, x, g, b, eps):
+        return self.m.layer_normalization(x, g, b, epsilon=eps)

@@ -31,10 +31,42 @@ def test_pointwise(gpu, orc):
     rng = np.random.default_rng(3)
     x = rng.normal(0, 2, size=(33, 257)).astype(np.float32)
     y = rng.normal(0, 2, size=(33, 257)).astype(np.float32)
-    close(gpu.gelu(x), orc.gelu(x), 1e-5, 1e-6)
+    close(gpu.gelu(x), orc.gelu(x), 1e-5, 1e-7)
     assert gpu.add(x, y).tobytes() == (x + y).tobytes()
     t = rng.normal(size=(2, 5, 3, 16)).astype(np.float32)
     assert np.array_equal(gpu.transpose_0213(t), orc.transpose_0213(t))
+
+
+def test_gelu_dense_sweep_relative_bound(gpu, orc):
+    # 2 M points over [-8, 8].  The documented bound of omcudaGelu against the
+    # reference's 0.5 x (1 + erff(x / sqrt 2)): 4e-6 relative and no absolute
+    # term for x >= 0; for x < 0 additionally one rounding step of the
+    # reference's own `1 + erff` (erff is rounded to fp32 before the add, which
+    # quantizes the reference's result to multiples of 0.5 |x| 2^-24 -- the
+    # library evaluates 0.5 x erfc(-x / sqrt 2) without that cancellation).
+    x = np.linspace(-8.0, 8.0, 2 * 1024 * 1024 + 1).astype(np.float32)
+    got, want = gpu.gelu(x).astype(np.float64), orc.gelu(x).astype(np.float64)
+    x64 = x.astype(np.float64)
+    err = np.abs(got - want)
+    step = 0.5 * np.abs(x64) * 2.0 ** -24
+    bound = 4e-6 * np.abs(want) + np.where(x < 0, step, 0.0)
+    assert (err <= bound).all(), (x[np.argmax(err - bound)], (err / np.maximum(bound, 1e-300)).max())
+    # purely relative, atol = 0, wherever the reference's quantization step is
+    # below 1e-5 of its result (x >= -2.9), zero excluded
+    sel = (x >= -2.9) & (want != 0)
+    rel = err[sel] / np.abs(want[sel])
+    assert rel.max() <= 1e-5, rel.max()
+    # beyond x = -5.7 the reference is exactly -0; the library stays within
+    # half a step of it
+    far = x < -5.7
+    assert (want[far] == 0).all() and (err[far] <= step[far]).all()
+    print("\ngelu: max relative error for x >= -2.9: %.3g; max error / bound: %.3g"
+          % (rel.max(), (err / np.maximum(bound, 1e-300)).max()))
+    # special values
+    sp = np.array([0.0, -0.0, np.inf, np.nan, 1e30, -1e30], np.float32)
+    g = gpu.gelu(sp)
+    assert g[0] == 0 and g[1] == 0 and g[2] == np.inf and np.isnan(g[3])
+    assert g[4] == np.float32(1e30) and abs(g[5]) < 1e-7
 
 
 def test_matmul_f32(gpu, orc):
@@ -53,6 +85,30 @@ def test_attention(gpu, orc, B, S, heads, dh):
     q, k, v = (rng.normal(size=(B, S, heads * dh)).astype(np.float32) for _ in range(3))
     scale = 1.0 / np.sqrt(dh)
     close(gpu.attention(q, k, v, heads, scale), orc.attention(q, k, v, heads, scale), 1e-3, 1e-5)
+
+
+def test_attention_non_positive_scale(gpu, orc):
+    # The graph's Mul constant may be any float.  The tensor-core kernel folds
+    # the scale into the row maximum, which is only valid for a positive scale;
+    # omcudaAttention sends every other value to the fp32 kernels (which scale
+    # before taking the maximum), and the device-pointer entry of the
+    # tensor-core kernel refuses it.
+    from omcuda import dev
+    rng = np.random.default_rng(19)
+    B, S, heads, dh = 1, 128, 2, 64
+    q, k, v = (rng.normal(size=(B, S, heads * dh)).astype(np.float32) for _ in range(3))
+    for scale in (-0.125, 0.0):
+        close(gpu.attention(q, k, v, heads, scale), orc.attention(q, k, v, heads, scale),
+              1e-3, 1e-5)
+    planes = gpu.Tensor.device_empty((2, B * S, 3 * heads * dh), np.uint16)
+    out = gpu.Tensor.device_empty((B * S, heads * dh), np.float32)
+    H = heads * dh
+    for bad in (-0.125, 0.0, float("nan"), float("inf")):
+        with pytest.raises(gpu.OmcudaError) as ei:
+            dev.attention_bf16(planes.data_ptr, planes.data_ptr + 2 * B * S * 3 * H, 3 * H,
+                               0, H, 2 * H, B, S, heads, dh, bad, out.data_ptr, H, None,
+                               gpu.lib().omcudaGetStream())
+        assert ei.value.code == gpu.EINVAL
 
 
 @pytest.mark.parametrize("scales", [(0.1, 4.0, 0.1, 12.0), (6.0, 0.2, 0.2, 0.2),

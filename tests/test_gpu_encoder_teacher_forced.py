@@ -1,0 +1,115 @@
+"""Teacher-forced parity of the encoder configurations at their configured
+sizes: BERT-base shape whole (batch 32 x 128 tokens, 12 layers) and a
+2-sequence slice of the BERT-large shape through all 24 layers.
+
+The free-running comparison of two encoders can only be statistical: a
+one-ulp difference after a reordered reduction can move one activation across
+a rounding boundary of the next DynamicQuantizeLinear.  Here every op is
+instead checked on the library's OWN input of that op (copied out of the run
+by omcudaEncoderSetTap), so the bound of the path's contract holds element by
+element:
+
+  * every DynamicQuantizeLinear of the graph (four per layer): the oracle's
+    uint8 tensor, scale and zero point for the tapped input must equal the
+    library's bit for bit;
+  * attention, LayerNorm (reordered fp32 reductions) and the linears in front
+    of them: |got - want| <= 1e-3 * (|want| + rms(want)) per element;
+  * Gelu of the FFN-up linear: the Gelu contract of omcuda.h, 4e-6 relative
+    plus, for negative arguments, one rounding step of the reference's own
+    1 + erf;
+  * one oracle layer fed the library's layer input (three quantizations lie
+    between input and output, so activations next to a rounding boundary may
+    land one step apart in the two implementations and move the rows they
+    feed): the same 1e-3 bound on at least 95 % of the elements and a worst
+    deviation below 5e-2; the observed figures are printed.
+"""
+import numpy as np
+import pytest
+
+from omcuda.synthetic import make_encoder
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, want, rtol=1e-3):
+    want64 = want.astype(np.float64)
+    tol = rtol * (np.abs(want64) + np.sqrt((want64 ** 2).mean()))
+    err = np.abs(got.astype(np.float64) - want64)
+    return err <= tol, float((err / tol).max())
+
+
+def gelu_close(got, want, pre):
+    """Bound of omcudaGelu: 4e-6 relative; for x < 0 also half a unit in the
+    last place of erf near 1, scaled by 0.5 |x| (the reference rounds erff to
+    fp32 before adding 1)."""
+    tol = 4e-6 * np.abs(want.astype(np.float64)) + \
+        np.where(pre < 0, 0.5 * np.abs(pre.astype(np.float64)) * 2.0 ** -24, 0.0)
+    return np.abs(got.astype(np.float64) - want.astype(np.float64)) <= tol
+
+
+def check_site(orc, x, xq_gpu, site, what):
+    xq, s, z = orc.dynamic_quantize_linear(x)
+    assert s.tobytes() == np.float32(site[0]).tobytes(), (what, s, site)
+    assert int(z) == int(site[1]), (what, z, site)
+    assert np.array_equal(xq, xq_gpu), what
+
+
+@pytest.mark.parametrize("name,B,S,H,heads,F,nl", [
+    ("bert_base_whole", 32, 128, 768, 12, 3072, 12),
+    ("bert_large_two_sequences", 2, 512, 1024, 16, 4096, 24),
+])
+def test_teacher_forced_against_oracle(gpu, orc, name, B, S, H, heads, F, nl):
+    layers = make_encoder(31, H, F, nl)
+    x = np.random.default_rng(32).normal(size=(B, S, H)).astype(np.float32)
+    enc = gpu.Encoder(H, heads, F, layers)
+    y, taps = enc.run_tapped(x)
+    # the tap changes nothing
+    assert np.array_equal(enc.run(x), y)
+    enc.close()
+    assert np.array_equal(taps[0]["x"], x.reshape(B * S, H))
+    assert np.array_equal(taps[-1]["y"], y.reshape(B * S, H))
+    scale = np.float32(1.0) / np.sqrt(np.float32(H // heads))
+    worst = {"ctx": 0.0, "h1": 0.0, "y": 0.0, "layer": 0.0}
+    frac_bad_layer = 0.0
+    for l, (w, t) in enumerate(zip(layers, taps)):
+        if l > 0:
+            assert np.array_equal(t["x"], taps[l - 1]["y"])
+        lin = lambda a, wn, bn, i: orc.dyn_quant_linear(a, w[wn], w["sc"][i], w[bn])["Y"]
+        # -- the four DynamicQuantizeLinear sites: bit-exact
+        check_site(orc, t["x"], t["xq_x"], t["sites"][0], (name, l, "x"))
+        check_site(orc, t["ctx"], t["xq_ctx"], t["sites"][1], (name, l, "ctx"))
+        check_site(orc, t["h1"], t["xq_h1"], t["sites"][2], (name, l, "h1"))
+        check_site(orc, t["f"], t["xq_f"], t["sites"][3], (name, l, "f"))
+        # -- QKV linears + attention on the tapped layer input
+        q, k, v = lin(t["x"], "wq", "bq", 0), lin(t["x"], "wk", "bk", 1), lin(t["x"], "wv", "bv", 2)
+        ctx = orc.attention(q.reshape(B, S, H), k.reshape(B, S, H), v.reshape(B, S, H),
+                            heads, scale).reshape(B * S, H)
+        ok, r = close(t["ctx"], ctx)
+        assert ok.all(), (name, l, "ctx", r)
+        worst["ctx"] = max(worst["ctx"], r)
+        # -- output linear + residual + LayerNorm on the tapped ctx
+        a = lin(t["ctx"], "wo", "bo", 3)
+        h1 = orc.layernorm(t["x"] + a, w["ln1g"], w["ln1b"])
+        ok, r = close(t["h1"], h1)
+        assert ok.all(), (name, l, "h1", r)
+        worst["h1"] = max(worst["h1"], r)
+        # -- FFN-up linear + Gelu on the tapped h1
+        pre = lin(t["h1"], "w1", "b1", 4)
+        assert gelu_close(t["f"], orc.gelu(pre), pre).all(), (name, l, "gelu")
+        # -- FFN-down linear + residual + LayerNorm on the tapped f
+        o = lin(t["f"], "w2", "b2", 5)
+        yl = orc.layernorm(t["h1"] + o, w["ln2g"], w["ln2b"])
+        ok, r = close(t["y"], yl)
+        assert ok.all(), (name, l, "y", r)
+        worst["y"] = max(worst["y"], r)
+        # -- the whole oracle layer from the tapped layer input
+        want = orc.encoder_layer(t["x"], B, S, H, heads, F, w)
+        ok, r = close(t["y"], want)
+        frac_bad_layer = max(frac_bad_layer, 1.0 - ok.mean())
+        worst["layer"] = max(worst["layer"], float(np.abs(t["y"] - want).max()))
+        assert ok.mean() >= 0.95, (name, l, "layer", 1.0 - ok.mean())
+        assert np.abs(t["y"] - want).max() < 5e-2, (name, l, "layer")
+    print("\n%s: worst error / tolerance ctx %.3g, h1 %.3g, y %.3g; whole layer: "
+          "worst |err| %.3g, at most %.3g of a layer's elements beyond 1e-3"
+          % (name, worst["ctx"], worst["h1"], worst["y"], worst["layer"],
+             frac_bad_layer))

@@ -31,12 +31,6 @@ def rand8(rng, shape, dt):
 def test_lit_vectors(gpu, kat):
     A, B = arr(kat["A"]), arr(kat["B"])
     want = arr(kat["expected"])
-    broadcast_batch = B.ndim > 2 and (A.ndim != B.ndim or A.shape[:-2] != B.shape[:-2])
-    if broadcast_batch or A.ndim == 1 and B.ndim > 2:
-        with pytest.raises(gpu.OmcudaError) as ei:
-            gpu.matmul_integer(A, B, arr(kat["a_zero_point"]), arr(kat["b_zero_point"]))
-        assert ei.value.code in (gpu.ENOTSUP, gpu.EINVAL)
-        return
     got = gpu.matmul_integer(A, B, arr(kat["a_zero_point"]), arr(kat["b_zero_point"]))
     assert np.array_equal(got.reshape(want.shape), want)
 
@@ -91,6 +85,20 @@ def test_matmul_integer_api_shapes(gpu, orc):
     # vector operands
     a, b = rand8(rng, 32, np.uint8), rand8(rng, (32, 9), np.int8)
     assert np.array_equal(gpu.matmul_integer(a, b), orc.matmul_integer(a, b))
+    # numpy broadcasting of the batch dimensions (ONNXOps/Math/MatMul.cpp:46-166):
+    # size-1 and missing dimensions on either side, a vector against a batch
+    for sa, sb in (((4, 1, 5, 16), (3, 16, 7)), ((3, 5, 16), (2, 1, 16, 7)),
+                   ((16,), (2, 3, 16, 7)), ((2, 3, 5, 16), (16,)),
+                   ((1, 5, 16), (6, 16, 7)), ((2, 3, 5, 16), (2, 3, 16, 7))):
+        A, B = rand8(rng, sa, np.uint8), rand8(rng, sb, np.int8)
+        az, bz = np.array(9, np.uint8), np.array(-3, np.int8)
+        want = orc.matmul_integer(A, B, az, bz)
+        got = gpu.matmul_integer(A, B, az, bz)
+        assert got.shape == want.shape and np.array_equal(got, want), (sa, sb)
+        assert np.array_equal(gpu.matmul_integer(A, B, az, bz, device=True).numpy(), want)
+    with pytest.raises(gpu.OmcudaError) as ei:
+        gpu.matmul_integer(rand8(rng, (2, 5, 16), np.uint8), rand8(rng, (3, 16, 7), np.int8))
+    assert ei.value.code == gpu.EINVAL
     # per-row a zero point, per-column b zero point
     A, B = rand8(rng, (21, 32), np.uint8), rand8(rng, (32, 9), np.uint8)
     az, bz = rand8(rng, 21, np.uint8), rand8(rng, 9, np.uint8)
@@ -213,13 +221,14 @@ def test_dyn_quant_linear_forms(gpu, orc):
     assert got.tobytes() == want.tobytes()
 
 
-@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (16, 4096, 14336), (256, 14336, 4096),
-                                   (4096, 4096, 4096)])
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 14336), (14336, 4096)])
+@pytest.mark.parametrize("M", [1, 16, 256, 4096, 16384])
 def test_config3_sweep_members(gpu, orc, M, K, N):
-    # DynamicQuantizeLinear over the whole X, then sampled rows of the GEMM and
-    # of the dequantized output against the oracle.
+    # Every member of the MatMulInteger sweep: DynamicQuantizeLinear over the
+    # whole X, then sampled rows of the GEMM and of the dequantized output
+    # against the oracle.
     rng = np.random.default_rng(M + K + N)
-    X = rng.normal(size=(M, K)).astype(np.float32)
+    X = rng.standard_normal((M, K), dtype=np.float32)
     W = rng.integers(-127, 128, (K, N), dtype=np.int8)
     w_scale = np.float32(0.02 * 4 / 127)
     xq, xs, xz = orc.dynamic_quantize_linear(X)

@@ -168,3 +168,18 @@ import lit_ir_cases  # noqa: E402
 def test_oracle_matches_executed_lit_ir(orc, case):
     got, want = lit_ir_cases.run_case(case, lit_ir_cases.OracleBackend(orc))
     lit_ir_cases.assert_same(got, want)
+
+
+@pytest.mark.parametrize("case", lit_ir_cases.FP32_CASES, ids=lit_ir_cases.fp32_case_id)
+def test_oracle_fp32_ops_match_executed_lit_ir(orc, case):
+    # Softmax, MatMul and Gelu: the oracle performs the reference's fp32
+    # operations in the reference's order (and calls the same libm), so it
+    # must reproduce the executed IR bit for bit.  LayerNormalization: the
+    # reference's SIMD lowering sums in vector lanes, the oracle in order, so
+    # only the last bits of the two reductions differ.
+    got, want, kind, _ = lit_ir_cases.run_fp32_case(case, lit_ir_cases.OracleFp32Backend(orc))
+    assert got.shape == want.shape
+    if kind == "layernorm":
+        assert np.allclose(got, want, rtol=1e-5, atol=1e-5), np.abs(got - want).max()
+    else:
+        assert got.tobytes() == want.tobytes(), np.abs(got - want).max()
