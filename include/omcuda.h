@@ -122,8 +122,59 @@ void omcudaSynchronize(void);
  * omcudaForgetConstants.  Without this, B is prepared on every call. */
 void omcudaRegisterConstant(const OMTensor *t);
 void omcudaForgetConstants(void);
+/* The reference's two non-default arithmetic modes.  They are compile-time
+ * options there; the plugin passes the ones a model was compiled with once, at
+ * model initialisation.  Process wide; 0 (the default) is the arithmetic
+ * every other comment of this header describes.
+ *   OMCUDA_MODE_NO_ZERO_POINT  --disable-quantization-zero-point:
+ *       DynamicQuantizeLinear derives the scale as usual and reports zero
+ *       point 0 (src/Conversion/ONNXToKrnl/Quantization/DynamicQuantizeLinear.cpp:72-83,142),
+ *       QuantizeLinear and DequantizeLinear ignore a given zero point
+ *       (QuantizeLinear.cpp:231-237, Math/Elementwise.cpp:1453).
+ *   OMCUDA_MODE_FAST_MATH  convert-onnx-to-krnl=enable-fast-math: the
+ *       quantize step multiplies by RN(1 / scale) instead of dividing by the
+ *       scale (QuantizeLinear.cpp:43-44,117-131); results differ from the
+ *       default in rare last-place cases, exactly as the reference's do. */
+#define OMCUDA_MODE_NO_ZERO_POINT 1
+#define OMCUDA_MODE_FAST_MATH 2
+void omcudaSetQuantizationMode(int64_t flags);
+int64_t omcudaGetQuantizationMode(void);
 /* Number of kernels this library has launched in this process. */
 int64_t omcudaLaunchCount(void);
+
+/* ---------------------------------------------------------------------- */
+/* Loading compiled models and their constants                              */
+/* ---------------------------------------------------------------------- */
+
+/* What onnx-mlir's ExecutionSession gives a host program
+ * (src/Runtime/ExecutionSession.cpp:60-380), as a C API: open a compiled
+ * model, query its entry points and signatures, run it.  The tag selects the
+ * suffixed symbols a model is compiled with (run_main_graph_<tag>, ...):
+ * NULL or "" means the file name without extension in lower case, "NONE" the
+ * unsuffixed symbols.  OM_CONSTANT_PATH is set to the model's folder unless the
+ * caller set it.  Tensors are passed through untouched, so a model compiled
+ * with the CUDA accelerator can be given (and returns) device-resident
+ * tensors and models can be chained without a trip through host memory.
+ * omcudaSessionRun returns NULL with errno set when the model fails. */
+typedef struct omcudaSession omcudaSession;
+omcudaSession *omcudaSessionCreate(
+    const char *sharedLibPath, const char *tag, int defaultEntryPoint);
+const char *const *omcudaSessionQueryEntryPoints(
+    omcudaSession *s, int64_t *numOfEntryPoints);
+int omcudaSessionSetEntryPoint(omcudaSession *s, const char *entryPointName);
+const char *omcudaSessionInputSignature(omcudaSession *s);
+const char *omcudaSessionOutputSignature(omcudaSession *s);
+OMTensorList *omcudaSessionRun(omcudaSession *s, OMTensorList *inputs);
+void omcudaSessionDestroy(omcudaSession *s);
+
+/* The external-constants loader a compiled model calls for its
+ * <model>.constants.bin (replaces omLoadConstantData / omUnloadConstantData,
+ * src/Runtime/OMExternalConstant.c:57-138,176-189): the file is looked up in
+ * OM_CONSTANT_PATH and mapped read-only; constAddr[0] receives its address (a
+ * second call is a no-op).  Returns an omcudaStatus. */
+int omcudaLoadConstantData(
+    void **constAddr, const char *fname, int64_t size, int64_t isLE);
+int omcudaUnloadConstantData(void **constAddr, int64_t size);
 
 /* ---------------------------------------------------------------------- */
 /* krnl.call targets                                                        */

@@ -26,6 +26,7 @@ LIB = os.path.join(LIBDIR, "libomcuda.so")
 SOURCES = [
     "runtime/om_tensor.c",
     "runtime/context.cpp",
+    "runtime/execution_session.cpp",
     "api/krnl_call_api.cpp",
     "api/no_alloc.cu",
     "model/encoder.cpp",

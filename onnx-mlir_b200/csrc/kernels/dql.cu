@@ -15,6 +15,7 @@
 // from device memory; for tensors that fit in L2 its read of x is served from
 // there.
 #include "../common.cuh"
+#include "../runtime/internal.h"
 #include "quantize.cuh"
 
 namespace omcuda {
@@ -34,7 +35,7 @@ struct DqlScratch {
 __global__ void __launch_bounds__(kDqlThreads)
     dql_minmax_kernel(const float *__restrict__ x, int64_t n,
         DqlScratch *__restrict__ scr, float *__restrict__ y_scale,
-        uint8_t *__restrict__ y_zp) {
+        uint8_t *__restrict__ y_zp, int mode) {
   float lo = INFINITY, hi = -INFINITY;
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(kDqlThreads)
       hi = fmaxf(hi, s_hi[w]);
     }
     float s, z;
-    dql_params_from_range(lo, hi, &s, &z);
+    dql_params_from_range(lo, hi, &s, &z, mode);
     scr->params[0] = s;
     scr->params[1] = z;
     if (y_scale)
@@ -149,14 +150,14 @@ __global__ void __launch_bounds__(kDqlThreads)
     quantize_kernel(const float *__restrict__ x, int64_t n,
         uint8_t *__restrict__ y, const float *__restrict__ params,
         const float *__restrict__ scale_ptr, const void *__restrict__ zp8,
-        int has_zp, const uint32_t *__restrict__ range, QuantOutputs outs) {
+        int has_zp, const uint32_t *__restrict__ range, QuantOutputs outs, int mode) {
   float scale, zp_f;
   if (range) {
     // Scale and zero point straight from a producer's running range (every
     // thread derives the same two scalars; block 0 also publishes them for
     // the ops that follow).
     dql_params_from_range(ordered_to_f32(__ldg(range)), ordered_to_f32(__ldg(range + 1)),
-        &scale, &zp_f);
+        &scale, &zp_f, mode);
     if (blockIdx.x == 0 && threadIdx.x == 0) {
       outs.params[0] = scale;
       outs.params[1] = zp_f;
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(kDqlThreads)
     else
       zp_f = (float)*reinterpret_cast<const uint8_t *>(zp8);
   }
-  const QuantConsts qc = make_quant_consts(scale, zp_f);
+  const QuantConsts qc = make_quant_consts(scale, zp_f, mode);
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   const bool aligned = (((uintptr_t)x & 15u) == 0) && (((uintptr_t)y & 3u) == 0);
@@ -237,7 +238,7 @@ int launch_quantize_with_params(const float *x, int64_t n, uint8_t *y,
     const float *params, cudaStream_t st) {
   int grid = grid_for(n, kDqlThreads * 16);
   quantize_kernel<false><<<grid, kDqlThreads, 0, st>>>(
-      x, n, y, params, nullptr, nullptr, 1, nullptr, QuantOutputs{});
+      x, n, y, params, nullptr, nullptr, 1, nullptr, QuantOutputs{}, quant_mode());
   OMCUDA_CHECK_LAUNCH("quantize_kernel");
   return OMCUDA_OK;
 }
@@ -257,7 +258,7 @@ extern "C" int omcudaDevDynamicQuantizeLinear(const float *x, int64_t n,
   cudaStream_t st = (cudaStream_t)stream;
   DqlScratch *scr = (DqlScratch *)scratch;
   int grid = grid_for(n, kDqlThreads * 16);
-  dql_minmax_kernel<<<grid, kDqlThreads, 0, st>>>(x, n, scr, y_scale, y_zp);
+  dql_minmax_kernel<<<grid, kDqlThreads, 0, st>>>(x, n, scr, y_scale, y_zp, quant_mode());
   OMCUDA_CHECK_LAUNCH("dql_minmax_kernel");
   if (n > 0)
     return launch_quantize_with_params(x, n, y, scr->params, st);
@@ -274,7 +275,7 @@ extern "C" int omcudaDevQuantizeFromRange(const float *x, int64_t n, void *range
   int grid = grid_for(n, kDqlThreads * 16);
   QuantOutputs outs{params, y_scale, y_zp};
   quantize_kernel<false><<<grid, kDqlThreads, 0, st>>>(
-      x, n, y, nullptr, nullptr, nullptr, 1, (const uint32_t *)range, outs);
+      x, n, y, nullptr, nullptr, nullptr, 1, (const uint32_t *)range, outs, quant_mode());
   OMCUDA_CHECK_LAUNCH("quantize_kernel");
   return OMCUDA_OK;
 }
@@ -289,10 +290,12 @@ extern "C" int omcudaDevQuantizeLinear(const float *x, int64_t n, void *y,
   int grid = grid_for(n, kDqlThreads * 16);
   if (y_signed)
     quantize_kernel<true><<<grid, kDqlThreads, 0, st>>>(
-        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr, nullptr, QuantOutputs{});
+        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr, nullptr, QuantOutputs{},
+        quant_mode());
   else
     quantize_kernel<false><<<grid, kDqlThreads, 0, st>>>(
-        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr, nullptr, QuantOutputs{});
+        x, n, (uint8_t *)y, nullptr, scale, zp, zp != nullptr, nullptr, QuantOutputs{},
+        quant_mode());
   OMCUDA_CHECK_LAUNCH("quantize_kernel");
   return OMCUDA_OK;
 }
@@ -304,6 +307,8 @@ extern "C" int omcudaDevDequantizeLinear(const void *x, int dtype, int64_t n,
   if (n == 0)
     return OMCUDA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (quant_mode() & OMCUDA_MODE_NO_ZERO_POINT)
+    zp = nullptr; // the reference drops the subtraction (Math/Elementwise.cpp:1453)
   int grid = grid_for(n, 256 * 4);
   if (dtype == 0)
     dequantize_kernel<uint8_t><<<grid, 256, 0, st>>>(

@@ -59,6 +59,10 @@ struct EpiParams {
   uint8_t *q_zp;           // optional y_zero_point out
   int vec_ok;    // per-column vectors are 16-byte aligned: 128-bit loads allowed
   int line_store; // set by the tensor-core launcher: Y takes 16-byte line stores
+  // L2 eviction hints of the tensor-core kernels' TMA copies: bit 0 output
+  // stores evict_first, bit 1 A loads evict_first, bit 2 B loads evict_last.
+  int l2_hints;
+  int quant_mode; // OMCUDA_MODE_* flags for the quantizing tail
 };
 
 // Host: flattens the public argument block (gemm_simt.cu).

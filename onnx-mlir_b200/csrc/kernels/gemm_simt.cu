@@ -13,6 +13,8 @@
 // for shapes the tensor-core kernel does not take (K not a multiple of 16,
 // unaligned bases).  Integer accumulation wraps in 32 bits in any order, so
 // its results are bit-identical to the tensor-core kernel's.
+#include <cstdlib>
+
 #include "../runtime/internal.h"
 #include "gemm_epilogue.cuh"
 
@@ -187,6 +189,120 @@ __global__ void __launch_bounds__(256)
     epi_range_commit(p.out_range, lo, hi);
 }
 
+
+// ---- GEMV-shaped GEMM for M <= 16 ----------------------------------------------
+//
+// With a handful of rows the GEMM is one pass over the K*N bytes of the
+// weight: HBM bound.  A block of kGemvWarps warps owns CB adjacent output
+// columns (CB rows of Bt) and MT rows of A, and splits K between its warps:
+// chunk c (16 bytes of K) goes to thread c mod (32 * kGemvWarps), so that a
+// warp-wide load of Bt is one coalesced 512-byte access and every SM keeps
+// tens of kilobytes of weight reads in flight (CB loads per thread and trip,
+// trips unrolled by two).  A is tiny (M*K bytes) and is served by L1; loading
+// one A chunk for CB columns keeps the L1 traffic per weight byte at MT / CB.
+// The partial sums are folded with shuffles inside each warp and through
+// shared memory between the warps (no global workspace, no atomics); the
+// first MT * CB threads of the block run the epilogue.  Integer addition is
+// exact in any order, so the result equals the other kernels' bit for bit.
+constexpr int kGemvWarps = 4;
+
+template <int MT, int CB, bool kASigned, bool kBSigned>
+__global__ void __launch_bounds__(32 * kGemvWarps)
+    gemm_i8_gemv_kernel(const uint8_t *__restrict__ A,
+        const uint8_t *__restrict__ Bt, int64_t kp, EpiParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t n0 = (int64_t)blockIdx.x * CB;
+  const int64_t m0 = (int64_t)blockIdx.y * MT;
+  const bool vec_ok = ((p.K & 15) == 0) && (((uintptr_t)A & 15u) == 0);
+  int32_t acc[MT][CB];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < CB; ++j)
+      acc[i][j] = 0;
+  const uint4 *brow[CB];
+#pragma unroll
+  for (int j = 0; j < CB; ++j) // columns past N re-read the last one; never stored
+    brow[j] = reinterpret_cast<const uint4 *>(Bt + (n0 + j < p.N ? n0 + j : p.N - 1) * kp);
+  const int64_t chunks = kp >> 4;
+  constexpr int kStep = 32 * kGemvWarps;
+  auto consume = [&](int64_t c, const uint4 (&b)[CB]) {
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      const uint4 a = load_a_chunk(A, m0 + i, p.M, p.K, c << 4, vec_ok);
+#pragma unroll
+      for (int j = 0; j < CB; ++j) {
+        int32_t s = acc[i][j];
+        s = dp4a_mixed<kASigned, kBSigned>(a.x, b[j].x, s);
+        s = dp4a_mixed<kASigned, kBSigned>(a.y, b[j].y, s);
+        s = dp4a_mixed<kASigned, kBSigned>(a.z, b[j].z, s);
+        s = dp4a_mixed<kASigned, kBSigned>(a.w, b[j].w, s);
+        acc[i][j] = s;
+      }
+    }
+  };
+  int64_t c = threadIdx.x;
+  for (; c + kStep < chunks; c += 2 * kStep) {
+    uint4 b0[CB], b1[CB];
+#pragma unroll
+    for (int j = 0; j < CB; ++j) {
+      b0[j] = __ldcs(brow[j] + c);
+      b1[j] = __ldcs(brow[j] + c + kStep);
+    }
+    consume(c, b0);
+    consume(c + kStep, b1);
+  }
+  if (c < chunks) {
+    uint4 b0[CB];
+#pragma unroll
+    for (int j = 0; j < CB; ++j)
+      b0[j] = __ldcs(brow[j] + c);
+    consume(c, b0);
+  }
+  __shared__ int32_t part[kGemvWarps][MT * CB];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < CB; ++j) {
+      int32_t v = acc[i][j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0)
+        part[warp][i * CB + j] = v;
+    }
+  __syncthreads();
+  // Thread t finishes output (row m0 + t / CB, column n0 + t % CB).
+  static_assert(MT * CB <= 32, "the epilogue runs in the first warp");
+  if (warp != 0)
+    return;
+  const EpiScalars sc = epi_scalars(p);
+  float lo = INFINITY, hi = -INFINITY;
+  const int64_t m = m0 + lane / CB, n = n0 + lane % CB;
+  if (lane < MT * CB && m < p.M && n < p.N) {
+    int32_t sum = 0;
+#pragma unroll
+    for (int w = 0; w < kGemvWarps; ++w)
+      sum += part[w][lane];
+    const EpiRow row = epi_row(p, m);
+    const int32_t v = epi_int(p, row, sum, n);
+    if (p.kind == OMCUDA_EPI_I32) {
+      reinterpret_cast<int32_t *>(p.Y)[m * p.N + n] = v;
+    } else if (p.kind == OMCUDA_EPI_DEQUANT) {
+      float y = epi_dequant(p, sc, v, n);
+      if (p.residual)
+        y = __fadd_rn(y, __ldg(p.residual + m * p.N + n));
+      reinterpret_cast<float *>(p.Y)[m * p.N + n] = y;
+      lo = fminf(lo, y);
+      hi = fmaxf(hi, y);
+    } else {
+      reinterpret_cast<uint8_t *>(p.Y)[m * p.N + n] = (uint8_t)epi_requant(p, sc, v, n);
+    }
+  }
+  if (p.out_range && p.kind == OMCUDA_EPI_DEQUANT)
+    epi_range_commit(p.out_range, lo, hi);
+}
+
 EpiParams make_epi_params(const omcudaGemmArgs &a) {
   EpiParams p;
   p.M = a.M;
@@ -221,6 +337,8 @@ EpiParams make_epi_params(const omcudaGemmArgs &a) {
   p.vec_ok = ((((uintptr_t)a.B.colsum | (uintptr_t)a.bias | sb_vec) & 15u) == 0) &&
              (a.N % 4 == 0);
   p.line_store = 0;
+  p.l2_hints = 0;
+  p.quant_mode = quant_mode();
   return p;
 }
 
@@ -247,7 +365,53 @@ static void launch_warp_gemm(const omcudaGemmArgs &a, cudaStream_t st) {
   }
 }
 
+template <int MT, int CB>
+static void launch_gemv(const omcudaGemmArgs &a, cudaStream_t st) {
+  EpiParams p = make_epi_params(a);
+  dim3 grid((unsigned)ceil_div(a.N, CB), (unsigned)ceil_div(a.M, MT));
+  const uint8_t *A = (const uint8_t *)a.A;
+  const uint8_t *Bt = (const uint8_t *)a.B.bt;
+  const int threads = 32 * kGemvWarps;
+  int sel = (a.a_signed ? 2 : 0) | (a.B.b_signed ? 1 : 0);
+  switch (sel) {
+  case 0:
+    gemm_i8_gemv_kernel<MT, CB, false, false><<<grid, threads, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  case 1:
+    gemm_i8_gemv_kernel<MT, CB, false, true><<<grid, threads, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  case 2:
+    gemm_i8_gemv_kernel<MT, CB, true, false><<<grid, threads, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  default:
+    gemm_i8_gemv_kernel<MT, CB, true, true><<<grid, threads, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  }
+}
+
+// OMCUDA_GEMV=0 keeps the older warp-per-column kernel for every M, for
+// experiments.
+static bool gemv_wanted() {
+  static const bool on = [] {
+    const char *s = getenv("OMCUDA_GEMV");
+    return !(s && atoi(s) == 0);
+  }();
+  return on;
+}
+
 int launch_gemm_simt(const omcudaGemmArgs &a, cudaStream_t st) {
+  if (a.M <= 16 && gemv_wanted()) {
+    if (a.M <= 1)
+      launch_gemv<1, 2>(a, st);
+    else if (a.M <= 2)
+      launch_gemv<2, 2>(a, st);
+    else if (a.M <= 4)
+      launch_gemv<4, 4>(a, st);
+    else
+      launch_gemv<8, 4>(a, st); // 9..16 rows: two row groups share the weight through L2
+    OMCUDA_CHECK_LAUNCH("gemm_i8_gemv_kernel");
+    return OMCUDA_OK;
+  }
   if (a.M <= 1)
     launch_warp_gemm<1>(a, st);
   else if (a.M <= 4)
@@ -367,7 +531,10 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
     return fail(OMCUDA_ENOTSUP,
         "GemmI8: the split-bf16, range-only and quantizing tails exist on the "
         "tensor-core kernel only (K %% 16 == 0, 16-byte aligned A)");
+  // Up to 16 rows the GEMM is one read of the weight: the GEMV-shaped SIMT
+  // kernel streams it at HBM speed, which a 128-row tensor-core tile on a
+  // few SMs cannot.
   bool use_tc = (a.kernel_choice == 1) || tc_only ||
-                (a.kernel_choice == 0 && tc_ok && a.M > 4);
+                (a.kernel_choice == 0 && tc_ok && a.M > 16);
   return use_tc ? launch_gemm_tc(a, st) : launch_gemm_simt(a, st);
 }

@@ -293,7 +293,7 @@ __device__ __forceinline__ QuantConsts epi_quant_consts(const EpiParams &p, bool
     return QuantConsts{1.0f, 1.0f, 0.0f, true};
   float scale, zp_f;
   dql_params_from_range(ordered_to_f32(__ldg(p.q_range)),
-      ordered_to_f32(__ldg(p.q_range + 1)), &scale, &zp_f);
+      ordered_to_f32(__ldg(p.q_range + 1)), &scale, &zp_f, p.quant_mode);
   if (publish) {
     p.q_params[0] = scale;
     p.q_params[1] = zp_f;
@@ -302,7 +302,7 @@ __device__ __forceinline__ QuantConsts epi_quant_consts(const EpiParams &p, bool
     if (p.q_zp)
       *p.q_zp = (uint8_t)(unsigned int)zp_f; // fptoui; zp_f is in [0,255]
   }
-  return make_quant_consts(scale, zp_f);
+  return make_quant_consts(scale, zp_f, p.quant_mode);
 }
 
 // Drains one accumulator tile half (this warp's 32 TMEM lanes x kHalfCols
@@ -320,6 +320,8 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
     const EpiScalars &sc, const QuantConsts &qc, uint32_t taddr, int64_t m_warp,
     int64_t n0, uint32_t slab0, int lane, bool use_slab, float &lo, float &hi,
     const CUtensorMap *map_y, const CUtensorMap *map_y2, Release &&release) {
+  const bool hint_store = (p.l2_hints & 1) != 0;
+  const uint64_t pol_out = hint_store ? l2_policy_evict_first() : 0;
   // EPI_DEQUANT_SPLIT stages like the 4-byte tails (32 columns per 128-byte
   // slab row: 16 words of bf16 hi pairs, then 16 words of lo pairs).
   constexpr bool kSplit = EPI == OMCUDA_EPI_DEQUANT_SPLIT;
@@ -413,9 +415,15 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
       fence_proxy_async_smem(); // the slab was written through the generic proxy
       __syncwarp();
       if (lane == 0 && warp_in && ng < p.N) {
-        tma_store_2d(map_y, slab0, (int32_t)ng, (int32_t)m_warp);
-        if (kSplit)
-          tma_store_2d(map_y2, slab0 + 2048u, (int32_t)ng, (int32_t)m_warp);
+        if (hint_store) {
+          tma_store_2d_hint(map_y, slab0, (int32_t)ng, (int32_t)m_warp, pol_out);
+          if (kSplit)
+            tma_store_2d_hint(map_y2, slab0 + 2048u, (int32_t)ng, (int32_t)m_warp, pol_out);
+        } else {
+          tma_store_2d(map_y, slab0, (int32_t)ng, (int32_t)m_warp);
+          if (kSplit)
+            tma_store_2d(map_y2, slab0 + 2048u, (int32_t)ng, (int32_t)m_warp);
+        }
         tma_store_commit();
       }
     }
@@ -541,6 +549,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t pol_a = l2_policy_evict_first(), pol_b = l2_policy_evict_last();
       for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         const int32_t m0 = (int32_t)((t / tiles_n) * kBM);
         const int32_t n0 = (int32_t)((t % tiles_n) * BN);
@@ -553,8 +562,14 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           const uint32_t sa = smem_base + stage * Cfg::kStageBytes;
           const uint32_t sb = sa + Cfg::kABytes;
           mbar_expect_tx(full, Cfg::kStageBytes);
-          tma_load_2d(sa, &map_a, kb * kBK, m0, full);
-          tma_load_2d(sb, &map_b, kb * kBK, n0, full);
+          if (p.l2_hints & 2)
+            tma_load_2d_hint(sa, &map_a, kb * kBK, m0, full, pol_a);
+          else
+            tma_load_2d(sa, &map_a, kb * kBK, m0, full);
+          if (p.l2_hints & 4)
+            tma_load_2d_hint(sb, &map_b, kb * kBK, n0, full, pol_b);
+          else
+            tma_load_2d(sb, &map_b, kb * kBK, n0, full);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -797,6 +812,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const uint64_t pol_a = l2_policy_evict_first(), pol_b = l2_policy_evict_last();
       for (int64_t u = cluster_id; u < num_units && ok; u += num_clusters) {
         const PairUnit un = pair_unit(u, full_units);
         const int64_t t = un.tile;
@@ -816,8 +832,15 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           const uint32_t sb = sa + kABytes;
           if (rank == 0)
             mbar_expect_tx(smem_u32(&bar_full[stage]), 2 * stage_tx);
-          tma_load_2d_pair(sa, &map_a, kb * kBK, m0, full_leader);
-          tma_load_2d_pair(sb, un.narrow ? &map_b_half : &map_b, kb * kBK, n0, full_leader);
+          if (p.l2_hints & 2)
+            tma_load_2d_pair_hint(sa, &map_a, kb * kBK, m0, full_leader, pol_a);
+          else
+            tma_load_2d_pair(sa, &map_a, kb * kBK, m0, full_leader);
+          if (p.l2_hints & 4)
+            tma_load_2d_pair_hint(sb, un.narrow ? &map_b_half : &map_b, kb * kBK, n0,
+                full_leader, pol_b);
+          else
+            tma_load_2d_pair(sb, un.narrow ? &map_b_half : &map_b, kb * kBK, n0, full_leader);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -1088,6 +1111,16 @@ int make_y_maps(const omcudaGemmArgs &a, int half_cols, bool line_store,
   return rc;
 }
 
+// L2 eviction hints (EpiParams::l2_hints); OMCUDA_GEMM_L2_HINTS=0..7 overrides
+// the default, for experiments.
+inline int l2_hints_wanted() {
+  static const int v = [] {
+    const char *s = getenv("OMCUDA_GEMM_L2_HINTS");
+    return s ? atoi(s) & 7 : 0;
+  }();
+  return v;
+}
+
 template <int BN, int EPI, int EW>
 int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   using Cfg = TcConfig<BN, EW>;
@@ -1106,6 +1139,7 @@ int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
     return rc;
   EpiParams p = make_epi_params(a);
   p.line_store = y_takes_line_stores<EPI>(a);
+  p.l2_hints = l2_hints_wanted();
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
@@ -1212,6 +1246,7 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
     return rc;
   EpiParams p = make_epi_params(a);
   p.line_store = y_takes_line_stores<EPI>(a);
+  p.l2_hints = l2_hints_wanted();
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");

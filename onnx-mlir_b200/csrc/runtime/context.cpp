@@ -153,6 +153,11 @@ void PerDeviceInt::set(int x) {
   v[dev] = x;
 }
 
+namespace {
+std::atomic<int> g_quant_mode{0};
+}
+int quant_mode() { return g_quant_mode.load(std::memory_order_relaxed); }
+
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int sm_count() { return g_sm_count > 0 ? g_sm_count : 148; }
@@ -410,5 +415,12 @@ void omcudaHostFree(void *p) {
 }
 
 int64_t omcudaLaunchCount(void) { return g_launches.load(); }
+
+void omcudaSetQuantizationMode(int64_t flags) {
+  g_quant_mode.store((int)(flags & (OMCUDA_MODE_NO_ZERO_POINT | OMCUDA_MODE_FAST_MATH)),
+      std::memory_order_relaxed);
+}
+
+int64_t omcudaGetQuantizationMode(void) { return quant_mode(); }
 
 } // extern "C"

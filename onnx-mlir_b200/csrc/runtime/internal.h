@@ -33,6 +33,9 @@ struct PerDeviceInt {
   void set(int x);
 };
 
+// OMCUDA_MODE_* flags set with omcudaSetQuantizationMode (process wide).
+int quant_mode();
+
 // dql.cu
 int launch_quantize_with_params(const float *x, int64_t n, uint8_t *y,
     const float *params, cudaStream_t st);

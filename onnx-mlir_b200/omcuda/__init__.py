@@ -107,6 +107,9 @@ def lib():
         L.omcudaSetStream.argtypes = [vp]
         L.omcudaRegisterConstant.argtypes = [vp]
         L.omcudaLaunchCount.restype = i64
+        L.omcudaSetQuantizationMode.argtypes = [i64]
+        L.omcudaSetQuantizationMode.restype = None
+        L.omcudaGetQuantizationMode.restype = i64
         for name, n in (("omcudaDynamicQuantizeLinear", 4),
                         ("omcudaQuantizeLinear", 4),
                         ("omcudaMatMulInteger", 5), ("omcudaQLinearMatMul", 9),

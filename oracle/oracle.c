@@ -55,6 +55,18 @@ float orc_round_even(float x) {
 /* DynamicQuantizeLinear                                                     */
 /* ------------------------------------------------------------------------ */
 
+/* The reference's two non-default arithmetic modes, compile-time flags there:
+ *   ORC_MODE_NO_ZERO_POINT  --disable-quantization-zero-point: zero point 0 in
+ *       DynamicQuantizeLinear (DynamicQuantizeLinear.cpp:72-83,142), a given
+ *       zero point ignored by QuantizeLinear (QuantizeLinear.cpp:231-237) and
+ *       by DequantizeLinear (Math/Elementwise.cpp:1453);
+ *   ORC_MODE_FAST_MATH  convert-onnx-to-krnl=enable-fast-math: x / scale
+ *       becomes x * (1 / scale) (QuantizeLinear.cpp:43-44,117-131).
+ * The lit tests Quantization/QuantizationWithoutZeroPoint.mlir and
+ * QuantizeLinear_with_fast_math_canonicalize.mlir pin both. */
+static int g_quant_mode = 0;
+void orc_set_quant_mode(int flags) { g_quant_mode = flags; }
+
 void orc_minmax_f32(const float *x, int64_t n, float *mn, float *mx) {
   float lo = INFINITY, hi = -INFINITY;
   for (int64_t i = 0; i < n; ++i) {
@@ -76,6 +88,8 @@ void orc_dql_params(
   float inter = qmin - xmin / s;
   float sat = clipf(inter, qmin, qmax); /* saturate first ... */
   float z = orc_round_even(sat);        /* ... then round (:77-79) */
+  if (g_quant_mode & ORC_MODE_NO_ZERO_POINT)
+    z = 0.0f;
   *scale = s;
   *zp_f = z;
   /* math.cast f32 -> ui8: fptoui to 32 bits, then truncate
@@ -85,10 +99,13 @@ void orc_dql_params(
 
 void orc_quantize_u8(
     const float *x, int64_t n, float scale, float zp_f, uint8_t *y) {
+  const int fast = (g_quant_mode & ORC_MODE_FAST_MATH) != 0;
+  const int no_zp = (g_quant_mode & ORC_MODE_NO_ZERO_POINT) != 0;
+  const float rcp = 1.0f / scale;
   for (int64_t i = 0; i < n; ++i) {
-    float q = x[i] / scale;
+    float q = fast ? x[i] * rcp : x[i] / scale;
     float r = orc_round_even(q);
-    float a = r + zp_f;
+    float a = no_zp ? r : r + zp_f;
     float s = clipf(a, 0.0f, 255.0f);
     y[i] = (uint8_t)(uint32_t)s;
   }
@@ -96,10 +113,13 @@ void orc_quantize_u8(
 
 void orc_quantize_i8(
     const float *x, int64_t n, float scale, float zp_f, int8_t *y) {
+  const int fast = (g_quant_mode & ORC_MODE_FAST_MATH) != 0;
+  const int no_zp = (g_quant_mode & ORC_MODE_NO_ZERO_POINT) != 0;
+  const float rcp = 1.0f / scale;
   for (int64_t i = 0; i < n; ++i) {
-    float q = x[i] / scale;
+    float q = fast ? x[i] * rcp : x[i] / scale;
     float r = orc_round_even(q);
-    float a = r + zp_f;
+    float a = no_zp ? r : r + zp_f;
     float s = clipf(a, -128.0f, 127.0f);
     y[i] = (int8_t)(int32_t)s;
   }
@@ -240,7 +260,7 @@ void orc_dequant_tail(const int32_t *acc, int64_t M, int64_t N, float s0,
 
 void orc_dequantize_linear(
     const void *x, int dtype, int64_t n, float scale, int32_t zp, float *y) {
-  float zf = (float)zp;
+  float zf = (g_quant_mode & ORC_MODE_NO_ZERO_POINT) ? 0.0f : (float)zp;
   for (int64_t i = 0; i < n; ++i) {
     float xf;
     if (dtype == 0)

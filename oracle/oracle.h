@@ -37,6 +37,10 @@ float orc_round_even(float x);
 
 /* src/Conversion/ONNXToKrnl/Math/Reduction.cpp:191-260,394-548: whole-tensor
  * min and max with minnum/maxnum combine and +inf/-inf identities. */
+/* Non-default arithmetic modes of the reference (see oracle.c); 0 = default. */
+#define ORC_MODE_NO_ZERO_POINT 1
+#define ORC_MODE_FAST_MATH 2
+void orc_set_quant_mode(int flags);
 void orc_minmax_f32(const float *x, int64_t n, float *mn, float *mx);
 
 /* src/Conversion/ONNXToKrnl/Quantization/DynamicQuantizeLinear.cpp:43-84. */

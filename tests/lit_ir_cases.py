@@ -10,6 +10,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CASES = json.load(open(os.path.join(HERE, "golden", "lit_ir_golden.json")))["cases"]
 
 
+MODE_CASES = json.load(open(os.path.join(HERE, "golden", "lit_ir_golden_modes.json")))["cases"]
+MODE_FLAGS = {"no_zero_point": 1, "fast_math": 2}   # OMCUDA_MODE_* / ORC_MODE_*
+
+
+def mode_case_id(c):
+    return "%s-%s-%d" % (c["mode"], c["function"], len(c["inputs"][0]["data"]))
+
+
 def _arr(t):
     return np.array(t["data"], dtype=np.dtype(t["dtype"])).reshape(t["shape"])
 

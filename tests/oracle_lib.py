@@ -34,6 +34,7 @@ class Oracle:
         L.orc_round_even.argtypes = [ctypes.c_float]
         L.orc_selftest_round_even_exhaustive.restype = _i64
         L.orc_max_threads.restype = _i32
+        L.orc_set_quant_mode.argtypes = [_i32]
         L.orc_dql_params.argtypes = [ctypes.c_float, ctypes.c_float, _vp, _vp, _vp]
         L.orc_minmax_f32.argtypes = [_vp, _i64, _vp, _vp]
         L.orc_quantize_u8.argtypes = [_vp, _i64, ctypes.c_float, ctypes.c_float, _vp]

@@ -183,3 +183,19 @@ def test_oracle_fp32_ops_match_executed_lit_ir(orc, case):
         assert np.allclose(got, want, rtol=1e-5, atol=1e-5), np.abs(got - want).max()
     else:
         assert got.tobytes() == want.tobytes(), np.abs(got - want).max()
+
+
+@pytest.mark.parametrize("case", lit_ir_cases.MODE_CASES, ids=lit_ir_cases.mode_case_id)
+def test_oracle_modes_match_executed_lit_ir(orc, case):
+    # --disable-quantization-zero-point and enable-fast-math, against the
+    # executed IR of the reference's lowering tests for those options.
+    orc.L.orc_set_quant_mode(lit_ir_cases.MODE_FLAGS[case["mode"]])
+    try:
+        got, want = lit_ir_cases.run_case(case, lit_ir_cases.OracleBackend(orc))
+    finally:
+        orc.L.orc_set_quant_mode(0)
+    lit_ir_cases.assert_same(got, want)
+    if case["mode"] == "fast_math":
+        # the fixture tells the modes apart: the default arithmetic must not match
+        got0, _ = lit_ir_cases.run_case(case, lit_ir_cases.OracleBackend(orc))
+        assert got0[0].tobytes() != want[0].tobytes()
