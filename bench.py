@@ -632,6 +632,26 @@ def strong_scaling_leg(env, wl, world, rank, dist, barrier, steps=5, warmup=2):
     step_ms = sum(a.elapsed_time(c_) for a, _, c_ in rows) / steps
     run_ms = sum(a.elapsed_time(b) for a, b, _ in rows) / steps
     gather_ms = sum(b.elapsed_time(c_) for _, b, c_ in rows) / steps
+    # The same with every DynamicQuantizeLinear range all-reduced over the
+    # ranks (global quantization: the sharded run then equals the whole-batch
+    # run bit for bit); 4 * layers + 1 two-word NCCL all-reduces per step.
+    from omcuda.sharding import make_range_sync
+    wl.enc.set_range_sync(make_range_sync())
+    gq = []
+    for i in range(warmup + steps):
+        env.flush_l2()
+        a, b = ev(), ev()
+        a.record(env.stream)
+        wl.enc.run_dev(x.data_ptr(), b_local, c["S"], y_local.data_ptr(), env.sptr())
+        gather_rows(y_local, B, out=y_all)
+        b.record(env.stream)
+        if i >= warmup:
+            gq.append((a, b))
+        if i == warmup - 1:
+            barrier()
+    barrier()
+    wl.enc.set_range_sync(None)
+    gq_ms = sum(a.elapsed_time(b) for a, b in gq) / steps
     # the whole batch on one GPU, no gather
     one = []
     for i in range(1 + 3):
@@ -644,8 +664,8 @@ def strong_scaling_leg(env, wl, world, rank, dist, barrier, steps=5, warmup=2):
             one.append((a, b))
     barrier()
     one_ms = sum(a.elapsed_time(b) for a, b in one) / len(one)
-    step_ms, run_ms, gather_ms, one_ms = _max_over_ranks(
-        env, dist, world, [step_ms, run_ms, gather_ms, one_ms])
+    step_ms, run_ms, gather_ms, one_ms, gq_ms = _max_over_ranks(
+        env, dist, world, [step_ms, run_ms, gather_ms, one_ms, gq_ms])
     return {"scaling": "strong", "global_batch": B, "batch_per_gpu": b_local,
             "steps": steps, "warmup": warmup,
             "value": B / (step_ms * 1e-3), "unit": "seq/s", "ms_per_step": step_ms,
@@ -655,6 +675,14 @@ def strong_scaling_leg(env, wl, world, rank, dist, barrier, steps=5, warmup=2):
             "speedup_over_one_gpu": one_ms / step_ms,
             "efficiency": one_ms / step_ms / world,
             "gpu_launches_per_step": int(launches),
+            "quantization": "per-shard ranges (a rank's result equals the reference's on "
+                            "its rows)",
+            "global_quant": {"ms_per_step": gq_ms, "value": B / (gq_ms * 1e-3),
+                             "speedup_over_one_gpu": one_ms / gq_ms,
+                             "range_all_reduces_per_step": 4 * c["layers"] + 1,
+                             "quantization": "ranges all-reduced over the ranks (the "
+                                             "sharded result equals the whole-batch result "
+                                             "bit for bit)"},
             "timing": "CUDA events on the launching stream, max over ranks; the "
                       "gather is synchronous (the step ends when the rows have arrived)"}
 
@@ -708,6 +736,8 @@ def run_strong_only(args, env, world, rank, dist):
     if rank == 0:
         cfg = wl.config()
         cfg.pop("batch_per_gpu")
+        cfg["parallelism"] = ("configured batch split over the GPUs, weights replicated, "
+                              "one all-gather of the output rows inside every step")
         cfg.update({"global_batch": st["global_batch"], "batch_per_gpu": st["batch_per_gpu"]})
         emit({"metric": wl.metric, "value": st["value"], "unit": wl.unit, "n_gpus": world,
               "steps": args.steps, "warmup": args.warmup, "ms_per_step": st["ms_per_step"],

@@ -441,6 +441,9 @@ int omcudaDevAttentionBf16(const void *hi, const void *lo, int64_t ld_planes,
  * quantizes x, in one launch.  The range is left as it is: arm it again
  * before its producer runs a second time. */
 int omcudaDevRangeInit(void *ranges, int64_t count, void *stream);
+/* Folds the min / max of x into an armed range (for a tensor that no kernel of
+ * the library produced). */
+int omcudaDevRangeFold(const float *x, int64_t n, void *range, void *stream);
 int omcudaDevQuantizeFromRange(const float *x, int64_t n, void *range,
     uint8_t *y, float *params /* 2 floats */, float *y_scale, uint8_t *y_zp,
     void *stream);
@@ -508,6 +511,22 @@ int omcudaEncoderRunDev(omcudaEncoder *enc, const float *x, int64_t batch,
 void omcudaEncoderSetProfiling(omcudaEncoder *enc, int on);
 int omcudaEncoderGemmStats(
     omcudaEncoder *enc, double *ms_total, double *ops_total, int64_t *launches);
+/* Global quantization ranges for a batch that is sharded over several GPUs.
+ * DynamicQuantizeLinear is per tensor: its scale and zero point depend on every
+ * row of the activation (DynamicQuantizeLinear.cpp:136-145 reduces over the
+ * flattened tensor).  By default each rank quantizes with the range of its own
+ * rows, so a rank's result equals the reference's on that rank's rows.  With a
+ * hook set, the harness calls it once per DynamicQuantizeLinear of the graph
+ * (4 per layer + 1), after the range of the local rows is complete and before
+ * it is used: `range` is device memory holding two uint32, order-preserving
+ * encodings (larger encoding = larger float) of the running minimum and
+ * maximum; the callee must replace them, in `stream` order, by the minimum of
+ * [0] and the maximum of [1] over all ranks (a 2-word all-reduce).  The
+ * sharded run then equals the reference's run on the whole batch bit for bit.
+ * No counterpart in the reference, which has no multi-device support. */
+typedef void (*omcudaRangeSyncFn)(void *ctx, void *range, void *stream);
+int omcudaEncoderSetRangeSync(omcudaEncoder *enc, omcudaRangeSyncFn fn, void *ctx);
+
 /* Parity-test tap (no counterpart in the reference, which is inspected with
  * its own instrumentation passes instead): while a tap buffer is set, every
  * run also copies each layer's intermediates into it, so that a test can feed

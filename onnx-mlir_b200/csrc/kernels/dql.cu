@@ -134,6 +134,36 @@ __global__ void __launch_bounds__(kDqlThreads)
   }
 }
 
+// Folds the min / max of x into a running range (the encoding and the commit
+// rule of range_commit_warp): the reduction of DynamicQuantizeLinear in the
+// form the producers of the encoder harness use, for a tensor that has no
+// producer on the device.
+__global__ void __launch_bounds__(kDqlThreads)
+    range_fold_kernel(const float *__restrict__ x, int64_t n, uint32_t *__restrict__ range) {
+  float lo = INFINITY, hi = -INFINITY;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  if ((((uintptr_t)x) & 15u) == 0) {
+    const int64_t n4 = n >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    for (int64_t i = tid; i < n4; i += nthreads) {
+      const float4 a = __ldcs(x4 + i);
+      lo = fminf(lo, fminf(fminf(a.x, a.y), fminf(a.z, a.w)));
+      hi = fmaxf(hi, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
+    }
+    for (int64_t j = (n4 << 2) + tid; j < n; j += nthreads) {
+      lo = fminf(lo, x[j]);
+      hi = fmaxf(hi, x[j]);
+    }
+  } else {
+    for (int64_t j = tid; j < n; j += nthreads) {
+      lo = fminf(lo, x[j]);
+      hi = fmaxf(hi, x[j]);
+    }
+  }
+  range_commit_warp(range, lo, hi);
+}
+
 // Where the range-driven form of the kernel leaves its scalars.
 struct QuantOutputs {
   float *params;  // {scale, zero point as float}
@@ -262,6 +292,17 @@ extern "C" int omcudaDevDynamicQuantizeLinear(const float *x, int64_t n,
   OMCUDA_CHECK_LAUNCH("dql_minmax_kernel");
   if (n > 0)
     return launch_quantize_with_params(x, n, y, scr->params, st);
+  return OMCUDA_OK;
+}
+
+extern "C" int omcudaDevRangeFold(const float *x, int64_t n, void *range, void *stream) {
+  if (n < 0 || (n > 0 && !x) || !range)
+    return fail(OMCUDA_EINVAL, "RangeFold: bad argument");
+  if (n == 0)
+    return OMCUDA_OK;
+  int grid = grid_for(n, kDqlThreads * 16);
+  range_fold_kernel<<<grid, kDqlThreads, 0, (cudaStream_t)stream>>>(x, n, (uint32_t *)range);
+  OMCUDA_CHECK_LAUNCH("range_fold_kernel");
   return OMCUDA_OK;
 }
 

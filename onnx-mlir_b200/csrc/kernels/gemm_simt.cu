@@ -400,6 +400,9 @@ static bool gemv_wanted() {
 }
 
 int launch_gemm_simt(const omcudaGemmArgs &a, cudaStream_t st) {
+  // Up to 16 rows when the tensor-core kernel cannot take the shape; the
+  // dispatcher sends tensor-core-capable shapes here only for M <= 4 (with
+  // more rows the dp4a work per weight byte outgrows the weight read).
   if (a.M <= 16 && gemv_wanted()) {
     if (a.M <= 1)
       launch_gemv<1, 2>(a, st);
@@ -531,10 +534,11 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
     return fail(OMCUDA_ENOTSUP,
         "GemmI8: the split-bf16, range-only and quantizing tails exist on the "
         "tensor-core kernel only (K %% 16 == 0, 16-byte aligned A)");
-  // Up to 16 rows the GEMM is one read of the weight: the GEMV-shaped SIMT
-  // kernel streams it at HBM speed, which a 128-row tensor-core tile on a
-  // few SMs cannot.
+  // Up to 4 rows the GEMM is one read of the weight, which the GEMV-shaped
+  // SIMT kernel streams faster than a 128-row tensor-core tile on a few SMs
+  // (measured: M = 1 19 us against 23-27 us on the 58 MB weights; at M = 16 the
+  // dp4a work makes it 30-68 us against the tensor-core kernel's 20-37 us).
   bool use_tc = (a.kernel_choice == 1) || tc_only ||
-                (a.kernel_choice == 0 && tc_ok && a.M > 16);
+                (a.kernel_choice == 0 && tc_ok && a.M > 4);
   return use_tc ? launch_gemm_tc(a, st) : launch_gemm_simt(a, st);
 }

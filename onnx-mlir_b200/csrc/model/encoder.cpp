@@ -103,6 +103,10 @@ struct omcudaEncoder {
   // optional copy of every layer's intermediates (omcudaEncoderSetTap)
   uint8_t *tap = nullptr;
   int64_t tap_bytes = 0;
+  // optional all-reduce of every quantization range over the ranks that share
+  // a batch (omcudaEncoderSetRangeSync)
+  omcudaRangeSyncFn range_sync = nullptr;
+  void *range_sync_ctx = nullptr;
 };
 
 namespace {
@@ -436,6 +440,13 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
   const bool ffn_two_pass = ffn_two_pass_wanted();
   omcudaEncoderTapLayout tl;
   tap_layout(e->cfg, T, &tl);
+  if (e->range_sync && ffn_two_pass)
+    return fail(OMCUDA_ENOTSUP, "EncoderRun: range sync and the two-pass FFN do not combine");
+#define SYNC_RANGE(r)                                                          \
+  do {                                                                         \
+    if (e->range_sync)                                                         \
+      e->range_sync(e->range_sync_ctx, (r), (void *)st);                       \
+  } while (0)
   if (e->tap && (ffn_two_pass || e->tap_bytes < tl.total))
     return fail(OMCUDA_EINVAL,
         "EncoderRun: the tap buffer holds %lld bytes, this run needs %lld",
@@ -454,8 +465,17 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
   // float (both read by the quantize pass), [2] scale as the op's y_scale
   // output, [3] first byte: zero point as uint8 (the GEMM's a_zero_point).
   // The model input has no producer here: it gets the standalone reduction.
-  RUN(omcudaDevDynamicQuantizeLinear(x, T * H, xq, params + 2,
-      (uint8_t *)(params + 3), e->dql_scratch.p, st));
+  if (e->range_sync) {
+    // global ranges: the input's range is folded like a producer's, reduced
+    // over the ranks, and the quantize pass derives scale and zero point
+    RUN(omcudaDevRangeFold(x, T * H, ranges, st));
+    SYNC_RANGE(ranges);
+    RUN(omcudaDevQuantizeFromRange(x, T * H, ranges, xq, params, params + 2,
+        (uint8_t *)(params + 3), st));
+  } else {
+    RUN(omcudaDevDynamicQuantizeLinear(x, T * H, xq, params + 2,
+        (uint8_t *)(params + 3), e->dql_scratch.p, st));
+  }
   const float *cur = x;
   for (int64_t l = 0; l < e->cfg.layers; ++l) {
     LayerState &L = e->layers[(size_t)l];
@@ -469,9 +489,11 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
     float *p_h1 = params + (size_t)(4 * l + 2) * 4;
     float *p_f = params + (size_t)(4 * l + 3) * 4;
     float *nxt = (l + 1 == e->cfg.layers) ? y : (float *)e->ybuf[l & 1].p;
-    if (l > 0)
+    if (l > 0) {
+      SYNC_RANGE(r_x);
       RUN(omcudaDevQuantizeFromRange(cur, T * H, r_x, xq, p_x, p_x + 2,
           (uint8_t *)(p_x + 3), st));
+    }
     const int64_t tb = l * tl.layer_stride;
     RUN(tap_copy(e, tb + tl.x, cur, T * H * 4, st));
     RUN(tap_copy(e, tb + tl.xq_x, xq, T * H, st));
@@ -491,6 +513,7 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
       RUN(omcudaDevAttentionEx(q, q + H, q + 2 * H, batch, seq, heads, dh,
           att_scale, (float *)e->ctx.p, 3 * H, H, r_ctx, st));
     }
+    SYNC_RANGE(r_ctx);
     RUN(omcudaDevQuantizeFromRange((const float *)e->ctx.p, T * H, r_ctx, xq,
         p_ctx, p_ctx + 2, (uint8_t *)(p_ctx + 3), st));
     RUN(tap_copy(e, tb + tl.ctx, e->ctx.p, T * H * 4, st));
@@ -506,6 +529,7 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
         fuse_residual ? nullptr : (const float *)e->a.p, T, H,
         (const float *)L.ln1g.p, L.has_ln1b ? (const float *)L.ln1b.p : nullptr,
         eps, (float *)e->h1.p, r_h1, st));
+    SYNC_RANGE(r_h1);
     RUN(omcudaDevQuantizeFromRange((const float *)e->h1.p, T * H, r_h1, xq,
         p_h1, p_h1 + 2, (uint8_t *)(p_h1 + 3), st));
     RUN(tap_copy(e, tb + tl.h1, e->h1.p, T * H * 4, st));
@@ -521,6 +545,7 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
       RUN(gemm(e, xq, (const uint8_t *)(p_h1 + 3), p_h1 + 2, L.w1, T,
           (const float *)L.scal.p + 1, 1, (const float *)L.b1.p, 1,
           (float *)e->f.p, r_f, st));
+      SYNC_RANGE(r_f);
       RUN(omcudaDevQuantizeFromRange((const float *)e->f.p, T * F, r_f, xq, p_f,
           p_f + 2, (uint8_t *)(p_f + 3), st));
       RUN(tap_copy(e, tb + tl.f, e->f.p, T * F * 4, st));
@@ -539,6 +564,7 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
   }
   RUN(tap_copy(e, tl.params, params, (4 * e->cfg.layers + 1) * 16, st));
 #undef RUN
+#undef SYNC_RANGE
   return OMCUDA_OK;
 }
 
@@ -733,6 +759,15 @@ extern "C" int omcudaEncoderWait(omcudaEncoder *e) {
   }
   omcudaSynchronize(); // surfaces a bounded-wait timeout of the kernels
   return sticky_error() ? omcudaGetLastError() : OMCUDA_OK;
+}
+
+extern "C" int omcudaEncoderSetRangeSync(
+    omcudaEncoder *e, omcudaRangeSyncFn fn, void *ctx) {
+  if (!e)
+    return fail(OMCUDA_EINVAL, "EncoderSetRangeSync: null encoder");
+  e->range_sync = fn;
+  e->range_sync_ctx = ctx;
+  return OMCUDA_OK;
 }
 
 extern "C" int omcudaEncoderGetTapLayout(const omcudaEncoder *e, int64_t batch,

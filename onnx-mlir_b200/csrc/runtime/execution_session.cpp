@@ -66,14 +66,21 @@ extern "C" omcudaSession *omcudaSessionCreate(
     return nullptr;
   }
   std::string path = shared_lib_path;
+  // The model's constructor looks its constants file up in OM_CONSTANT_PATH
+  // while dlopen runs: point it at the model's folder for that long, unless
+  // the caller chose a folder.
+  bool set_constant_path = false;
   if (!getenv("OM_CONSTANT_PATH")) {
     size_t slash = path.find_last_of('/');
     setenv("OM_CONSTANT_PATH", slash == std::string::npos ? "." : path.substr(0, slash).c_str(),
         /*overwrite=*/0);
+    set_constant_path = true;
   }
   std::string t = (tag && *tag) ? tag : lower_stem(path);
   std::string suffix = strcasecmp(t.c_str(), "NONE") == 0 ? "" : "_" + t;
   void *h = dlopen(path.c_str(), RTLD_LAZY | RTLD_GLOBAL);
+  if (set_constant_path)
+    unsetenv("OM_CONSTANT_PATH");
   if (!h) {
     fail(OMCUDA_EINVAL, "SessionCreate: cannot open library '%s': %s", path.c_str(), dlerror());
     return nullptr;

@@ -569,6 +569,17 @@ class Encoder:
             taps.append(d)
         return y, taps
 
+    def set_range_sync(self, fn):
+        """fn: an omcuda.sharding.make_range_sync(...) callback, or None for
+        per-shard quantization ranges (the default)."""
+        L = lib()
+        L.omcudaEncoderSetRangeSync.argtypes = [ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_void_p]
+        self._range_sync = fn            # keeps the ctypes callback alive
+        ptr = ctypes.cast(fn, ctypes.c_void_p) if fn is not None else None
+        if L.omcudaEncoderSetRangeSync(self.handle, ptr, None) != 0:
+            check()
+
     def set_profiling(self, on):
         lib().omcudaEncoderSetProfiling.argtypes = [ctypes.c_void_p, ctypes.c_int]
         lib().omcudaEncoderSetProfiling(self.handle, int(on))

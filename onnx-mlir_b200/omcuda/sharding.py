@@ -5,9 +5,63 @@ weights, so ranks take contiguous row ranges and never exchange data inside a
 forward pass; the only collective is the final all-gather of output rows.
 Per-tensor dynamic quantization then uses each rank's own min/max ("replica
 mode"): a rank's result equals the reference's result on that rank's rows.
+
+Global-quantization mode (optional): the encoder harness can call a hook for
+every DynamicQuantizeLinear range (omcudaEncoderSetRangeSync); reduce_ranges /
+make_range_sync below implement it as one 2-word all-reduce, after which every
+rank quantizes with the range of the WHOLE batch and the sharded run equals
+the reference's run on the whole batch bit for bit.
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
+
+_INT_MIN = -0x80000000
+
+
+def reduce_ranges(t, group=None):
+    """t: int32 tensor [..., 2] holding, as raw bits, the order-preserving
+    uint32 encodings of running {min, max} (larger encoding = larger float).
+    Replaces every pair in place by {min over ranks, max over ranks}.
+    Flipping the top bit turns the unsigned order into int32 order; the
+    bitwise complement of the second word turns its maximum into a minimum, so
+    one MIN all-reduce serves both."""
+    v = t ^ _INT_MIN
+    v[..., 1] = ~v[..., 1]
+    dist.all_reduce(v, op=dist.ReduceOp.MIN, group=group)
+    v[..., 1] = ~v[..., 1]
+    t.copy_(v ^ _INT_MIN)
+    return t
+
+
+class _DevWords:
+    """Two int32 words of device memory as a zero-copy torch tensor."""
+
+    def __init__(self, ptr):
+        self.__cuda_array_interface__ = {"shape": (2,), "typestr": "<i4",
+                                         "data": (int(ptr), False), "version": 2}
+
+
+RANGE_SYNC_FN = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p)
+
+
+def make_range_sync(group=None, via_host=False):
+    """The omcudaRangeSyncFn for omcudaEncoderSetRangeSync.  The all-reduce is
+    queued in `stream` order (NCCL on device tensors); via_host routes it
+    through two host words instead (for process groups without device
+    collectives, e.g. gloo in tests).  Keep the returned object alive while
+    the encoder may call it."""
+    def fn(_ctx, range_ptr, stream):
+        with torch.cuda.stream(torch.cuda.ExternalStream(int(stream or 0))):
+            t = torch.as_tensor(_DevWords(range_ptr), device="cuda")
+            if via_host:
+                h = t.cpu()
+                reduce_ranges(h, group)
+                t.copy_(h)
+            else:
+                reduce_ranges(t, group)
+    return RANGE_SYNC_FN(fn)
 
 
 def shard_rows(total_rows, world, rank):

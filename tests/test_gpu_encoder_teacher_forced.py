@@ -20,8 +20,9 @@ element:
   * one oracle layer fed the library's layer input (three quantizations lie
     between input and output, so activations next to a rounding boundary may
     land one step apart in the two implementations and move the rows they
-    feed): the same 1e-3 bound on at least 95 % of the elements and a worst
-    deviation below 5e-2; the observed figures are printed.
+    feed): statistical, an rms deviation below 2e-3 of the output's rms and a
+    worst deviation below 5e-2; the share of elements beyond the 1e-3 bound is
+    printed with the other observed figures.
 """
 import numpy as np
 import pytest
@@ -107,9 +108,12 @@ def test_teacher_forced_against_oracle(gpu, orc, name, B, S, H, heads, F, nl):
         ok, r = close(t["y"], want)
         frac_bad_layer = max(frac_bad_layer, 1.0 - ok.mean())
         worst["layer"] = max(worst["layer"], float(np.abs(t["y"] - want).max()))
-        assert ok.mean() >= 0.95, (name, l, "layer", 1.0 - ok.mean())
-        assert np.abs(t["y"] - want).max() < 5e-2, (name, l, "layer")
+        d = (t["y"] - want).astype(np.float64)
+        rel_rms = float(np.sqrt((d ** 2).mean()) / np.sqrt((want.astype(np.float64) ** 2).mean()))
+        worst["layer_rms"] = max(worst.get("layer_rms", 0.0), rel_rms)
+        assert rel_rms < 2e-3, (name, l, "layer", rel_rms)
+        assert np.abs(d).max() < 5e-2, (name, l, "layer")
     print("\n%s: worst error / tolerance ctx %.3g, h1 %.3g, y %.3g; whole layer: "
-          "worst |err| %.3g, at most %.3g of a layer's elements beyond 1e-3"
-          % (name, worst["ctx"], worst["h1"], worst["y"], worst["layer"],
-             frac_bad_layer))
+          "rms error / rms %.3g, worst |err| %.3g, at most %.3g of a layer's elements "
+          "beyond 1e-3" % (name, worst["ctx"], worst["h1"], worst["y"], worst["layer_rms"],
+                           worst["layer"], frac_bad_layer))

@@ -13,7 +13,7 @@ def test_bounded_wait_gives_up_and_service_resumes(gpu, orc):
     from omcuda import dev
     L = gpu.lib()
     st = L.omcudaGetStream()
-    waited = gpu.Tensor.from_numpy(np.zeros(1, np.uint64)).to_device()
+    waited = gpu.Tensor.from_numpy(np.zeros(1, np.int64)).to_device()
     dev.set_wait_limit_ns(1_000_000)  # 1 ms
     try:
         # One CTA allocates tensor memory and waits, through the same mbar_wait

@@ -75,3 +75,60 @@ def test_shard_rows_partition():
             assert covered == list(range(total))
     with pytest.raises(ValueError):
         shard_rows(8, 2, 2)
+
+
+def _f32_to_ordered(f):
+    """The library's order-preserving float -> uint32 encoding (common.cuh)."""
+    u = np.asarray(f, np.float32).view(np.uint32)
+    return np.where(u & 0x80000000, ~u, u | 0x80000000).astype(np.uint32)
+
+
+def _ordered_to_f32(u):
+    u = np.asarray(u, np.uint32)
+    return np.where(u & 0x80000000, u & 0x7fffffff, ~u).astype(np.uint32).view(np.float32)
+
+
+def _range_worker(rank, world, port, q):
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.join(root, "onnx-mlir_b200"))
+    from omcuda.sharding import reduce_ranges
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # ranges of mixed sign, equal values, infinities (an empty shard)
+        rng = np.random.default_rng(100 + rank)
+        lo = rng.normal(0, 3, 6).astype(np.float32)
+        hi = lo + np.abs(rng.normal(0, 3, 6)).astype(np.float32)
+        lo[4], hi[4] = np.float32(1.5), np.float32(1.5)
+        if rank == 0:
+            lo[5], hi[5] = np.inf, -np.inf          # nothing seen on this rank
+        enc = np.stack([_f32_to_ordered(lo), _f32_to_ordered(hi)], -1)
+        t = torch.from_numpy(enc.view(np.int32).copy())
+        reduce_ranges(t)
+        out = t.numpy().view(np.uint32)
+        q.put((rank, lo, hi, _ordered_to_f32(out[:, 0]), _ordered_to_f32(out[:, 1])))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_global_quantization_range_reduce(world):
+    # The 2-word all-reduce behind omcudaEncoderSetRangeSync: every rank ends up
+    # with the minimum of the minima and the maximum of the maxima, exactly.
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_range_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted((q.get(timeout=120) for _ in range(world)), key=lambda r: r[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    want_lo = np.min([r[1] for r in results], axis=0)
+    want_hi = np.max([r[2] for r in results], axis=0)
+    for _, _, _, got_lo, got_hi in results:
+        assert got_lo.tobytes() == want_lo.tobytes()
+        assert got_hi.tobytes() == want_hi.tobytes()
