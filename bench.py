@@ -431,7 +431,13 @@ def run_gpu(args):
     if is_encoder and args.scaling == "strong" and world > 1:
         return run_strong_only(args, env, world, rank, dist)
     if is_encoder:
+        if args.batch:
+            EncoderWorkload.SHAPES[args.workload] = dict(
+                EncoderWorkload.SHAPES[args.workload], B=args.batch)
         wl = EncoderWorkload(env, args.workload, 42 + rank, world, dist)
+    elif args.shape:
+        M, K, N = (int(v) for v in args.shape.lower().split("x"))
+        wl = LinearWorkload(env, "mmi_%dx%dx%d" % (M, K, N), 42 + rank, shape=(M, K, N))
     else:
         wl = LinearWorkload(env, args.workload, seed=42 + rank)
     peaks = load_peaks()
@@ -582,7 +588,7 @@ def run_gpu(args):
     if extra is not None:
         out["extra"] = extra
     # CPU baseline on a bounded sample of the same workload (rank 0, N=1 only).
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not args.shape and not args.batch:
         out["cpu_baseline"] = cpu_baseline(args.workload, wl, long_sample=True)
     emit(out)
     if world > 1:
@@ -1043,6 +1049,12 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true",
                     help="skip the extra kernels of the default N = 1 run")
+    ap.add_argument("--shape", type=str, default=None, metavar="MxKxN",
+                    help="with --workload mmi_4096: another member of the GEMM sweep, "
+                         "e.g. 1x4096x14336 (small cases for profiling)")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="encoder workloads: a smaller batch than the configured one "
+                         "(small cases for profiling; the JSON line names it)")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="N > 1, encoder workloads: weak = every rank runs the configured "
                          "batch (default); strong = the configured batch is split")

@@ -14,7 +14,10 @@
 // device memory for it until the process exits.
 //
 // The function calls no cudaMalloc, cudaFree or allocating library routine.
-// It has no counterpart in onnx-mlir.
+// (Its first call on a device looks the array's address up with
+// cudaGetSymbolAddress, which may make the CUDA runtime load the library's
+// device code on that device; make that first call at start-up, before any
+// stream capture.)  It has no counterpart in onnx-mlir.
 #include <cuda_runtime.h>
 
 #include <mutex>

@@ -211,95 +211,102 @@ __global__ void __launch_bounds__(32 * kGemvWarps)
     gemm_i8_gemv_kernel(const uint8_t *__restrict__ A,
         const uint8_t *__restrict__ Bt, int64_t kp, EpiParams p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t n0 = (int64_t)blockIdx.x * CB;
   const int64_t m0 = (int64_t)blockIdx.y * MT;
   const bool vec_ok = ((p.K & 15) == 0) && (((uintptr_t)A & 15u) == 0);
-  int32_t acc[MT][CB];
-#pragma unroll
-  for (int i = 0; i < MT; ++i)
-#pragma unroll
-    for (int j = 0; j < CB; ++j)
-      acc[i][j] = 0;
-  const uint4 *brow[CB];
-#pragma unroll
-  for (int j = 0; j < CB; ++j) // columns past N re-read the last one; never stored
-    brow[j] = reinterpret_cast<const uint4 *>(Bt + (n0 + j < p.N ? n0 + j : p.N - 1) * kp);
   const int64_t chunks = kp >> 4;
   constexpr int kStep = 32 * kGemvWarps;
-  auto consume = [&](int64_t c, const uint4 (&b)[CB]) {
-#pragma unroll
-    for (int i = 0; i < MT; ++i) {
-      const uint4 a = load_a_chunk(A, m0 + i, p.M, p.K, c << 4, vec_ok);
-#pragma unroll
-      for (int j = 0; j < CB; ++j) {
-        int32_t s = acc[i][j];
-        s = dp4a_mixed<kASigned, kBSigned>(a.x, b[j].x, s);
-        s = dp4a_mixed<kASigned, kBSigned>(a.y, b[j].y, s);
-        s = dp4a_mixed<kASigned, kBSigned>(a.z, b[j].z, s);
-        s = dp4a_mixed<kASigned, kBSigned>(a.w, b[j].w, s);
-        acc[i][j] = s;
-      }
-    }
-  };
-  int64_t c = threadIdx.x;
-  for (; c + kStep < chunks; c += 2 * kStep) {
-    uint4 b0[CB], b1[CB];
-#pragma unroll
-    for (int j = 0; j < CB; ++j) {
-      b0[j] = __ldcs(brow[j] + c);
-      b1[j] = __ldcs(brow[j] + c + kStep);
-    }
-    consume(c, b0);
-    consume(c + kStep, b1);
-  }
-  if (c < chunks) {
-    uint4 b0[CB];
-#pragma unroll
-    for (int j = 0; j < CB; ++j)
-      b0[j] = __ldcs(brow[j] + c);
-    consume(c, b0);
-  }
   __shared__ int32_t part[kGemvWarps][MT * CB];
-#pragma unroll
-  for (int i = 0; i < MT; ++i)
-#pragma unroll
-    for (int j = 0; j < CB; ++j) {
-      int32_t v = acc[i][j];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1)
-        v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0)
-        part[warp][i * CB + j] = v;
-    }
-  __syncthreads();
-  // Thread t finishes output (row m0 + t / CB, column n0 + t % CB).
   static_assert(MT * CB <= 32, "the epilogue runs in the first warp");
-  if (warp != 0)
-    return;
   const EpiScalars sc = epi_scalars(p);
   float lo = INFINITY, hi = -INFINITY;
-  const int64_t m = m0 + lane / CB, n = n0 + lane % CB;
-  if (lane < MT * CB && m < p.M && n < p.N) {
-    int32_t sum = 0;
+  // A block walks column groups (grid-stride), so that a launch is a few
+  // resident blocks per SM streaming the weight rather than thousands of
+  // short-lived ones.
+  const int64_t groups = ceil_div(p.N, CB);
+  for (int64_t g = blockIdx.x; g < groups; g += gridDim.x) {
+    const int64_t n0 = g * CB;
+    int32_t acc[MT][CB];
 #pragma unroll
-    for (int w = 0; w < kGemvWarps; ++w)
-      sum += part[w][lane];
-    const EpiRow row = epi_row(p, m);
-    const int32_t v = epi_int(p, row, sum, n);
-    if (p.kind == OMCUDA_EPI_I32) {
-      reinterpret_cast<int32_t *>(p.Y)[m * p.N + n] = v;
-    } else if (p.kind == OMCUDA_EPI_DEQUANT) {
-      float y = epi_dequant(p, sc, v, n);
-      if (p.residual)
-        y = __fadd_rn(y, __ldg(p.residual + m * p.N + n));
-      reinterpret_cast<float *>(p.Y)[m * p.N + n] = y;
-      lo = fminf(lo, y);
-      hi = fmaxf(hi, y);
-    } else {
-      reinterpret_cast<uint8_t *>(p.Y)[m * p.N + n] = (uint8_t)epi_requant(p, sc, v, n);
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int j = 0; j < CB; ++j)
+        acc[i][j] = 0;
+    const uint4 *brow[CB];
+#pragma unroll
+    for (int j = 0; j < CB; ++j) // columns past N re-read the last one; never stored
+      brow[j] = reinterpret_cast<const uint4 *>(Bt + (n0 + j < p.N ? n0 + j : p.N - 1) * kp);
+    auto consume = [&](int64_t c, const uint4 (&b)[CB]) {
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        const uint4 a = load_a_chunk(A, m0 + i, p.M, p.K, c << 4, vec_ok);
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+          int32_t s = acc[i][j];
+          s = dp4a_mixed<kASigned, kBSigned>(a.x, b[j].x, s);
+          s = dp4a_mixed<kASigned, kBSigned>(a.y, b[j].y, s);
+          s = dp4a_mixed<kASigned, kBSigned>(a.z, b[j].z, s);
+          s = dp4a_mixed<kASigned, kBSigned>(a.w, b[j].w, s);
+          acc[i][j] = s;
+        }
+      }
+    };
+    int64_t c = threadIdx.x;
+    for (; c + kStep < chunks; c += 2 * kStep) {
+      uint4 b0[CB], b1[CB];
+#pragma unroll
+      for (int j = 0; j < CB; ++j) {
+        b0[j] = __ldcs(brow[j] + c);
+        b1[j] = __ldcs(brow[j] + c + kStep);
+      }
+      consume(c, b0);
+      consume(c + kStep, b1);
     }
+    if (c < chunks) {
+      uint4 b0[CB];
+#pragma unroll
+      for (int j = 0; j < CB; ++j)
+        b0[j] = __ldcs(brow[j] + c);
+      consume(c, b0);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int j = 0; j < CB; ++j) {
+        int32_t v = acc[i][j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+          v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0)
+          part[warp][i * CB + j] = v;
+      }
+    __syncthreads();
+    // Thread t of the first warp finishes output (row m0 + t / CB, column n0 + t % CB).
+    if (warp == 0) {
+      const int64_t m = m0 + lane / CB, n = n0 + lane % CB;
+      if (lane < MT * CB && m < p.M && n < p.N) {
+        int32_t sum = 0;
+#pragma unroll
+        for (int w = 0; w < kGemvWarps; ++w)
+          sum += part[w][lane];
+        const EpiRow row = epi_row(p, m);
+        const int32_t v = epi_int(p, row, sum, n);
+        if (p.kind == OMCUDA_EPI_I32) {
+          reinterpret_cast<int32_t *>(p.Y)[m * p.N + n] = v;
+        } else if (p.kind == OMCUDA_EPI_DEQUANT) {
+          float y = epi_dequant(p, sc, v, n);
+          if (p.residual)
+            y = __fadd_rn(y, __ldg(p.residual + m * p.N + n));
+          reinterpret_cast<float *>(p.Y)[m * p.N + n] = y;
+          lo = fminf(lo, y);
+          hi = fmaxf(hi, y);
+        } else {
+          reinterpret_cast<uint8_t *>(p.Y)[m * p.N + n] = (uint8_t)epi_requant(p, sc, v, n);
+        }
+      }
+    }
+    __syncthreads(); // part[] is rewritten by the next group
   }
-  if (p.out_range && p.kind == OMCUDA_EPI_DEQUANT)
+  if (warp == 0 && p.out_range && p.kind == OMCUDA_EPI_DEQUANT)
     epi_range_commit(p.out_range, lo, hi);
 }
 
@@ -368,7 +375,10 @@ static void launch_warp_gemm(const omcudaGemmArgs &a, cudaStream_t st) {
 template <int MT, int CB>
 static void launch_gemv(const omcudaGemmArgs &a, cudaStream_t st) {
   EpiParams p = make_epi_params(a);
-  dim3 grid((unsigned)ceil_div(a.N, CB), (unsigned)ceil_div(a.M, MT));
+  // Up to 12 resident blocks of 128 threads per SM (1536 threads, 8 x 16-byte
+  // loads in flight each with CB = 4).
+  const int64_t groups = ceil_div(a.N, CB), resident = (int64_t)sm_count() * 12;
+  dim3 grid((unsigned)(groups < resident ? groups : resident), (unsigned)ceil_div(a.M, MT));
   const uint8_t *A = (const uint8_t *)a.A;
   const uint8_t *Bt = (const uint8_t *)a.B.bt;
   const int threads = 32 * kGemvWarps;
@@ -405,9 +415,9 @@ int launch_gemm_simt(const omcudaGemmArgs &a, cudaStream_t st) {
   // more rows the dp4a work per weight byte outgrows the weight read).
   if (a.M <= 16 && gemv_wanted()) {
     if (a.M <= 1)
-      launch_gemv<1, 2>(a, st);
+      launch_gemv<1, 4>(a, st);
     else if (a.M <= 2)
-      launch_gemv<2, 2>(a, st);
+      launch_gemv<2, 4>(a, st);
     else if (a.M <= 4)
       launch_gemv<4, 4>(a, st);
     else
