@@ -1,15 +1,10 @@
-"""Builds libomcuda (sm_100a) and the CPU oracle in-tree.
+"""Builds libomcuda (sm_100a) in-tree.
 
-    python onnx-mlir_b200/build.py [--force]
+    python onnx-mlir_b200/build.py [--force] [-v]
 
-Outputs:
-    onnx-mlir_b200/lib/libomcuda.so   the product: CUDA kernels + C ABI
-    oracle/_build/liboracle.so        test infrastructure: CPU restatement
-    oracle/_ref/libcruntime_ref.so    only where the onnx-mlir tree is present:
-                                      the reference's own OMTensor runtime,
-                                      compiled from its sources where they lie,
-                                      used to check ABI compatibility
-nvcc cross-compiles without a GPU, so this runs on a CPU-only machine.
+Output: onnx-mlir_b200/lib/libomcuda.so, the product (CUDA kernels + C ABI).
+nvcc cross-compiles without a GPU, so this runs on a CPU-only machine.  (The
+test infrastructure -- the CPU oracle -- has its own script, oracle/build.py.)
 """
 import concurrent.futures
 import os
@@ -102,36 +97,5 @@ def build_lib(force=False, verbose=False):
     return LIB
 
 
-def build_oracle(force=False):
-    odir = os.path.join(ROOT, "oracle")
-    out = os.path.join(odir, "_build", "liboracle.so")
-    srcs = [os.path.join(odir, "oracle.c"), os.path.join(odir, "oracle.h")]
-    if force or _newer(srcs, out):
-        _run(["make", "-s", "-C", odir, "oracle"])
-    return out
-
-
-def build_ref_runtime(force=False):
-    """Compiles the reference's OMTensor runtime where its tree is present."""
-    odir = os.path.join(ROOT, "oracle")
-    ref = os.environ.get("ONNX_MLIR_SRC", "/root/reference")
-    out = os.path.join(odir, "_ref", "libcruntime_ref.so")
-    if not os.path.isdir(os.path.join(ref, "src", "Runtime")):
-        return out if os.path.exists(out) else None
-    if force or not os.path.exists(out):
-        _run(["make", "-s", "-C", odir, "ref", "ONNX_MLIR_SRC=" + ref])
-    return out
-
-
-def build_all(force=False, verbose=False):
-    lib = build_lib(force, verbose)
-    orc = build_oracle(force)
-    ref = build_ref_runtime(force)
-    return lib, orc, ref
-
-
 if __name__ == "__main__":
-    force = "--force" in sys.argv
-    verbose = "-v" in sys.argv
-    for p in build_all(force, verbose):
-        print(p)
+    print(build_lib("--force" in sys.argv, "-v" in sys.argv))

@@ -17,12 +17,14 @@ def built():
     """Builds (or reuses) the library and the oracle; returns their paths."""
     sys.path.insert(0, ROOT)
     import importlib.util
-    spec = importlib.util.spec_from_file_location(
-        "omcuda_build", os.path.join(ROOT, "onnx-mlir_b200", "build.py"))
-    mod = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(mod)
-    lib, orc, ref = mod.build_all()
-    return {"lib": lib, "oracle": orc, "ref_runtime": ref}
+    def load(name, path):
+        spec = importlib.util.spec_from_file_location(name, path)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+    lib = load("omcuda_build", os.path.join(ROOT, "onnx-mlir_b200", "build.py")).build_lib()
+    ob = load("oracle_build", os.path.join(ROOT, "oracle", "build.py"))
+    return {"lib": lib, "oracle": ob.build_oracle(), "ref_runtime": ob.build_ref_runtime()}
 
 
 @pytest.fixture(scope="session")

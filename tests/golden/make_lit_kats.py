@@ -1,7 +1,7 @@
 """Extracts known-answer vectors for the quantized path from onnx-mlir's own
 lit tests and writes them to lit_kats.json (committed beside this script).
 
-    python tests/golden/make_lit_kats.py [/path/to/onnx-mlir]
+    python tests/golden/make_lit_kats.py /path/to/onnx-mlir      (or ONNX_MLIR_SRC)
 
 Source: test/mlir/onnx/onnx_constprop.mlir.  Its constant-propagation tests
 fold MatMulInteger and Round on literal operands and FileCheck the folded
@@ -18,7 +18,9 @@ import os
 import re
 import sys
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ONNX_MLIR_SRC")
+if not REF or not os.path.isdir(REF):
+    sys.exit("usage: make_lit_kats.py /path/to/onnx-mlir  (or set ONNX_MLIR_SRC)")
 SRC = os.path.join(REF, "test/mlir/onnx/onnx_constprop.mlir")
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lit_kats.json")
 
