@@ -310,6 +310,147 @@ __global__ void __launch_bounds__(32 * kGemvWarps)
     epi_range_commit(p.out_range, lo, hi);
 }
 
+// ---- GEMV-shaped GEMM for 5..16 rows on mma.sync ---------------------------------
+//
+// From five rows on, the dp4a work per weight byte of the kernel above outgrows
+// the weight read.  This kernel keeps the same shape (a pass over the weight,
+// HBM bound) and hands the arithmetic to mma.sync.m16n8k32: the 16 rows of
+// the A fragment are the (up to) 16 rows of the problem, the 8 columns of the
+// B fragment are 8 adjacent output columns, and a warp consumes the weight in
+// 64-byte blocks of K: lane (g, q) (g = lane / 4 the column, q = lane % 4)
+// loads the 16 bytes at offset 16 q of column g's block straight from global
+// memory into its B registers.  The instruction's own K order is different
+// (lane q holds K bytes 4q..4q+3 and 16+4q..16+4q+3), but a sum over K does not
+// care in which order the bytes are paired as long as A and B agree, so A is
+// loaded with the same permutation (the 16 bytes at offset 16 q of rows g and
+// g + 8) and one 16-byte load feeds two MMAs.  The kGemvMmaWarps warps of a
+// block split K between them and fold their fragments through shared memory;
+// all threads then run the epilogue, consecutive threads on consecutive
+// columns.  Integer sums are exact in any order: bit-identical to the other
+// kernels.
+constexpr int kGemvMmaWarps = 8;
+constexpr int kGemvMmaUnroll = 4; // 64-byte blocks of K in flight per warp
+
+template <bool kASigned, bool kBSigned>
+__device__ __forceinline__ void mma_m16n8k32(int32_t (&c)[4], uint32_t a0,
+    uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  if (kASigned && kBSigned)
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else if (kASigned && !kBSigned)
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else if (!kASigned && kBSigned)
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 "
+                 "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int CG, bool kASigned, bool kBSigned>
+__global__ void __launch_bounds__(32 * kGemvMmaWarps)
+    gemm_i8_gemv_mma_kernel(const uint8_t *__restrict__ A,
+        const uint8_t *__restrict__ Bt, int64_t kp, EpiParams p) {
+  constexpr int kCols = 8 * CG;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, q = lane & 3;
+  const int64_t m0 = (int64_t)blockIdx.y * 16;
+  const bool vec_ok = ((p.K & 15) == 0) && (((uintptr_t)A & 15u) == 0);
+  const int64_t blocks64 = (kp + 63) >> 6;
+  __shared__ int32_t part[kGemvMmaWarps][16][kCols + 1];
+  const EpiScalars sc = epi_scalars(p);
+  float lo = INFINITY, hi = -INFINITY;
+  const int64_t groups = ceil_div(p.N, kCols);
+  for (int64_t grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+    const int64_t n0 = grp * kCols;
+    int32_t acc[CG][4];
+#pragma unroll
+    for (int j = 0; j < CG; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        acc[j][i] = 0;
+    const uint8_t *brow[CG];
+#pragma unroll
+    for (int j = 0; j < CG; ++j) { // columns past N re-read the last one; never stored
+      const int64_t n = n0 + 8 * j + g;
+      brow[j] = Bt + (n < p.N ? n : p.N - 1) * kp + 16 * q;
+    }
+    // Warp w takes runs of kGemvMmaUnroll adjacent blocks (256 bytes of every
+    // column), run r = w, w + kGemvMmaWarps, ...
+    for (int64_t b0 = (int64_t)warp * kGemvMmaUnroll; b0 < blocks64;
+         b0 += (int64_t)kGemvMmaWarps * kGemvMmaUnroll) {
+      uint4 bw[kGemvMmaUnroll][CG];
+#pragma unroll
+      for (int u = 0; u < kGemvMmaUnroll; ++u) {
+        const int64_t koff = ((b0 + u) << 6) + 16 * q;
+#pragma unroll
+        for (int j = 0; j < CG; ++j)
+          bw[u][j] = koff < kp
+                         ? __ldcs(reinterpret_cast<const uint4 *>(brow[j] + ((b0 + u) << 6)))
+                         : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kGemvMmaUnroll; ++u) {
+        const int64_t koff = ((b0 + u) << 6) + 16 * q;
+        const uint4 a_lo = load_a_chunk(A, m0 + g, p.M, p.K, koff, vec_ok);
+        const uint4 a_hi = load_a_chunk(A, m0 + g + 8, p.M, p.K, koff, vec_ok);
+#pragma unroll
+        for (int j = 0; j < CG; ++j) {
+          mma_m16n8k32<kASigned, kBSigned>(
+              acc[j], a_lo.x, a_hi.x, a_lo.y, a_hi.y, bw[u][j].x, bw[u][j].y);
+          mma_m16n8k32<kASigned, kBSigned>(
+              acc[j], a_lo.z, a_hi.z, a_lo.w, a_hi.w, bw[u][j].z, bw[u][j].w);
+        }
+      }
+    }
+    // Accumulator fragment: c0,c1 = row g, columns 2q, 2q+1; c2,c3 = row g + 8.
+#pragma unroll
+    for (int j = 0; j < CG; ++j) {
+      part[warp][g][8 * j + 2 * q] = acc[j][0];
+      part[warp][g][8 * j + 2 * q + 1] = acc[j][1];
+      part[warp][g + 8][8 * j + 2 * q] = acc[j][2];
+      part[warp][g + 8][8 * j + 2 * q + 1] = acc[j][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * kCols; idx += 32 * kGemvMmaWarps) {
+      const int r = idx / kCols, cidx = idx % kCols;
+      const int64_t m = m0 + r, n = n0 + cidx;
+      if (m < p.M && n < p.N) {
+        int32_t sum = 0;
+#pragma unroll
+        for (int w = 0; w < kGemvMmaWarps; ++w)
+          sum += part[w][r][cidx];
+        const EpiRow row = epi_row(p, m);
+        const int32_t v = epi_int(p, row, sum, n);
+        if (p.kind == OMCUDA_EPI_I32) {
+          reinterpret_cast<int32_t *>(p.Y)[m * p.N + n] = v;
+        } else if (p.kind == OMCUDA_EPI_DEQUANT) {
+          float y = epi_dequant(p, sc, v, n);
+          if (p.residual)
+            y = __fadd_rn(y, __ldg(p.residual + m * p.N + n));
+          reinterpret_cast<float *>(p.Y)[m * p.N + n] = y;
+          lo = fminf(lo, y);
+          hi = fmaxf(hi, y);
+        } else {
+          reinterpret_cast<uint8_t *>(p.Y)[m * p.N + n] = (uint8_t)epi_requant(p, sc, v, n);
+        }
+      }
+    }
+    __syncthreads(); // part[] is rewritten by the next group
+  }
+  if (p.out_range && p.kind == OMCUDA_EPI_DEQUANT)
+    epi_range_commit(p.out_range, lo, hi);
+}
+
 EpiParams make_epi_params(const omcudaGemmArgs &a) {
   EpiParams p;
   p.M = a.M;
@@ -399,6 +540,33 @@ static void launch_gemv(const omcudaGemmArgs &a, cudaStream_t st) {
   }
 }
 
+template <int CG>
+static void launch_gemv_mma(const omcudaGemmArgs &a, cudaStream_t st) {
+  EpiParams p = make_epi_params(a);
+  // One block per 8 * CG columns (it reads 8 * CG * K bytes of the weight); very
+  // wide weights wrap around a grid of 16 blocks per SM.
+  const int64_t groups = ceil_div(a.N, 8 * CG), cap = (int64_t)sm_count() * 16;
+  dim3 grid((unsigned)(groups < cap ? groups : cap), (unsigned)ceil_div(a.M, 16));
+  const uint8_t *A = (const uint8_t *)a.A;
+  const uint8_t *Bt = (const uint8_t *)a.B.bt;
+  const int threads = 32 * kGemvMmaWarps;
+  int sel = (a.a_signed ? 2 : 0) | (a.B.b_signed ? 1 : 0);
+  switch (sel) {
+  case 0:
+    gemm_i8_gemv_mma_kernel<CG, false, false><<<grid, threads, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  case 1:
+    gemm_i8_gemv_mma_kernel<CG, false, true><<<grid, threads, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  case 2:
+    gemm_i8_gemv_mma_kernel<CG, true, false><<<grid, threads, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  default:
+    gemm_i8_gemv_mma_kernel<CG, true, true><<<grid, threads, 0, st>>>(A, Bt, a.B.kp, p);
+    break;
+  }
+}
+
 // OMCUDA_GEMV=0 keeps the older warp-per-column kernel for every M, for
 // experiments.
 static bool gemv_wanted() {
@@ -409,10 +577,30 @@ static bool gemv_wanted() {
   return on;
 }
 
+// Largest M the mma.sync GEMV takes (row groups of 16 re-read the weight
+// through L2).  OMCUDA_GEMV_MMA_MAX_M overrides it; 0 switches the kernel off.
+static int64_t gemv_mma_max_m() {
+  static const int64_t v = [] {
+    const char *s = getenv("OMCUDA_GEMV_MMA_MAX_M");
+    return s ? (int64_t)atoll(s) : (int64_t)16;
+  }();
+  return v;
+}
+
+static int64_t gemv_max_m() {
+  if (!gemv_wanted())
+    return 0;
+  return gemv_mma_max_m() > 4 ? gemv_mma_max_m() : 4;
+}
+
 int launch_gemm_simt(const omcudaGemmArgs &a, cudaStream_t st) {
-  // Up to 16 rows when the tensor-core kernel cannot take the shape; the
-  // dispatcher sends tensor-core-capable shapes here only for M <= 4 (with
-  // more rows the dp4a work per weight byte outgrows the weight read).
+  // The GEMV-shaped kernels: dp4a up to 4 rows, mma.sync above (with more
+  // rows the dp4a work per weight byte outgrows the weight read).
+  if (a.M > 4 && a.M <= gemv_mma_max_m() && gemv_wanted()) {
+    launch_gemv_mma<2>(a, st);
+    OMCUDA_CHECK_LAUNCH("gemm_i8_gemv_mma_kernel");
+    return OMCUDA_OK;
+  }
   if (a.M <= 16 && gemv_wanted()) {
     if (a.M <= 1)
       launch_gemv<1, 4>(a, st);
@@ -544,11 +732,10 @@ extern "C" int omcudaDevGemmI8(const omcudaGemmArgs *args, void *stream) {
     return fail(OMCUDA_ENOTSUP,
         "GemmI8: the split-bf16, range-only and quantizing tails exist on the "
         "tensor-core kernel only (K %% 16 == 0, 16-byte aligned A)");
-  // Up to 4 rows the GEMM is one read of the weight, which the GEMV-shaped
-  // SIMT kernel streams faster than a 128-row tensor-core tile on a few SMs
-  // (measured: M = 1 19 us against 23-27 us on the 58 MB weights; at M = 16 the
-  // dp4a work makes it 30-68 us against the tensor-core kernel's 20-37 us).
+  // With a handful of rows the GEMM is one read of the weight, which the
+  // GEMV-shaped kernels stream faster than 128-row tensor-core tiles on a few
+  // SMs (measured: M = 1 19 us against 23-27 us on the 58 MB weights).
   bool use_tc = (a.kernel_choice == 1) || tc_only ||
-                (a.kernel_choice == 0 && tc_ok && a.M > 4);
+                (a.kernel_choice == 0 && tc_ok && a.M > gemv_max_m());
   return use_tc ? launch_gemm_tc(a, st) : launch_gemm_simt(a, st);
 }

@@ -107,9 +107,26 @@ struct omcudaEncoder {
   // a batch (omcudaEncoderSetRangeSync)
   omcudaRangeSyncFn range_sync = nullptr;
   void *range_sync_ctx = nullptr;
+  // Captured runs (CUDA graphs): a run is a fixed sequence of 11 launches per
+  // layer whose arguments depend only on (x, y, batch, seq, stream), so the
+  // second run with the same key is captured and later ones are one graph
+  // launch.  Dropped whenever a buffer a graph points into may have moved.
+  struct Captured {
+    const float *x;
+    float *y;
+    int64_t batch, seq;
+    cudaStream_t st;
+    int seen;             // uncaptured runs so far with this key
+    cudaGraphExec_t exec; // null until captured (or when capture failed)
+    bool failed;
+    int64_t launches;     // kernels in the graph, for the launch counter
+  };
+  std::vector<Captured> captured;
 };
 
 namespace {
+
+void drop_graphs(omcudaEncoder *e);
 
 int upload(DevBuf &dst, const OMTensor *t, size_t bytes, cudaStream_t st) {
   dst.ensure(bytes);
@@ -327,6 +344,7 @@ extern "C" int omcudaEncoderSetLayer(
       (w->ln2_beta && !is_f32_vec(w->ln2_beta, H)))
     return fail(OMCUDA_EINVAL, "EncoderSetLayer: bias / LayerNorm shapes");
   cudaStream_t st = current_stream();
+  drop_graphs(e); // captured runs hold the old weights' addresses
   LayerState &L = e->layers[(size_t)layer];
   int rc = OMCUDA_OK;
   // [Wq | Wk | Wv] as one [H, 3H] operand
@@ -408,6 +426,29 @@ extern "C" int omcudaEncoderSetLayer(
   return OMCUDA_OK;
 }
 
+namespace {
+
+void drop_graphs(omcudaEncoder *e) {
+  for (auto &c : e->captured)
+    if (c.exec)
+      cudaGraphExecDestroy(c.exec);
+  e->captured.clear();
+}
+
+// OMCUDA_ENCODER_GRAPH=0 launches every run kernel by kernel.
+bool graphs_wanted() {
+  static const bool on = [] {
+    const char *s = getenv("OMCUDA_ENCODER_GRAPH");
+    return !(s && atoi(s) == 0);
+  }();
+  return on;
+}
+
+int run_launches(omcudaEncoder *e, const float *x, int64_t batch, int64_t seq, float *y,
+    cudaStream_t st);
+
+} // namespace
+
 extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
     int64_t batch, int64_t seq, float *y, void *stream) {
   if (!e || !x || !y || batch <= 0 || seq <= 0)
@@ -415,12 +456,85 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
   for (auto &L : e->layers)
     if (!L.set)
       return fail(OMCUDA_EINVAL, "EncoderRun: a layer has no weights");
-  const int64_t H = e->cfg.hidden, F = e->cfg.ffn, heads = e->cfg.heads;
-  const int64_t dh = H / heads, T = batch * seq;
   cudaStream_t st = (cudaStream_t)stream;
-  int rc = ensure_workspace(e, T, st);
+  const int64_t tokens_before = e->tokens;
+  int rc = ensure_workspace(e, batch * seq, st);
   if (rc != OMCUDA_OK)
     return rc;
+  if (e->tokens != tokens_before)
+    drop_graphs(e); // the workspace moved
+  // Runs that call back to the host (range sync), copy intermediates out (tap)
+  // or record events between launches (profiling) are not captured.
+  if (!graphs_wanted() || e->tap || e->range_sync || e->profiling)
+    return run_launches(e, x, batch, seq, y, st);
+  omcudaEncoder::Captured *c = nullptr;
+  for (auto &k : e->captured)
+    if (k.x == x && k.y == y && k.batch == batch && k.seq == seq && k.st == st)
+      c = &k;
+  if (!c) {
+    if (e->captured.size() >= 8)
+      drop_graphs(e);
+    e->captured.push_back({x, y, batch, seq, st, 0, nullptr, false, 0});
+    c = &e->captured.back();
+  }
+  if (c->exec) {
+    OMCUDA_CHECK(cudaGraphLaunch(c->exec, st));
+    count_launch((int)c->launches);
+    return OMCUDA_OK;
+  }
+  if (c->failed || c->seen < 1) {
+    // The first run with a key goes kernel by kernel: it performs the one-time
+    // set-up of the launchers (function attributes, the status word), which
+    // must not happen inside a capture.
+    ++c->seen;
+    return run_launches(e, x, batch, seq, y, st);
+  }
+  cudaStreamCaptureStatus busy = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &busy) != cudaSuccess || busy != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return run_launches(e, x, batch, seq, y, st); // the caller is capturing: join its graph
+  }
+  const int64_t before = omcudaLaunchCount();
+  if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    (void)cudaGetLastError();
+    c->failed = true;
+    return run_launches(e, x, batch, seq, y, st);
+  }
+  rc = run_launches(e, x, batch, seq, y, st);
+  cudaGraph_t graph = nullptr;
+  cudaError_t ce = cudaStreamEndCapture(st, &graph);
+  const int64_t captured_launches = omcudaLaunchCount() - before;
+  count_launch((int)-captured_launches); // nothing ran yet
+  if (rc != OMCUDA_OK || ce != cudaSuccess || !graph) {
+    (void)cudaGetLastError();
+    if (graph)
+      cudaGraphDestroy(graph);
+    c->failed = true;
+    if (rc != OMCUDA_OK)
+      return rc;
+    return run_launches(e, x, batch, seq, y, st);
+  }
+  ce = cudaGraphInstantiate(&c->exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (ce != cudaSuccess) {
+    (void)cudaGetLastError();
+    c->exec = nullptr;
+    c->failed = true;
+    return run_launches(e, x, batch, seq, y, st);
+  }
+  c->launches = captured_launches;
+  OMCUDA_CHECK(cudaGraphLaunch(c->exec, st));
+  count_launch((int)c->launches);
+  return OMCUDA_OK;
+}
+
+namespace {
+
+int run_launches(omcudaEncoder *e, const float *x, int64_t batch, int64_t seq, float *y,
+    cudaStream_t st) {
+  const int64_t H = e->cfg.hidden, F = e->cfg.ffn, heads = e->cfg.heads;
+  const int64_t dh = H / heads, T = batch * seq;
+  int rc = OMCUDA_OK;
   const float att_scale = 1.0f / sqrtf((float)dh);
   const float eps = (float)e->cfg.epsilon;
   const int64_t nranges = 4 * e->cfg.layers + 1;
@@ -567,6 +681,8 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
 #undef SYNC_RANGE
   return OMCUDA_OK;
 }
+
+} // namespace
 
 extern "C" OMTensorList *omcudaEncoderRun(omcudaEncoder *e, OMTensorList *inputs) {
   if (sticky_error() || ensure_init() != OMCUDA_OK)
@@ -816,6 +932,7 @@ extern "C" void omcudaEncoderDestroy(omcudaEncoder *e) {
     return;
   if (OMIsInitAccelCUDA)
     cudaStreamSynchronize(current_stream());
+  drop_graphs(e);
   for (cudaEvent_t ev : e->ev)
     cudaEventDestroy(ev);
   for (auto &sl : e->slot) {

@@ -111,21 +111,28 @@ def test_pipelined_submit_equals_run_into(gpu):
     layers = make_encoder(13, H, F, 2)
     enc = gpu.Encoder(H, heads, F, layers)
     rng = np.random.default_rng(14)
-    xs = [rng.normal(size=(B, S, H)).astype(np.float32) * (1 + i) for i in range(5)]
+    # (seven batches over two staging slots: the first run of a slot goes
+    # kernel by kernel, the second is captured as a CUDA graph, the later ones
+    # replay it -- all must give the synchronous call's bytes)
+    xs = [rng.normal(size=(B, S, H)).astype(np.float32) * (1 + i) for i in range(7)]
     want = []
     for x in xs:
         y = np.zeros((B, S, H), np.float32)
         enc.run_into(gpu.Tensor.from_numpy(x), gpu.Tensor.from_numpy(y))
         want.append(y)
     ys = [np.zeros((B, S, H), np.float32) for _ in xs]
-    keep = []
+    keep, counts = [], [gpu.launch_count()]
     for x, y in zip(xs, ys):
         tx, ty = gpu.Tensor.from_numpy(x), gpu.Tensor.from_numpy(y)
         keep.append((tx, ty))
         enc.submit(tx, ty)
+        counts.append(gpu.launch_count())
     enc.wait()
     for y, w in zip(ys, want):
         assert np.array_equal(y, w)
+    # a replayed run counts the launches it replays
+    per_run = np.diff(counts)
+    assert per_run[0] > 0 and (per_run == per_run[0]).all(), per_run
     # a larger batch afterwards grows the staging buffers
     x = rng.normal(size=(2 * B, S, H)).astype(np.float32)
     y, w = np.zeros_like(x), np.zeros_like(x)

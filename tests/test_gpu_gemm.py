@@ -71,6 +71,26 @@ def test_signedness_and_zero_point_forms(gpu, orc, adt, bdt, choice):
         assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("choice", [0, 2], ids=["auto", "simt"])
+@pytest.mark.parametrize("adt,bdt", [(np.uint8, np.uint8), (np.int8, np.int8),
+                                     (np.int8, np.uint8), (np.uint8, np.int8)])
+def test_gemv_shaped_rows_1_to_16(gpu, orc, adt, bdt, choice):
+    # The GEMV-shaped kernels (dp4a up to 4 rows, mma.sync m16n8k32 with a
+    # permuted K order above): ragged M, K (not a multiple of 16 / of the
+    # 64-byte block / of a warp's run of blocks) and N (not a multiple of the
+    # 16 columns of a block), every signedness and zero-point form.
+    rng = np.random.default_rng(41)
+    dg = DevGemm(gpu)
+    for M, K, N in [(1, 100, 33), (3, 1040, 17), (5, 7, 3), (8, 64, 16), (9, 144, 40),
+                    (13, 2000, 70), (16, 4160, 136), (16, 2048, 1000)]:
+        A, B = rand8(rng, (M, K), adt), rand8(rng, (K, N), bdt)
+        for az, bz in [(None, None), (rand8(rng, 1, adt), None),
+                       (rand8(rng, M, adt), rand8(rng, N, bdt))]:
+            want = orc.matmul_integer_2d(A, B, az, bz)
+            got = dg.matmul_integer(A, B, az, bz, choice)
+            assert np.array_equal(got, want), (M, K, N, np.argwhere(got != want)[:8])
+
+
 def test_matmul_integer_api_shapes(gpu, orc):
     rng = np.random.default_rng(12)
     # 3-D A times 2-D B (the encoder's broadcast-A form), host and device tensors
@@ -370,7 +390,8 @@ def test_whole_output_checksums(gpu, orc, M, K, N):
     As = A.astype(np.int64) - 117
     assert np.array_equal(Y.astype(np.int64).sum(0), As.sum(0) @ B.astype(np.int64))
 
-@pytest.mark.parametrize("M,K,N,choice", [(300, 256, 192, 1), (260, 512, 1000, 1), (3, 100, 70, 2)])
+@pytest.mark.parametrize("M,K,N,choice", [(300, 256, 192, 1), (260, 512, 1000, 1), (3, 100, 70, 2),
+                                          (13, 200, 70, 2), (16, 1040, 136, 0)])
 def test_dequant_tail_with_residual(gpu, M, K, N, choice):
     # y = tail(acc) + residual, the onnx.Add of a residual connection folded
     # into the GEMM: one more separately rounded fp32 add, so it must equal
