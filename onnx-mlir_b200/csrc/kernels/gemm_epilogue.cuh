@@ -63,6 +63,12 @@ struct EpiParams {
   // stores evict_first, bit 1 A loads evict_first, bit 2 B loads evict_last.
   int l2_hints;
   int quant_mode; // OMCUDA_MODE_* flags for the quantizing tail
+  // Split-K pass of the tensor-core kernels: a work unit is one of split_k
+  // slices of a tile's K loop and stores its raw sums (EPI_I32 without zero
+  // points) into rows [slice * ws_rows, slice * ws_rows + M) of a workspace;
+  // splitk_reduce_kernel adds the slices and runs the real tail.  1: off.
+  int split_k;
+  int64_t ws_rows;
 };
 
 // Host: flattens the public argument block (gemm_simt.cu).

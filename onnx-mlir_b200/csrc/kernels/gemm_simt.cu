@@ -310,10 +310,10 @@ __global__ void __launch_bounds__(32 * kGemvWarps)
     epi_range_commit(p.out_range, lo, hi);
 }
 
-// ---- GEMV-shaped GEMM for 5..16 rows on mma.sync ---------------------------------
+// ---- GEMV-shaped GEMM for 2..16 rows on mma.sync ---------------------------------
 //
-// From five rows on, the dp4a work per weight byte of the kernel above outgrows
-// the weight read.  This kernel keeps the same shape (a pass over the weight,
+// With more than one row the dp4a work per weight byte of the kernel above
+// starts to outgrow the weight read.  This kernel keeps the same shape (a pass over the weight,
 // HBM bound) and hands the arithmetic to mma.sync.m16n8k32: the 16 rows of
 // the A fragment are the (up to) 16 rows of the problem, the 8 columns of the
 // B fragment are 8 adjacent output columns, and a warp consumes the weight in
@@ -487,6 +487,8 @@ EpiParams make_epi_params(const omcudaGemmArgs &a) {
   p.line_store = 0;
   p.l2_hints = 0;
   p.quant_mode = quant_mode();
+  p.split_k = 1;
+  p.ws_rows = 0;
   return p;
 }
 
@@ -596,7 +598,14 @@ static int64_t gemv_max_m() {
 int launch_gemm_simt(const omcudaGemmArgs &a, cudaStream_t st) {
   // The GEMV-shaped kernels: dp4a up to 4 rows, mma.sync above (with more
   // rows the dp4a work per weight byte outgrows the weight read).
-  if (a.M > 4 && a.M <= gemv_mma_max_m() && gemv_wanted()) {
+  // (OMCUDA_GEMV_MMA_MIN_M moves the hand-over from the dp4a kernel, for
+  // experiments: measured on 4096 x 14336 the dp4a kernel reads one row's
+  // weight in 19 us and four rows' in 29 us, the mma.sync kernel 22 and 24 us.)
+  static const int64_t mma_min_m = [] {
+    const char *s = getenv("OMCUDA_GEMV_MMA_MIN_M");
+    return s ? (int64_t)atoll(s) : (int64_t)2;
+  }();
+  if (a.M >= mma_min_m && a.M <= gemv_mma_max_m() && gemv_wanted()) {
     launch_gemv_mma<2>(a, st);
     OMCUDA_CHECK_LAUNCH("gemm_i8_gemv_mma_kernel");
     return OMCUDA_OK;

@@ -319,7 +319,8 @@ template <int BN, int EPI, int EW, typename Release>
 __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
     const EpiScalars &sc, const QuantConsts &qc, uint32_t taddr, int64_t m_warp,
     int64_t n0, uint32_t slab0, int lane, bool use_slab, float &lo, float &hi,
-    const CUtensorMap *map_y, const CUtensorMap *map_y2, Release &&release) {
+    const CUtensorMap *map_y, const CUtensorMap *map_y2, Release &&release,
+    int32_t store_row_off = 0) {
   const bool hint_store = (p.l2_hints & 1) != 0;
   const uint64_t pol_out = hint_store ? l2_policy_evict_first() : 0;
   // EPI_DEQUANT_SPLIT stages like the 4-byte tails (32 columns per 128-byte
@@ -416,11 +417,11 @@ __device__ __forceinline__ void epilogue_tile(const EpiParams &p,
       __syncwarp();
       if (lane == 0 && warp_in && ng < p.N) {
         if (hint_store) {
-          tma_store_2d_hint(map_y, slab0, (int32_t)ng, (int32_t)m_warp, pol_out);
+          tma_store_2d_hint(map_y, slab0, (int32_t)ng, (int32_t)m_warp + store_row_off, pol_out);
           if (kSplit)
             tma_store_2d_hint(map_y2, slab0 + 2048u, (int32_t)ng, (int32_t)m_warp, pol_out);
         } else {
-          tma_store_2d(map_y, slab0, (int32_t)ng, (int32_t)m_warp);
+          tma_store_2d(map_y, slab0, (int32_t)ng, (int32_t)m_warp + store_row_off);
           if (kSplit)
             tma_store_2d(map_y2, slab0 + 2048u, (int32_t)ng, (int32_t)m_warp);
         }
@@ -511,8 +512,11 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 
   const int64_t tiles_m = ceil_div(p.M, kBM);
   const int64_t tiles_n = ceil_div(p.N, BN);
-  const int64_t num_tiles = tiles_m * tiles_n;
   const int num_kb = (int)ceil_div(p.K, kBK);
+  // Work units: tiles, or (split-K pass) the split_k K slices of every tile,
+  // slices of one tile next to each other.
+  const int split = p.split_k;
+  const int64_t num_units = tiles_m * tiles_n * split;
 
   if (threadIdx.x == 32) { // (a thread that has nothing else to set up)
     prefetch_tensormap(&map_a);
@@ -550,10 +554,14 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       uint32_t phase = 0;
       bool ok = true;
       const uint64_t pol_a = l2_policy_evict_first(), pol_b = l2_policy_evict_last();
-      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int64_t u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        const int64_t t = split > 1 ? u / split : u;
+        const int ks = split > 1 ? (int)(u % split) : 0;
+        const int kb0 = (int)((int64_t)ks * num_kb / split);
+        const int kb1 = (int)((int64_t)(ks + 1) * num_kb / split);
         const int32_t m0 = (int32_t)((t / tiles_n) * kBM);
         const int32_t n0 = (int32_t)((t % tiles_n) * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, wait_ns)) {
             ok = false;
             break;
@@ -588,7 +596,10 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       // MMA issue, commit); whether a stage has landed is therefore asked one
       // stage ahead, before the MMAs of the current stage are issued.
       bool landed = false;
-      for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+      for (int64_t u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++it) {
+        const int ks = split > 1 ? (int)(u % split) : 0;
+        const int kb0 = (int)((int64_t)ks * num_kb / split);
+        const int kb1 = (int)((int64_t)(ks + 1) * num_kb / split);
         const int buf = (int)(it & 1);
         const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
         if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp, wait_ns)) {
@@ -597,7 +608,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!landed && !mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, wait_ns)) {
             ok = false;
             break;
@@ -610,7 +621,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           const uint32_t sb = sa + Cfg::kABytes;
           static_assert(kBK / kUmmaK == 4, "four K slices per stage");
           umma_i8_x4(d_tmem, make_smem_desc(sa), make_smem_desc(sb), idesc,
-              kb != 0 ? 1u : 0u);
+              kb != kb0 ? 1u : 0u);
           umma_commit(smem_u32(&bar_empty[stage]));
           stage = nstage;
           phase = nphase;
@@ -632,7 +643,9 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
     bool ok = active;
     int64_t it = 0;
     float lo = INFINITY, hi = -INFINITY; // range of this warp's f32 outputs
-    for (int64_t t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+    for (int64_t u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++it) {
+      const int64_t t = split > 1 ? u / split : u;
+      const int32_t row_off = split > 1 ? (int32_t)((u % split) * p.ws_rows) : 0;
       const int buf = (int)(it & 1);
       const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
       const int64_t m_warp = (t / tiles_n) * kBM + quad * 32;
@@ -676,7 +689,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
             __syncwarp();
             if (lane == 0)
               mbar_arrive(smem_u32(&bar_acc_empty[buf]));
-          });
+          }, row_off);
     }
     // One commit of the running range per warp, and every store of this warp
     // complete before the CTA may exit.
@@ -776,6 +789,9 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
 
   const int64_t tiles_n = ceil_div(p.N, BN);
   const int num_kb = (int)ceil_div(p.K, kBK);
+  // Split-K pass: unit u is K slice u % split of tile u / split (all units
+  // whole tiles then).
+  const int split = p.split_k;
   if (threadIdx.x == 32) { // (a thread that has nothing else to set up)
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -815,14 +831,17 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       const uint64_t pol_a = l2_policy_evict_first(), pol_b = l2_policy_evict_last();
       for (int64_t u = cluster_id; u < num_units && ok; u += num_clusters) {
         const PairUnit un = pair_unit(u, full_units);
-        const int64_t t = un.tile;
+        const int64_t t = split > 1 ? un.tile / split : un.tile;
+        const int ks = split > 1 ? (int)(un.tile % split) : 0;
+        const int kb0 = (int)((int64_t)ks * num_kb / split);
+        const int kb1 = (int)((int64_t)(ks + 1) * num_kb / split);
         const int32_t m0 = (int32_t)((t / tiles_n) * (2 * kBM) + rank * kBM);
         // this CTA's share of the B columns: 128 of 256, or 64 of 128
         const int32_t n0 = un.narrow
                                ? (int32_t)((t % tiles_n) * BN + un.half * (BN / 2) + rank * (BN / 4))
                                : (int32_t)((t % tiles_n) * BN + rank * (BN / 2));
         const uint32_t stage_tx = un.narrow ? kABytes + kBHalfBytes / 2 : kStageBytes;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, wait_ns)) {
             ok = false;
             break;
@@ -858,6 +877,9 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       bool landed = false; // asked one stage ahead, see the single-CTA kernel
       for (int64_t u = cluster_id; u < num_units && ok; u += num_clusters, ++it) {
         const uint32_t unit_idesc = u < full_units ? idesc : idesc_half;
+        const int ks = split > 1 ? (int)(u % split) : 0;
+        const int kb0 = (int)((int64_t)ks * num_kb / split);
+        const int kb1 = (int)((int64_t)(ks + 1) * num_kb / split);
         const int buf = (int)(it & 1);
         const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
         if (!mbar_wait(smem_u32(&bar_acc_empty[buf]), acc_phase ^ 1u, abortp, wait_ns)) {
@@ -866,7 +888,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
         }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!landed && !mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, wait_ns)) {
             ok = false;
             break;
@@ -879,7 +901,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
           const uint32_t sb = sa + kABytes;
           static_assert(kBK / kUmmaK == 4, "four K slices per stage");
           umma_i8_pair_x4(d_tmem, make_smem_desc(sa), make_smem_desc(sb), unit_idesc,
-              kb != 0 ? 1u : 0u);
+              kb != kb0 ? 1u : 0u);
           umma_commit_pair(smem_u32(&bar_empty[stage]), 3);
           stage = nstage;
           phase = nphase;
@@ -903,7 +925,8 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
     float lo = INFINITY, hi = -INFINITY; // range of this warp's f32 outputs
     for (int64_t u = cluster_id; u < num_units && ok; u += num_clusters, ++it) {
       const PairUnit un = pair_unit(u, full_units);
-      const int64_t t = un.tile;
+      const int64_t t = split > 1 ? un.tile / split : un.tile;
+      const int32_t row_off = split > 1 ? (int32_t)((un.tile % split) * p.ws_rows) : 0;
       const int buf = (int)(it & 1);
       const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
       const int64_t m_warp = (t / tiles_n) * (2 * kBM) + rank * kBM + quad * 32;
@@ -947,7 +970,7 @@ __global__ void __launch_bounds__(tc_threads(EW), 1)
       };
       if (mine)
         epilogue_tile<BN, EPI, EW>(p, sc, qc, taddr, m_warp, n0, slab0, lane, use_slab,
-            lo, hi, &map_y, &map_y2, release);
+            lo, hi, &map_y, &map_y2, release, row_off);
       else
         release();
     }
@@ -1121,8 +1144,102 @@ inline int l2_hints_wanted() {
   return v;
 }
 
+// ---- split-K -------------------------------------------------------------------------
+//
+// A GEMM with few output tiles and a long K loop leaves most SMs idle, and the
+// ones that work are bound by how fast one SM takes operands in.  Split-K
+// deals the K loop of every tile to `split` work units; each stores its raw
+// 32-bit sums into its own slice of a workspace (the EPI_I32 tail without zero
+// points, through the same TMA stores), and splitk_reduce_kernel adds the
+// slices and runs the real tail.  Integer sums are exact in any order, so the
+// result equals the unsplit kernel's bit for bit.
+struct SplitPlan {
+  int split = 1;
+  int64_t ws_rows = 0;   // rows per slice: M rounded up to the 32 rows of a store slab
+  int32_t *ws = nullptr; // [split][ws_rows][N]
+};
+
+// One thread per four adjacent outputs of a row.
+__global__ void __launch_bounds__(256)
+    splitk_reduce_kernel(const int32_t *__restrict__ ws, int split, int64_t ws_rows,
+        EpiParams p) {
+  const int64_t n4 = p.N >> 2; // the split path requires N % 4 == 0
+  const int64_t total = p.M * n4;
+  const EpiScalars sc = epi_scalars(p);
+  float lo = INFINITY, hi = -INFINITY;
+  const bool y16 = (((uintptr_t)p.Y) & 15u) == 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / n4, n = (i - m * n4) << 2;
+    int4 acc = make_int4(0, 0, 0, 0);
+    for (int k = 0; k < split; ++k) {
+      const int4 v = __ldcs(reinterpret_cast<const int4 *>(
+          ws + ((int64_t)k * ws_rows + m) * p.N + n));
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    const EpiRow row = epi_row(p, m);
+    const int32_t v[4] = {epi_int(p, row, acc.x, n), epi_int(p, row, acc.y, n + 1),
+        epi_int(p, row, acc.z, n + 2), epi_int(p, row, acc.w, n + 3)};
+    if (p.kind == OMCUDA_EPI_I32) {
+      int32_t *dst = reinterpret_cast<int32_t *>(p.Y) + m * p.N + n;
+      if (y16)
+        *reinterpret_cast<int4 *>(dst) = make_int4(v[0], v[1], v[2], v[3]);
+      else
+        for (int j = 0; j < 4; ++j)
+          dst[j] = v[j];
+    } else if (p.kind == OMCUDA_EPI_DEQUANT) {
+      float y[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        y[j] = epi_dequant(p, sc, v[j], n + j);
+        if (p.residual)
+          y[j] = __fadd_rn(y[j], __ldg(p.residual + m * p.N + n + j));
+        lo = fminf(lo, y[j]);
+        hi = fmaxf(hi, y[j]);
+      }
+      float *dst = reinterpret_cast<float *>(p.Y) + m * p.N + n;
+      if (y16)
+        *reinterpret_cast<float4 *>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+      else
+        for (int j = 0; j < 4; ++j)
+          dst[j] = y[j];
+    } else { // OMCUDA_EPI_REQUANT
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        w |= epi_requant(p, sc, v[j], n + j) << (8 * j);
+      uint8_t *dst = reinterpret_cast<uint8_t *>(p.Y) + m * p.N + n;
+      if ((((uintptr_t)dst) & 3u) == 0)
+        *reinterpret_cast<uint32_t *>(dst) = w;
+      else
+        for (int j = 0; j < 4; ++j)
+          dst[j] = (uint8_t)(w >> (8 * j));
+    }
+  }
+  if (p.out_range && p.kind == OMCUDA_EPI_DEQUANT)
+    epi_range_commit(p.out_range, lo, hi);
+}
+
+// The arguments of the pass that produces the raw partial sums.
+omcudaGemmArgs split_pass_args(const omcudaGemmArgs &a, const SplitPlan &plan) {
+  omcudaGemmArgs r = a;
+  r.epilogue = OMCUDA_EPI_I32;
+  r.a_zp = nullptr;
+  r.a_zp_len = 0;
+  r.b_zp = nullptr;
+  r.b_zp_len = 0;
+  r.a_rowsum = nullptr;
+  r.residual = nullptr;
+  r.out_minmax = nullptr;
+  r.Y = plan.ws;
+  return r;
+}
+
 template <int BN, int EPI, int EW>
-int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
+int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st, const SplitPlan &plan = SplitPlan()) {
   using Cfg = TcConfig<BN, EW>;
   static PerDeviceInt attr_set;
   if (!attr_set.get()) {
@@ -1140,14 +1257,19 @@ int launch_bn_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   EpiParams p = make_epi_params(a);
   p.line_store = y_takes_line_stores<EPI>(a);
   p.l2_hints = l2_hints_wanted();
+  p.split_k = plan.split;
+  p.ws_rows = plan.ws_rows;
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
   CUtensorMap map_y, map_y2;
-  rc = make_y_maps<EPI>(a, epi_cols_per_warp(BN, EW), p.line_store != 0, &map_y, &map_y2);
+  omcudaGemmArgs ya = a; // the matrix the stores see: all slices of the workspace
+  if (plan.split > 1)
+    ya.M = plan.split * plan.ws_rows;
+  rc = make_y_maps<EPI>(ya, epi_cols_per_warp(BN, EW), p.line_store != 0, &map_y, &map_y2);
   if (rc != OMCUDA_OK)
     return rc;
-  int64_t tiles = ceil_div(a.M, kBM) * ceil_div(a.N, BN);
+  int64_t tiles = ceil_div(a.M, kBM) * ceil_div(a.N, BN) * plan.split;
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());
   uint32_t idesc = make_idesc(a.a_signed, a.B.b_signed, BN);
   gemm_i8_tc_kernel<BN, EPI, EW><<<grid, tc_threads(EW), Cfg::kSmemBytes, st>>>(
@@ -1207,7 +1329,7 @@ inline bool pair_half_tiles_wanted() {
 
 // The 2-CTA kernel: 256 x 256 tiles on clusters of two CTAs.
 template <int EPI, int EW>
-int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
+int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st, const SplitPlan &plan = SplitPlan()) {
   constexpr int kThreads = tc_threads(EW);
   constexpr int kPairSmemBytes =
       tc_stages(kBM * kBK + 128 * kBK, EW) * (kBM * kBK + 128 * kBK) +
@@ -1247,15 +1369,19 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   EpiParams p = make_epi_params(a);
   p.line_store = y_takes_line_stores<EPI>(a);
   p.l2_hints = l2_hints_wanted();
+  p.split_k = plan.split;
+  p.ws_rows = plan.ws_rows;
   int *status = tc_status_word();
   if (!status)
     return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the status word");
-  int64_t tiles = ceil_div(a.M, 2 * kBM) * ceil_div(a.N, 256);
+  int64_t tiles = ceil_div(a.M, 2 * kBM) * ceil_div(a.N, 256) * plan.split;
   // Units: whole tiles for the complete rounds; a last round that would keep
-  // at most half of the clusters busy runs as twice as many half tiles.
+  // at most half of the clusters busy runs as twice as many half tiles
+  // (never in a split-K pass, whose units are K slices of whole tiles).
   const int64_t rounds_full = (tiles / max_clusters) * max_clusters;
   const int64_t rest = tiles - rounds_full;
-  const bool split_rest = rest > 0 && 2 * rest <= max_clusters && pair_half_tiles_wanted();
+  const bool split_rest = plan.split == 1 && rest > 0 && 2 * rest <= max_clusters &&
+                          pair_half_tiles_wanted();
   const int64_t full_units = split_rest ? rounds_full : tiles;
   const int64_t num_units = split_rest ? rounds_full + 2 * rest : tiles;
   int clusters = (int)(num_units < max_clusters ? num_units : max_clusters);
@@ -1277,7 +1403,10 @@ int launch_pair_epi_ew(const omcudaGemmArgs &a, cudaStream_t st) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   CUtensorMap map_y, map_y2;
-  rc = make_y_maps<EPI>(a, epi_cols_per_warp(256, EW), p.line_store != 0, &map_y, &map_y2);
+  omcudaGemmArgs ya = a; // the matrix the stores see: all slices of the workspace
+  if (plan.split > 1)
+    ya.M = plan.split * plan.ws_rows;
+  rc = make_y_maps<EPI>(ya, epi_cols_per_warp(256, EW), p.line_store != 0, &map_y, &map_y2);
   if (rc != OMCUDA_OK)
     return rc;
   OMCUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_i8_tc2_kernel<EPI, EW>, map_a, map_b,
@@ -1312,6 +1441,87 @@ int launch_pair(const omcudaGemmArgs &a, cudaStream_t st) {
   }
 }
 
+// OMCUDA_GEMM_SPLIT_K=0 switches split-K off, N > 1 forces N slices wherever
+// the shape allows it (experiments).
+inline int split_k_forced() {
+  static const int v = [] {
+    const char *s = getenv("OMCUDA_GEMM_SPLIT_K");
+    return s ? atoi(s) : -1;
+  }();
+  return v;
+}
+
+// How many K slices a GEMM of up to 512 rows should run as (1: none).  The
+// partial pass uses 128 x 256 tiles on single CTAs up to 128 rows and 256 x
+// 256 tiles on CTA pairs above.  The second launch and the round trip of the
+// partial sums through L2 cost about 6 us, so it pays only when those tiles
+// would occupy at most half of the machine and the K loop is long (measured
+// with 32..512 rows: K = 14336, N = 4096 29-36 us against 43-45 us unsplit;
+// K = 4096 20-37 us against 19-27 us, so K below 8192 stays unsplit).
+int split_k_for(const omcudaGemmArgs &a, cudaStream_t st) {
+  if (split_k_forced() == 0 || a.M > 512 || a.N < 256 || (a.N & 3) != 0)
+    return 1;
+  if (a.epilogue != OMCUDA_EPI_I32 && a.epilogue != OMCUDA_EPI_DEQUANT &&
+      a.epilogue != OMCUDA_EPI_REQUANT)
+    return 1;
+  const int64_t num_kb = ceil_div(a.K, kBK);
+  if (num_kb < 64 && split_k_forced() <= 1)
+    return 1;
+  const bool pair = a.M > kBM;
+  const int64_t units = (pair ? ceil_div(a.M, 2 * kBM) : 1) * ceil_div(a.N, 256);
+  const int64_t slots = pair ? sm_count() / 2 : sm_count();
+  int64_t split = slots / units;
+  if (split_k_forced() > 1)
+    split = split_k_forced();
+  if (split > num_kb / 4)
+    split = num_kb / 4;
+  if (split > 16)
+    split = 16;
+  if (split < 2)
+    return 1;
+  // The workspace comes from the stream-ordered pool, whose bookkeeping
+  // (an event per freed block) must not run inside a stream capture.
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return 1;
+  }
+  return (int)split;
+}
+
+int launch_split_k(const omcudaGemmArgs &a, cudaStream_t st, int split) {
+  SplitPlan plan;
+  plan.split = split;
+  plan.ws_rows = (a.M + 31) & ~int64_t(31);
+  const size_t ws_bytes = (size_t)split * (size_t)plan.ws_rows * (size_t)a.N * sizeof(int32_t);
+  plan.ws = static_cast<int32_t *>(pool_alloc_on(ws_bytes, st));
+  if (!plan.ws)
+    return fail(OMCUDA_ENOMEM, "GemmI8: cannot allocate the split-K workspace");
+  const omcudaGemmArgs part = split_pass_args(a, plan);
+  int rc;
+  if (a.M > kBM)
+    rc = want_wide_epilogue(a) ? launch_pair_epi_ew<OMCUDA_EPI_I32, 16>(part, st, plan)
+                               : launch_pair_epi_ew<OMCUDA_EPI_I32, 8>(part, st, plan);
+  else
+    rc = want_wide_epilogue(a) ? launch_bn_epi_ew<256, OMCUDA_EPI_I32, 16>(part, st, plan)
+                               : launch_bn_epi_ew<256, OMCUDA_EPI_I32, 8>(part, st, plan);
+  if (rc == OMCUDA_OK) {
+    const EpiParams p = make_epi_params(a);
+    const int64_t total = a.M * (a.N >> 2);
+    const int64_t blocks = ceil_div(total, 256);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    splitk_reduce_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(
+        plan.ws, split, plan.ws_rows, p);
+    cudaError_t ce = cudaGetLastError();
+    if (ce != cudaSuccess)
+      rc = fail(OMCUDA_ECUDA, "splitk_reduce_kernel: %s", cudaGetErrorString(ce));
+    else
+      count_launch();
+  }
+  pool_free_on(plan.ws, st);
+  return rc;
+}
+
 } // namespace
 
 bool gemm_tc_supported(const omcudaGemmArgs &a) {
@@ -1328,6 +1538,11 @@ int launch_gemm_tc(const omcudaGemmArgs &a, cudaStream_t st) {
     const char *s = getenv("OMCUDA_GEMM_BN");
     return s ? atoi(s) : 0;
   }();
+  if (forced_bn == 0 || split_k_forced() > 1) {
+    const int split = split_k_for(a, st);
+    if (split > 1)
+      return launch_split_k(a, st, split);
+  }
   if (forced_bn == 512)
     return launch_pair(a, st);
   if (forced_bn == 256)
@@ -1338,8 +1553,13 @@ int launch_gemm_tc(const omcudaGemmArgs &a, cudaStream_t st) {
     return launch_bn<64>(a, st);
   const int64_t tm = ceil_div(a.M, kBM);
   const int sms = sm_count();
-  // Enough 256 x 256 tiles to occupy every pair of SMs: the 2-CTA kernel.
-  if (a.N > 128 && ceil_div(a.M, 2 * kBM) * ceil_div(a.N, 256) >= sms / 2)
+  // Enough 256 x 256 tiles to occupy the pairs of SMs (three quarters of them
+  // will do when both CTAs of a pair have rows to work on): the 2-CTA kernel.
+  // (256 x 4096 x 14336: 56 tiles on 74 pairs run 32.6 us, the 224 tiles of
+  // 128 x 128 in one and a half rounds 37.1 us; with 128 rows or fewer the
+  // single-CTA tiles win, 26 against 31 us.)
+  const int64_t pair_tiles = ceil_div(a.M, 2 * kBM) * ceil_div(a.N, 256);
+  if (a.N > 128 && (pair_tiles >= sms / 2 || (a.M > kBM && pair_tiles * 4 >= (sms / 2) * 3)))
     return launch_pair(a, st);
   if (a.N > 128 && tm * ceil_div(a.N, 256) >= sms)
     return launch_bn<256>(a, st);

@@ -91,6 +91,37 @@ def test_gemv_shaped_rows_1_to_16(gpu, orc, adt, bdt, choice):
             assert np.array_equal(got, want), (M, K, N, np.argwhere(got != want)[:8])
 
 
+@pytest.mark.parametrize("M,K,N", [(17, 8192, 256), (100, 8208, 260), (128, 16384, 512),
+                                   (129, 8192, 512), (300, 8208, 768), (512, 9216, 1024)])
+def test_split_k_shapes(gpu, orc, M, K, N):
+    # Up to 512 rows, with few output tiles and K of 8192 or more, the
+    # tensor-core kernels deal each tile's K loop to several work units (raw partial sums through a
+    # workspace, then one reduce pass with the real tail): on single CTAs up to
+    # 128 rows, on CTA pairs above.  All three tails against the oracle, every
+    # zero-point form, K not a multiple of the 128-byte K step.
+    rng = np.random.default_rng(M + K + N)
+    dg = DevGemm(gpu)
+    for adt, bdt in [(np.uint8, np.int8), (np.int8, np.uint8)]:
+        A, B = rand8(rng, (M, K), adt), rand8(rng, (K, N), bdt)
+        for az, bz in [(None, None), (rand8(rng, 1, adt), None),
+                       (rand8(rng, M, adt), rand8(rng, N, bdt))]:
+            want = orc.matmul_integer_2d(A, B, az, bz)
+            for choice in (0, 1):
+                got = dg.matmul_integer(A, B, az, bz, choice)
+                assert np.array_equal(got, want), (adt, choice, np.argwhere(got != want)[:8])
+    # DEQUANT tail (DynamicQuantizeLinear -> MatMulInteger -> Cast -> Mul -> Add)
+    X = rng.normal(size=(M, K)).astype(np.float32)
+    W = rng.integers(-127, 128, (K, N), dtype=np.int8)
+    bias = rng.normal(0, 0.02, N).astype(np.float32)
+    ref = orc.dyn_quant_linear(X, W, np.float32(0.0157), bias)
+    Y = gpu.dyn_quant_linear(X, W, np.float32(0.0157), None, bias, 0)
+    assert Y.tobytes() == ref["Y"].tobytes()
+    # REQUANT tail (QLinearMatMul), per-column scales and zero points
+    A, B, bs, bz = qlinear_case(rng, (M,), K, N)
+    args = (A, np.float32(0.02), np.uint8(128), B, bs, bz, np.float32(0.5), np.uint8(128))
+    assert np.array_equal(gpu.qlinear_matmul(*args), orc.qlinear_matmul(*args))
+
+
 def test_matmul_integer_api_shapes(gpu, orc):
     rng = np.random.default_rng(12)
     # 3-D A times 2-D B (the encoder's broadcast-A form), host and device tensors
