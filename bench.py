@@ -824,6 +824,26 @@ def extra_kernels(env, peaks):
                    "to be read twice (range, then quantize): 9 B/element is what the two "
                    "launches move")
     out["dynamic_quantize_linear"] = dql
+    # A store-only stream for scale: the library fill of 1 GiB.  The f32 tails
+    # of the K = 1024 GEMMs are store streams (2.1 GB written per launch
+    # against 0.14 GB read), and a store stream does not reach the copy figure,
+    # which is half reads.
+    buf = torch.empty(1 << 30, dtype=torch.uint8, device=env.device)
+    ts = []
+    for i in range(7):
+        a, b = ev(), ev()
+        a.record(env.stream)
+        buf.zero_()
+        b.record(env.stream)
+        if i >= 2:
+            ts.append((a, b))
+    torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in ts) / len(ts)
+    out["hbm_fill"] = {"bytes": 1 << 30, "ms": ms, "gbs": (1 << 30) / ms / 1e6,
+                       "frac_of_copy": (1 << 30) / ms / 1e6 / peaks["hbm_gbs"],
+                       "kernel": "torch zero_ (library fill), not a kernel of this package"}
+    del buf
+    torch.cuda.empty_cache()
     return out
 
 
