@@ -74,15 +74,17 @@ def test_signedness_and_zero_point_forms(gpu, orc, adt, bdt, choice):
 @pytest.mark.parametrize("choice", [0, 2], ids=["auto", "simt"])
 @pytest.mark.parametrize("adt,bdt", [(np.uint8, np.uint8), (np.int8, np.int8),
                                      (np.int8, np.uint8), (np.uint8, np.int8)])
-def test_gemv_shaped_rows_1_to_16(gpu, orc, adt, bdt, choice):
-    # The GEMV-shaped kernels (dp4a up to 4 rows, mma.sync m16n8k32 with a
-    # permuted K order above): ragged M, K (not a multiple of 16 / of the
-    # 64-byte block / of a warp's run of blocks) and N (not a multiple of the
-    # 16 columns of a block), every signedness and zero-point form.
+def test_gemv_shaped_rows_1_to_32(gpu, orc, adt, bdt, choice):
+    # The GEMV-shaped kernels (dp4a for one row, mma.sync m16n8k32 with a
+    # permuted K order for 2..16) and the hand-over to the tensor-core kernels
+    # above 16 rows: ragged M, K (not a multiple of 16 / of the 64-byte block /
+    # of a warp's run of blocks) and N (not a multiple of the 16 columns of a
+    # block, more blocks than SMs), every signedness and zero-point form.
     rng = np.random.default_rng(41)
     dg = DevGemm(gpu)
     for M, K, N in [(1, 100, 33), (3, 1040, 17), (5, 7, 3), (8, 64, 16), (9, 144, 40),
-                    (13, 2000, 70), (16, 4160, 136), (16, 2048, 1000)]:
+                    (13, 2000, 70), (16, 4160, 136), (16, 2048, 1000), (2, 16, 8),
+                    (7, 1024, 2400), (16, 13312, 48), (23, 1168, 72), (32, 3072, 520)]:
         A, B = rand8(rng, (M, K), adt), rand8(rng, (K, N), bdt)
         for az, bz in [(None, None), (rand8(rng, 1, adt), None),
                        (rand8(rng, M, adt), rand8(rng, N, bdt))]:
