@@ -108,7 +108,8 @@ struct omcudaEncoder {
   omcudaRangeSyncFn range_sync = nullptr;
   void *range_sync_ctx = nullptr;
   // Captured runs (CUDA graphs): a run is a fixed sequence of 11 launches per
-  // layer whose arguments depend only on (x, y, batch, seq, stream), so the
+  // layer whose arguments depend only on (x, y, batch, seq, stream) and two
+  // process-wide settings (quantization mode, wait limit), so the
   // second run with the same key is captured and later ones are one graph
   // launch.  Dropped whenever a buffer a graph points into may have moved.
   struct Captured {
@@ -116,6 +117,9 @@ struct omcudaEncoder {
     float *y;
     int64_t batch, seq;
     cudaStream_t st;
+    // process-wide settings that end up in kernel arguments
+    int quant_mode;
+    uint64_t wait_ns;
     int seen;             // uncaptured runs so far with this key
     cudaGraphExec_t exec; // null until captured (or when capture failed)
     bool failed;
@@ -468,13 +472,16 @@ extern "C" int omcudaEncoderRunDev(omcudaEncoder *e, const float *x,
   if (!graphs_wanted() || e->tap || e->range_sync || e->profiling)
     return run_launches(e, x, batch, seq, y, st);
   omcudaEncoder::Captured *c = nullptr;
+  const int mode = quant_mode();
+  const uint64_t wait_ns = tc_wait_limit_ns();
   for (auto &k : e->captured)
-    if (k.x == x && k.y == y && k.batch == batch && k.seq == seq && k.st == st)
+    if (k.x == x && k.y == y && k.batch == batch && k.seq == seq && k.st == st &&
+        k.quant_mode == mode && k.wait_ns == wait_ns)
       c = &k;
   if (!c) {
     if (e->captured.size() >= 8)
       drop_graphs(e);
-    e->captured.push_back({x, y, batch, seq, st, 0, nullptr, false, 0});
+    e->captured.push_back({x, y, batch, seq, st, mode, wait_ns, 0, nullptr, false, 0});
     c = &e->captured.back();
   }
   if (c->exec) {

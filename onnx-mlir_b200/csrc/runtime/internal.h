@@ -36,6 +36,9 @@ struct PerDeviceInt {
 // OMCUDA_MODE_* flags set with omcudaSetQuantizationMode (process wide).
 int quant_mode();
 
+// Wait limit the tensor-core kernels are launched with (gemm_tc.cu).
+uint64_t tc_wait_limit_ns();
+
 // dql.cu
 int launch_quantize_with_params(const float *x, int64_t n, uint8_t *y,
     const float *params, cudaStream_t st);

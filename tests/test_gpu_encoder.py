@@ -146,6 +146,37 @@ def test_pipelined_submit_equals_run_into(gpu):
     enc.close()
 
 
+def test_replayed_runs_follow_the_quantization_mode(gpu):
+    # The quantization mode is a process-wide setting that ends up in kernel
+    # arguments: a run captured in one mode must not be replayed in another.
+    B, S, H, heads, F = 2, 128, 128, 2, 256
+    layers = make_encoder(17, H, F, 2)
+    x = np.random.default_rng(18).normal(size=(B, S, H)).astype(np.float32)
+    L = gpu.lib()
+    enc = gpu.Encoder(H, heads, F, layers)
+    tx = gpu.Tensor.from_numpy(x).to_device()
+    ty = gpu.Tensor.device_empty((B, S, H), np.float32)
+    try:
+        for _ in range(4):          # kernel by kernel, captured, replayed twice
+            enc.run_into(tx, ty)
+        y_default = ty.numpy()
+        L.omcudaSetQuantizationMode(1)  # OMCUDA_MODE_NO_ZERO_POINT
+        enc.run_into(tx, ty)
+        y_mode = ty.numpy()
+        fresh = gpu.Encoder(H, heads, F, layers)
+        want_mode = fresh.run(x)
+        fresh.close()
+        L.omcudaSetQuantizationMode(0)
+        enc.run_into(tx, ty)
+        y_back = ty.numpy()
+    finally:
+        L.omcudaSetQuantizationMode(0)
+    enc.close()
+    assert np.array_equal(y_mode, want_mode)
+    assert not np.array_equal(y_mode, y_default)
+    assert np.array_equal(y_back, y_default)
+
+
 def test_encoder_rejects_wrong_input(gpu):
     layers = make_encoder(11, 128, 256, 1)
     enc = gpu.Encoder(128, 2, 256, layers)
