@@ -479,3 +479,35 @@ def test_random_shapes_against_exact_products(gpu, seed):
     Y = dg.matmul_integer(A, B, za, None, 1)
     want = (A.astype(np.float64) - za) @ B.astype(np.float64)
     assert np.array_equal(Y.astype(np.float64), want), (M, N, K, a_signed, b_signed, za)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_few_rows_long_k_auto_dispatch(gpu, seed):
+    # The dispatcher's small-M territory at random: 1..600 rows, K up to 16384,
+    # ragged N -- GEMV-shaped kernels (1..16 rows), split-K on single CTAs and
+    # on CTA pairs (K >= 8192, few tiles), narrow tiles, the 2-CTA kernel at
+    # three quarters occupancy.  Every output element against the exact integer
+    # product (float64 holds it exactly), per-row A zero points included.
+    from gpu_util import DevGemm
+    rng = np.random.default_rng(2000 + seed)
+    M = int(rng.choice([1, 2, 3, 7, 8, 15, 16, 17, 31, 64, 100, 128, 129, 200, 256, 300,
+                        511, 512, 513, 600]))
+    if seed % 3 == 0:
+        M = int(rng.integers(1, 601))
+    N = int(rng.integers(8, 3000))
+    if seed % 2 == 0:
+        N = (N + 3) & ~3
+    K = 16 * int(rng.integers(1, 1025))
+    if seed % 4 == 1:
+        K = 16 * int(rng.integers(512, 1025))  # split-K territory
+    a_signed, b_signed = bool(rng.integers(0, 2)), bool(rng.integers(0, 2))
+    A = rng.integers(-128 if a_signed else 0, 128 if a_signed else 256, (M, K)).astype(
+        np.int8 if a_signed else np.uint8)
+    B = rng.integers(-128 if b_signed else 0, 128 if b_signed else 256, (K, N)).astype(
+        np.int8 if b_signed else np.uint8)
+    za = rng.integers(-128 if a_signed else 0, 128 if a_signed else 256,
+                      M if seed % 5 == 0 else 1).astype(A.dtype)
+    dg = DevGemm(gpu)
+    Y = dg.matmul_integer(A, B, za, None, 0)
+    want = (A.astype(np.float64) - za.astype(np.float64).reshape(-1, 1)) @ B.astype(np.float64)
+    assert np.array_equal(Y.astype(np.float64), want), (M, N, K, a_signed, b_signed)
