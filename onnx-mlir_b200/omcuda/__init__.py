@@ -162,10 +162,41 @@ class Tensor:
     """An OMTensor wrapper.  Host tensors keep their numpy array alive; device
     tensors own a buffer from the library pool."""
 
-    def __init__(self, handle, array=None, device=False):
+    def __init__(self, handle, array=None, device=False, borrowed=False):
         self.handle = handle
         self.array = array
         self.device = device
+        self.borrowed = borrowed  # a device buffer owned by someone else
+
+    @staticmethod
+    def from_cuda_array(obj):
+        """Zero-copy view of a device buffer some other library owns: any object
+        with __cuda_array_interface__ (a torch.Tensor on the GPU, a cupy array).
+        The OMTensor is non-owning and keeps `obj` alive; the caller orders the
+        two libraries' streams (run on the same stream via set_stream, or
+        synchronize in between)."""
+        cai = obj.__cuda_array_interface__
+        if cai.get("strides") is not None:
+            raise ValueError("from_cuda_array needs a contiguous (C-order) buffer")
+        dt = np.dtype(cai["typestr"])
+        if dt not in _NP2OM:
+            raise TypeError("unsupported element type %s" % dt)
+        shape_t = tuple(int(d) for d in cai["shape"])
+        shape = (ctypes.c_int64 * max(len(shape_t), 1))(*shape_t)
+        ptr = ctypes.c_void_p(int(cai["data"][0]))
+        h = lib().omTensorCreate(ptr, shape, len(shape_t), _NP2OM[dt])
+        if not h:
+            raise MemoryError("omTensorCreate failed")
+        return Tensor(h, obj, True, True)
+
+    @property
+    def __cuda_array_interface__(self):
+        """Device tensors can be handed to torch / cupy without a copy
+        (torch.as_tensor(t, device="cuda")); the Tensor must outlive the view."""
+        if not self.device:
+            raise AttributeError("host tensor")
+        return {"shape": self.shape, "typestr": np.dtype(self.dtype).str,
+                "data": (int(self.data_ptr or 0), False), "version": 2, "strides": None}
 
     @staticmethod
     def from_numpy(a):
@@ -230,7 +261,7 @@ class Tensor:
 
     def free(self):
         if self.handle:
-            if self.device:
+            if self.device and not self.borrowed:
                 lib().omcudaTensorDestroy(self.handle)
             else:
                 lib().omTensorDestroy(self.handle)
@@ -251,6 +282,8 @@ def _wrap(x, device):
     """numpy array / Tensor / None -> Tensor on the requested side."""
     if x is None or isinstance(x, Tensor):
         return x
+    if hasattr(x, "__cuda_array_interface__"):
+        return Tensor.from_cuda_array(x)
     t = Tensor.from_numpy(np.asarray(x))
     return t.to_device() if device else t
 

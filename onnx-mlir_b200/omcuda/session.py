@@ -5,7 +5,10 @@ entry_points, set_entry_point, input_signature, output_signature), on top of
 the library's omcudaSession* C API.  Device-aware: run() takes numpy arrays
 (host tensors, results come back as numpy arrays) or omcuda.Tensor objects
 (passed as they are; device tensors in give device tensors out, so that models
-can be chained without touching host memory)."""
+can be chained without touching host memory) or any object with
+__cuda_array_interface__, e.g. a torch.Tensor on the GPU (wrapped without a
+copy; device results expose the same interface, so torch.as_tensor(result,
+device="cuda") is a view, not a copy)."""
 import ctypes
 import json
 
@@ -66,7 +69,9 @@ class OMExecutionSession:
         """inputs: list of numpy arrays and / or omcuda.Tensor objects.  Returns
         a list: numpy arrays for host results, Tensors for device results."""
         L = self.L
-        ts = [x if isinstance(x, Tensor) else Tensor.from_numpy(np.asarray(x)) for x in inputs]
+        ts = [x if isinstance(x, Tensor)
+              else Tensor.from_cuda_array(x) if hasattr(x, "__cuda_array_interface__")
+              else Tensor.from_numpy(np.asarray(x)) for x in inputs]
         arr = (ctypes.c_void_p * max(len(ts), 1))(*[t.handle for t in ts])
         ins = L.omTensorListCreate(arr, len(ts))
         ctypes.set_errno(0)

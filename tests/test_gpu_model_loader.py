@@ -76,6 +76,42 @@ def test_encoder_model_equals_the_harness_and_chains_on_device(gpu, tmp_path):
     s.close()
 
 
+def test_torch_tensors_pass_through_without_a_copy(gpu, orc, tmp_path):
+    # Device buffers of another library (anything with __cuda_array_interface__:
+    # a torch.Tensor on the GPU) go in as non-owning device OMTensors, and a
+    # device result is visible to torch as a view of the same memory.
+    import torch
+    from omcuda import model_builder
+    from omcuda.session import OMExecutionSession
+    rng = np.random.default_rng(44)
+    X = rng.normal(size=(64, 256)).astype(np.float32)
+    W = rng.integers(-127, 128, (256, 320), dtype=np.int8)
+    bias = rng.normal(0, 0.02, 320).astype(np.float32)
+    so = model_builder.build_dyn_quant_linear_model(str(tmp_path), "torch_io", W,
+                                                    np.float32(0.01), bias)
+    s = OMExecutionSession(so)
+    want = orc.dyn_quant_linear(X, W, np.float32(0.01), bias)["Y"]
+    xt = torch.from_numpy(X).cuda()
+    torch.cuda.synchronize()
+    view = gpu.Tensor.from_cuda_array(xt)
+    assert view.device and view.data_ptr == xt.data_ptr() and view.shape == (64, 256)
+    (yd,) = s.run([xt])
+    assert isinstance(yd, gpu.Tensor) and yd.device
+    gpu.synchronize()
+    yt = torch.as_tensor(yd, device="cuda")
+    assert yt.data_ptr() == yd.data_ptr and tuple(yt.shape) == (64, 320)
+    assert yt.cpu().numpy().tobytes() == want.tobytes()
+    # the plain operator API takes them too
+    xq, sc, zp = gpu.dynamic_quantize_linear(xt, device=True)
+    gpu.synchronize()
+    ref = orc.dynamic_quantize_linear(X)
+    assert np.array_equal(torch.as_tensor(xq, device="cuda").cpu().numpy(), ref[0])
+    with pytest.raises(ValueError):
+        gpu.Tensor.from_cuda_array(xt.t())      # not contiguous
+    del view
+    s.close()
+
+
 def test_command_line_runner_round_trip(gpu, tmp_path, capsys):
     from omcuda import model_builder, run_model
     rng = np.random.default_rng(44)
