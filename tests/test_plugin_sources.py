@@ -137,3 +137,32 @@ def test_accelerator_overrides_every_pure_virtual():
     cm = open(os.path.join(ACCEL, "CMakeLists.txt")).read()
     for src in re.findall(r"^\s+([\w/]+\.cpp)\s*$", cm, flags=re.M):
         assert os.path.exists(os.path.join(ACCEL, src)), src
+
+
+def test_backend_test_list_names_exported_symbols_of_lowered_ops(built):
+    # plugin/test/accelerators/CUDA/backend/CMakeLists.txt lists, per ONNX
+    # backend node test, the library function the compiled model must refer to
+    # (the instruction check of test/accelerators/NNPA/backend).  Every symbol
+    # must be a krnl.call target of the call table and an export of the
+    # library; every listed test must belong to an op with a table entry.
+    lib = exported()
+    table = {c[0] for c in table_calls()}
+    src = open(os.path.join(PLUGIN, "test", "accelerators", "CUDA", "backend",
+                            "CMakeLists.txt")).read()
+    body = src[src.index("set(CUDA_TEST_LIST"):]
+    body = body[:body.index("\n)\n")]
+    entries = re.findall(r'^\s*(test_\w+),(\w+),("[^"]*"|NO_DYNAMIC_SHAPE_TEST)\s*$', body, re.M)
+    assert len(entries) >= 15
+    for test, symbol, dims in entries:
+        assert symbol in table, (test, symbol)
+        assert hasattr(lib, symbol), symbol
+        op = symbol[len("omcuda"):].lower()
+        assert op.replace("normalization", "_normalization") in test or op in test.replace("_", ""), \
+            (test, symbol)
+    # the ops of the quantized path are all there
+    assert {"omcudaDynamicQuantizeLinear", "omcudaQuantizeLinear", "omcudaDequantizeLinear",
+            "omcudaMatMulInteger", "omcudaQLinearMatMul"} <= {e[1] for e in entries}
+    num = open(os.path.join(PLUGIN, "test", "accelerators", "CUDA", "numerical",
+                            "CMakeLists.txt")).read()
+    for symbol in re.findall(r"^add_cuda_numerical_test\(Test\w+ (\w+)", num, re.M):
+        assert symbol in table and hasattr(lib, symbol), symbol
