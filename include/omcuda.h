@@ -341,7 +341,12 @@ typedef struct {
   /* Optional running range (omcudaDevRangeInit) of the f32 outputs, for a
    * following DynamicQuantizeLinear. May be NULL. */
   void *out_minmax;
-  /* 0 = choose; 1 = force the tcgen05 kernel; 2 = force the SIMT kernel. */
+  /* 0 = choose (GEMV-shaped kernels up to 16 rows; tcgen05 above, with a
+   * split-K pass through a pool workspace for up to 512 rows, K >= 8192 and
+   * few tiles -- not inside a stream capture; the SIMT kernels when K is not
+   * a multiple of 16 or A is not 16-byte aligned); 1 = force the tcgen05
+   * kernels; 2 = force the SIMT (dp4a / mma.sync) kernels.  Every choice
+   * gives the same bytes. */
   int kernel_choice;
   /* DEQUANT only: optional f32 [M,N] added last (y = tail(acc) + residual),
    * the onnx.Add of a residual connection around the linear
