@@ -507,7 +507,13 @@ int omcudaEncoderRunInto(omcudaEncoder *enc, OMTensor *y, const OMTensor *x);
  * what omcudaEncoderRunInto computes. */
 int omcudaEncoderSubmit(omcudaEncoder *enc, OMTensor *y, const OMTensor *x);
 int omcudaEncoderWait(omcudaEncoder *enc);
-/* Device-pointer form: x, y are device f32 [batch*seq, hidden]. */
+/* Device-pointer form: x, y are device f32 [batch*seq, hidden].  An encoder
+ * object owns one workspace: its runs are ordered by the caller (one host
+ * thread at a time, runs on different streams ordered against each other);
+ * use one encoder per concurrent stream.  From the third run with the same
+ * (x, y, batch, seq, stream) on, the run is one CUDA-graph launch of the
+ * sequence captured on the second (OMCUDA_ENCODER_GRAPH=0 switches that off;
+ * a run on a stream that is itself being captured joins that capture). */
 int omcudaEncoderRunDev(omcudaEncoder *enc, const float *x, int64_t batch,
     int64_t seq, float *y, void *stream);
 /* Optional: bracket every int8 GEMM launch of later runs with CUDA events on
