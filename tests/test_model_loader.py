@@ -90,3 +90,23 @@ def test_run_without_gpu_fails_like_the_reference(models, omcuda):
     with pytest.raises(omcuda.OmcudaError):
         s.run([np.zeros((1, 8, 128), np.float32)])
     s.close()
+
+
+def test_cuda_array_interface_objects_are_checked_before_wrapping():
+    # The zero-copy wrapper of foreign device buffers refuses what it cannot
+    # describe as a dense OMTensor (no GPU needed to say no).
+    import numpy as np
+    import pytest
+    import omcuda
+
+    class Fake:
+        def __init__(self, **cai):
+            self.__cuda_array_interface__ = dict(version=2, data=(4096, False), **cai)
+
+    with pytest.raises(ValueError):
+        omcuda.Tensor.from_cuda_array(Fake(shape=(4, 4), typestr="<f4", strides=(4, 16)))
+    with pytest.raises(TypeError):
+        omcuda.Tensor.from_cuda_array(Fake(shape=(4,), typestr="<c8", strides=None))
+    host = omcuda.Tensor.__new__(omcuda.Tensor)
+    host.handle, host.array, host.device, host.borrowed = None, None, False, False
+    assert not hasattr(host, "__cuda_array_interface__")
